@@ -1,0 +1,176 @@
+/*
+ * nanoserve_b200 — C ABI of the sm_100a kernels behind nanoserve's continuous-batching forward path.
+ *
+ * Every entry point takes raw device pointers, explicit sizes / strides (in ELEMENTS unless a name says
+ * bytes), a dtype enum and the CUDA stream to launch on, and returns an ns_status (0 = ok). Nothing here
+ * allocates, frees, synchronises or reads device memory on the host, so every call can be captured in a
+ * CUDA graph. The caller owns all buffers, including the attention workspace. After a non-zero return,
+ * ns_last_error() gives a human-readable reason (thread-local).
+ *
+ * The reference has no FFI: its kernels are Python functions that the model imports by name. Each
+ * declaration below names the reference function it stands in for (path inside the reference project).
+ */
+#ifndef NANOSERVE_B200_H
+#define NANOSERVE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    NS_OK = 0,
+    NS_ERR_INVALID_ARG = 1,   /* null pointer, negative size, misaligned buffer */
+    NS_ERR_UNSUPPORTED = 2,   /* head layout / dtype / block size this build has no kernel for */
+    NS_ERR_WORKSPACE = 3,     /* workspace too small for the given batch */
+    NS_ERR_CUDA = 4           /* a CUDA runtime call (launch, attribute) failed */
+} ns_status;
+
+typedef enum { NS_BF16 = 0, NS_F32 = 1 } ns_dtype;
+
+/* Library version (major*10000 + minor*100 + patch) and last error text of the calling thread. */
+int ns_version(void);
+const char* ns_last_error(void);
+/* Number of SMs of the current device (grid sizing of the persistent kernels); <= 0 on error. */
+int ns_sm_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Fused token-wise ops.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* out = weight * rmsnorm(r), r = residual + x rounded to dtype (or r = x when residual == NULL); when
+ * residual != NULL, r is also stored to residual_out. fp32 mean of squares, the normalised value is rounded
+ * to dtype BEFORE the weight multiply. rows x hidden, contiguous; hidden % 8 == 0 (bf16) / % 4 == 0 (f32).
+ * Replaces: nanoserve/kernels/fused.py:45 rms_norm (+ _rms_norm_kernel :26-42); torch twin
+ * nanoserve/model.py:140-146. */
+int ns_add_rmsnorm(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
+                   int64_t rows, int32_t hidden, float eps, int dtype, void* stream);
+
+/* out[r, c] = round(silu(gate_up[r, c])) * gate_up[r, inter + c], rounded; gate_up is [rows, 2*inter].
+ * Replaces: nanoserve/kernels/fused.py:75 silu_mul (+ _silu_mul_kernel :63-72). */
+int ns_silu_mul(const void* gate_up, void* out, int64_t rows, int32_t inter, int dtype, void* stream);
+
+/* cos/sin tables [n_tokens, head_dim] in dtype from int64 positions and fp32 inv_freq[head_dim/2]:
+ * angle = float(position) * inv_freq[d % (head_dim/2)], cos/sin in fp32, then rounded to dtype.
+ * Replaces: nanoserve/model.py:212-217 Qwen2Model.rope. */
+int ns_rope_cos_sin(const int64_t* positions, const float* inv_freq, void* cos_out, void* sin_out,
+                    int64_t n_tokens, int32_t head_dim, int dtype, void* stream);
+
+/* Per token: rotate the n_heads query heads and n_kv_heads key heads of one merged QKV row (non-interleaved
+ * halves; every product and every sum rounded to dtype), copy the value heads, store q / k / v densely
+ * (any of q_out, k_out, v_out may be NULL to skip that store) and, when k_cache != NULL, store k and v into
+ * one layer's paged pool [num_blocks, block_size, n_kv_heads, head_dim] (contiguous) at flat row slots[t].
+ * Replaces: nanoserve/kernels/fused.py:156 rope_qkv (+ _rope_qkv_kernel :107-153) and the unfused
+ * nanoserve/kv_cache.py:274-279 PagedKVCache.write. */
+int ns_rope_qkv_kvwrite(const void* qkv, const void* cos, const void* sin, void* q_out, void* k_out, void* v_out,
+                        void* k_cache, void* v_cache, const int64_t* slots, int64_t n_tokens, int32_t n_heads,
+                        int32_t n_kv_heads, int32_t head_dim, int dtype, void* stream);
+
+/* Plain KV write: pool_row[slots[t]] = k_new[t] / v_new[t] for t < n_tokens (rows of n_kv_heads*head_dim).
+ * Replaces: nanoserve/kv_cache.py:274-279 PagedKVCache.write. */
+int ns_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int64_t* slots,
+                int64_t n_tokens, int32_t row_elems, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Ragged paged attention.
+ *
+ * A batch is S sequences over N flattened query tokens: sequence s owns query rows
+ * cu_seqlens[s] .. cu_seqlens[s+1]-1 and seq_lens[s] keys (cached context + this step's tokens, whose K/V
+ * are already in the pool); query j of a sequence with T new tokens sees keys 0 .. seq_len - T + j.
+ * Sequences with T == 1 are "decode" rows (HBM-bound, split over the KV length); T > 1 are prefill chunks
+ * (tensor-core tiles). Keys live in one layer's pool [num_blocks, block_size, n_kv_heads, head_dim]
+ * addressed through block_tables[row(s), j] (int32, row stride table_stride), row(s) = table_rows[s], or s
+ * when table_rows == NULL. cu_seqlens == NULL means every sequence has exactly one query token.
+ *
+ * The tensor-core path (bf16, block_size 16, head_dim 64 / 128, GQA group <= 8) needs a caller-owned
+ * workspace: ns_attn_workspace_bytes(ws_max_seqs, ws_max_tokens, ...) bytes, 256-byte aligned, zeroed once
+ * before first use; the same (ws_max_seqs, ws_max_tokens) must be passed to every call using it. Other
+ * layouts and fp32 run the scalar kernel and ignore the workspace.
+ * ---------------------------------------------------------------------------------------------- */
+
+int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim);
+
+/* Build the per-step plan in the workspace (shared by every layer of the step): the decode rows' KV blocks
+ * are cut into equal ranges, one per persistent decode CTA, and prefill chunks into query tiles.
+ * No reference counterpart (the reference plans on the host, nanoserve/kv_manager.py:158-179). */
+int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int32_t n_seqs, int32_t block_size,
+                 int32_t n_heads, int32_t head_dim, void* workspace, int64_t workspace_bytes, int32_t ws_max_seqs,
+                 int32_t ws_max_tokens, void* stream);
+
+/* One layer of attention over the batch described by the last ns_attn_plan call on this workspace.
+ * q, out: [N, n_heads, head_dim], row strides q_stride / out_stride (head stride = head_dim).
+ * Pool strides: pool_block_stride (per block), pool_pos_stride (per token in a block), pool_head_stride.
+ * Replaces: nanoserve/model.py:262-323 Qwen2Model._attend (per-sequence SDPA loop, gather, masks) together
+ * with nanoserve/kernels/paged_attention.py:85-105 paged_attention_decode (_paged_decode_kernel :34-82). */
+int ns_ragged_paged_attn(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
+                         const int32_t* table_rows, const int32_t* seq_lens, const int32_t* cu_seqlens, void* out,
+                         int32_t n_seqs, int64_t n_tokens, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                         int32_t block_size, int64_t table_stride, int64_t q_stride, int64_t out_stride,
+                         int64_t pool_block_stride, int64_t pool_pos_stride, int64_t pool_head_stride, float scale,
+                         int dtype, void* workspace, int64_t workspace_bytes, int32_t ws_max_seqs,
+                         int32_t ws_max_tokens, void* stream);
+
+/* Decode-only convenience: plan + attention for `batch` rows of one query token each (context_lens include
+ * the new token, whose K/V are already written).
+ * Replaces: nanoserve/kernels/paged_attention.py:85-105 paged_attention_decode. */
+int ns_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
+                         const int32_t* context_lens, void* out, int32_t batch, int32_t n_heads,
+                         int32_t n_kv_heads, int32_t head_dim, int32_t block_size, int64_t table_stride,
+                         int64_t q_stride, int64_t out_stride, int64_t pool_block_stride, int64_t pool_pos_stride,
+                         int64_t pool_head_stride, float scale, int dtype, void* workspace,
+                         int64_t workspace_bytes, int32_t ws_max_seqs, int32_t ws_max_tokens, void* stream);
+
+/* Scalar implementation of the same ragged attention (fp32 accumulation, one warp per (query token, head));
+ * any head layout, bf16 or fp32. Serves fp32 models and on-device cross-checks.
+ * Replaces: nanoserve/kernels/paged_attention.py:108-121 paged_attention_reference (gather + SDPA). */
+int ns_ragged_paged_attn_simple(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
+                                const int32_t* table_rows, const int32_t* seq_lens, const int32_t* cu_seqlens,
+                                void* out, int32_t n_seqs, int64_t n_tokens, int32_t n_heads, int32_t n_kv_heads,
+                                int32_t head_dim, int32_t block_size, int64_t table_stride, int64_t q_stride,
+                                int64_t out_stride, int64_t pool_block_stride, int64_t pool_pos_stride,
+                                int64_t pool_head_stride, float scale, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Step metadata and greedy sampling on the device.
+ *
+ * The host sends one packed int32 buffer per step: a header, one record per scheduled sequence
+ * {seat, ctx, n_new, tok_off}, the block-table entries appended since the previous step
+ * {seat, index, block}, and the token ids of prefill chunks. One kernel expands it into the static buffers
+ * a CUDA graph reads, padded to the graph bucket with rows that only touch the garbage block.
+ * Replaces the host-side list building of nanoserve/kv_manager.py:153-190 (begin_step / seq_input /
+ * decode_meta / forward_kwargs / graph_inputs) and the per-step torch.tensor(...) uploads of
+ * nanoserve/cuda_graphs.py:112-117 and :250-252.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t n_seqs;          /* real sequences this step */
+    int32_t n_tokens;        /* real flattened tokens this step */
+    int32_t pad_seqs;        /* sequences after padding to the graph bucket (>= n_seqs); padding = 1 token each */
+    int32_t pad_tokens;      /* token rows to fill (>= n_tokens + pad_seqs - n_seqs) */
+    int32_t n_appends;       /* block-table appends carried by this buffer */
+    int32_t garbage_block;   /* block every padding row reads and writes */
+    int32_t block_size;
+    int32_t table_width;     /* row stride of the device block-table mirror */
+} ns_step_header;
+
+/* packed (device, int32): [ns_step_header][n_seqs x {seat, ctx, n_new, tok_off}][n_appends x {seat, index,
+ * block}][token ids ...]. tok_off >= 0: the sequence's n_new token ids start at token ids[tok_off];
+ * tok_off == -1: a single decode token read from last_tokens[seat] (left there by ns_argmax_rows).
+ * Outputs: tokens / positions / slot_mapping int64 [pad_tokens]; cu_seqlens int32 [pad_seqs + 1]; seq_lens
+ * int32 [pad_seqs]; seat_of int32 [pad_seqs] (row of table_mirror per sequence; padding -> pad_seat, whose
+ * row must start with garbage_block); last_rows int64 [pad_seqs] (flattened row of each sequence's last token). */
+int ns_build_step_metadata(const int32_t* packed, int32_t packed_ints, int32_t* table_mirror,
+                           const int64_t* last_tokens, int32_t pad_seat, int64_t* tokens, int64_t* positions,
+                           int64_t* slot_mapping, int32_t* cu_seqlens, int32_t* seq_lens, int32_t* seat_of,
+                           int64_t* last_rows, int32_t max_seqs, int32_t max_tokens, void* stream);
+
+/* out[r] = argmax(logits[r, :vocab]) (lowest index on ties); when seat_of != NULL also
+ * last_tokens[seat_of[r]] = out[r], so the next step's decode token never leaves the device.
+ * Replaces: nanoserve/engine.py:239 logits.argmax(-1) (the .tolist() copy stays with the caller). */
+int ns_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t vocab, int64_t* out,
+                   const int32_t* seat_of, int64_t* last_tokens, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOSERVE_B200_H */

@@ -1,0 +1,91 @@
+"""ctypes binding of libnanoserve_b200.so (the C ABI declared in include/nanoserve_b200.h).
+
+There is no fallback: if the library is missing or a call fails, the caller gets an exception. The product
+path never routes through PyTorch ops or CPU code for work this library owns.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libnanoserve_b200.so"
+
+NS_BF16, NS_F32 = 0, 1
+
+# name -> (restype, argtypes); mirrors include/nanoserve_b200.h declaration by declaration.
+_P, _I32, _I64, _F = c_void_p, c_int32, c_int64, c_float
+SIGNATURES: dict[str, tuple] = {
+    "ns_version": (c_int, []),
+    "ns_last_error": (c_char_p, []),
+    "ns_sm_count": (c_int, []),
+    "ns_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, _F, c_int, _P]),
+    "ns_silu_mul": (c_int, [_P, _P, _I64, _I32, c_int, _P]),
+    "ns_rope_cos_sin": (c_int, [_P, _P, _P, _P, _I64, _I32, c_int, _P]),
+    "ns_rope_qkv_kvwrite": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, c_int, _P]),
+    "ns_kv_write": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, c_int, _P]),
+    "ns_attn_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
+    "ns_attn_plan": (c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I64, _I32, _I32, _P]),
+    "ns_ragged_paged_attn": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _I32, _I64, _I64,
+                                     _I64, _I64, _I64, _I64, _F, c_int, _P, _I64, _I32, _I32, _P]),
+    "ns_paged_attn_decode": (c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I64, _I64, _I64, _I64,
+                                     _I64, _I64, _F, c_int, _P, _I64, _I32, _I32, _P]),
+    "ns_ragged_paged_attn_simple": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _I32, _I64,
+                                            _I64, _I64, _I64, _I64, _I64, _F, c_int, _P]),
+    "ns_build_step_metadata": (c_int, [_P, _I32, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P]),
+    "ns_argmax_rows": (c_int, [_P, _I64, _I32, _I32, _P, _P, _P, c_int, _P]),
+}
+
+_lib = None
+
+
+class NanoserveB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built (no CPU / PyTorch fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NanoserveB200Error(
+                f"{LIB_PATH} is missing: build it with `python -m nanoserve_b200.build` "
+                "(the sm_100a kernels are the only implementation of these ops)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)      # AttributeError here = header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def call(name: str, *args) -> None:
+    """Invoke a status-returning entry point; raise with the library's message on failure."""
+    lib = load()
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise NanoserveB200Error(f"{name} failed (status {status}): {lib.ns_last_error().decode()}")
+
+
+def dtype_code(dtype) -> int:
+    import torch
+    if dtype == torch.bfloat16:
+        return NS_BF16
+    if dtype == torch.float32:
+        return NS_F32
+    raise NotImplementedError(f"nanoserve_b200 kernels handle bfloat16 and float32, not {dtype}")
+
+
+def stream_ptr() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NanoserveB200Error("nanoserve_b200 kernels run on CUDA tensors only (there is no CPU path)")

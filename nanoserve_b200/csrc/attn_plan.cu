@@ -1,0 +1,124 @@
+// Per-step attention plan: one small kernel whose output every layer of the step reuses.
+#include "attn_plan.cuh"
+#include "common.cuh"
+
+namespace ns {
+
+constexpr int kPlanThreads = 1024;
+
+// Block-wide exclusive scan of one int per thread (kPlanThreads threads). Returns the exclusive prefix and the
+// block total through `total`.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sums[lane];
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_sums[lane] = winc - w;          // exclusive prefix of the warp sums
+        if (lane == 31) warp_sums[32] = winc;
+    }
+    __syncthreads();
+    const int excl = warp_sums[warp] + inc - v;
+    total = warp_sums[32];
+    __syncthreads();
+    return excl;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* __restrict__ seq_lens,
+                                                                 const int32_t* __restrict__ cu_seqlens, int n_seqs,
+                                                                 int block_size, int decode_ctas, uint8_t* ws,
+                                                                 WsLayout L, int max_items) {
+    __shared__ int warp_sums[33];
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + L.header);
+    int32_t* dec_seq = reinterpret_cast<int32_t*>(ws + L.dec_seq);
+    int32_t* dec_indptr = reinterpret_cast<int32_t*>(ws + L.dec_indptr);
+    int32_t* cta_first = reinterpret_cast<int32_t*>(ws + L.cta_first);
+    int2* items = reinterpret_cast<int2*>(ws + L.prefill_items);
+
+    int n_dec = 0, dec_blocks = 0, n_items = 0;
+    for (int base = 0; base < n_seqs; base += kPlanThreads) {
+        const int s = base + threadIdx.x;
+        int is_dec = 0, nb = 0, tiles = 0, T = 0;
+        if (s < n_seqs) {
+            T = cu_seqlens ? cu_seqlens[s + 1] - cu_seqlens[s] : 1;
+            const int len = seq_lens[s];
+            if (T == 1) {
+                is_dec = 1;
+                nb = (len + block_size - 1) / block_size;
+            } else if (T > 1) {
+                tiles = (T + kPrefillTileTokens - 1) / kPrefillTileTokens;
+            }
+        }
+        int tot;
+        const int pos = block_exclusive_scan(is_dec, warp_sums, tot);
+        const int d_tot = tot;
+        const int boff = block_exclusive_scan(nb, warp_sums, tot);
+        const int b_tot = tot;
+        const int ioff = block_exclusive_scan(tiles, warp_sums, tot);
+        const int i_tot = tot;
+        if (is_dec) {
+            dec_seq[n_dec + pos] = s;
+            dec_indptr[n_dec + pos] = dec_blocks + boff;
+        }
+        // Latest query tile first: under the causal mask it attends to the most keys, so the heaviest items
+        // start earliest.
+        for (int k = 0; k < tiles; ++k) {
+            const int idx = n_items + ioff + k;
+            if (idx < max_items) items[idx] = make_int2(s, (tiles - 1 - k) * kPrefillTileTokens);
+        }
+        n_dec += d_tot;
+        dec_blocks += b_tot;
+        n_items += i_tot;
+    }
+    if (threadIdx.x == 0) dec_indptr[n_dec] = dec_blocks;
+    __syncthreads();
+
+    int per = (dec_blocks + decode_ctas - 1) / decode_ctas;
+    if (per < 1) per = 1;
+    const int used = (dec_blocks + per - 1) / per;
+    // cta_first[c] = decode row containing block-unit c*per (binary search over dec_indptr).
+    for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) {
+        const int64_t u = (int64_t)c * per;
+        int lo = 0, hi = n_dec;               // answer in [0, n_dec]; n_dec when u >= dec_blocks
+        if (u >= dec_blocks) {
+            lo = n_dec;
+        } else {
+            while (hi - lo > 1) {             // invariant: dec_indptr[lo] <= u < dec_indptr[hi]
+                const int mid = (lo + hi) >> 1;
+                if (dec_indptr[mid] <= u) lo = mid; else hi = mid;
+            }
+        }
+        cta_first[c] = lo;
+    }
+    if (threadIdx.x == 0) {
+        hdr->n_dec = n_dec;
+        hdr->dec_total = dec_blocks;
+        hdr->dec_per_cta = per;
+        hdr->dec_ctas = used;
+        hdr->n_prefill_items = n_items < max_items ? n_items : max_items;
+        hdr->n_seqs = n_seqs;
+        hdr->block_size = block_size;
+        hdr->reserved = 0;
+    }
+}
+
+int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int n_seqs, int block_size, int decode_ctas,
+                     void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
+    attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, n_seqs, block_size, decode_ctas,
+                                                 (uint8_t*)ws, L, max_items);
+    return check_launch("attn_plan");
+}
+
+}  // namespace ns

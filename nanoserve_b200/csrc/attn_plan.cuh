@@ -1,0 +1,75 @@
+// Workspace layout and per-step plan shared by the ragged paged-attention kernels.
+//
+// The plan is built once per engine step (ns_attn_plan) and reused by every layer:
+//   * decode rows (one query token) are listed in batch order; their KV blocks form one flattened list of
+//     `dec_total` block-units that is cut into equal contiguous ranges, one per persistent decode CTA
+//     (stream-K style): every CTA reads the same number of bytes whatever the mix of context lengths;
+//   * prefill rows are cut into query tiles, heaviest (latest) tile first.
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace ns {
+
+constexpr int kMaxDecodeCtas = 1024;      // upper bound on the persistent decode grid
+constexpr int kMaxKvHeads = 8;            // counters per decode row
+constexpr int kPrefillTileTokens = 16;    // query tokens per prefill work item
+
+struct PlanHeader {
+    int32_t n_dec;          // decode rows
+    int32_t dec_total;      // sum of their KV blocks
+    int32_t dec_per_cta;    // block-units per decode CTA (>= 1)
+    int32_t dec_ctas;       // decode CTAs that own a non-empty range
+    int32_t n_prefill_items;
+    int32_t n_seqs;
+    int32_t block_size;
+    int32_t reserved;
+};
+
+// Byte offsets inside the workspace; everything 256-byte aligned.
+struct WsLayout {
+    int64_t header;         // PlanHeader
+    int64_t dec_seq;        // int32[max_seqs]    batch index of decode row i
+    int64_t dec_indptr;     // int32[max_seqs+1]  first block-unit of decode row i
+    int64_t cta_first;      // int32[kMaxDecodeCtas+1] decode row holding the first block-unit of each CTA
+    int64_t counters;       // int32[max_seqs*kMaxKvHeads] arrivals per (decode row, kv head); zero between launches
+    int64_t prefill_items;  // int2[max_prefill_items] (batch index, first query token of the tile)
+    int64_t partials;       // float[kMaxDecodeCtas*2][n_heads][head_dim+2]
+    int64_t total;
+};
+
+__host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+__host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int n_heads, int head_dim) {
+    WsLayout L;
+    int64_t o = 0;
+    L.header = o;         o = align256(o + (int64_t)sizeof(PlanHeader));
+    L.dec_seq = o;        o = align256(o + 4 * (int64_t)max_seqs);
+    L.dec_indptr = o;     o = align256(o + 4 * (int64_t)(max_seqs + 1));
+    L.cta_first = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
+    L.counters = o;       o = align256(o + 4 * (int64_t)max_seqs * kMaxKvHeads);
+    const int64_t max_items = (int64_t)max_tokens / kPrefillTileTokens + max_seqs + 1;
+    L.prefill_items = o;  o = align256(o + 8 * max_items);
+    L.partials = o;       o = align256(o + 4 * (int64_t)kMaxDecodeCtas * 2 * n_heads * (head_dim + 2));
+    L.total = o;
+    return L;
+}
+
+// Arguments shared by the tensor-core attention kernels (bf16).
+struct AttnParams {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    const int32_t* block_tables;
+    const int32_t* table_rows;     // may be null: sequence s uses row s of block_tables
+    const int32_t* seq_lens;
+    const int32_t* cu_seqlens;     // may be null: sequence s owns exactly query row s
+    __nv_bfloat16* out;
+    uint8_t* ws;
+    WsLayout L;
+    int64_t table_stride, q_stride, out_stride, blk_stride, pos_stride, head_stride;
+    int n_heads, n_kv_heads, group;
+    float scale_log2;              // softmax scale * log2(e)
+};
+
+}  // namespace ns

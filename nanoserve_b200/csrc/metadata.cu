@@ -1,0 +1,192 @@
+// Step metadata built on the device, and greedy sampling that leaves the sampled token on the device.
+//
+// The host ships one packed int32 buffer per step (a few hundred bytes for a decode step): a header, one
+// record per scheduled sequence, the block-table entries appended since the last step, and the token ids of
+// prefill chunks. One CTA expands it into the static buffers a CUDA graph reads: token ids, positions,
+// slot mapping, cu_seqlens, seq_lens, table rows and the row of each sequence's last token, padded to the
+// graph bucket with rows that only touch the reserved garbage block.
+#include "common.cuh"
+
+namespace ns {
+
+constexpr int kMetaThreads = 1024;
+
+__global__ void __launch_bounds__(kMetaThreads) build_step_metadata_kernel(
+    const int32_t* __restrict__ packed, int32_t* __restrict__ mirror, const int64_t* __restrict__ last_tokens,
+    int pad_seat, int64_t* __restrict__ tokens, int64_t* __restrict__ positions, int64_t* __restrict__ slot_mapping,
+    int32_t* __restrict__ cu_seqlens, int32_t* __restrict__ seq_lens, int32_t* __restrict__ seat_of,
+    int64_t* __restrict__ last_rows, int max_seqs, int max_tokens) {
+    extern __shared__ int32_t cu_sm[];        // [max_seqs + 1]
+    __shared__ int warp_sums[33];
+    const ns_step_header hd = *reinterpret_cast<const ns_step_header*>(packed);
+    const int S = min(hd.n_seqs, max_seqs);
+    const int PS = min(hd.pad_seqs, max_seqs);
+    const int PT = min(hd.pad_tokens, max_tokens);
+    const int32_t* rec = packed + sizeof(ns_step_header) / 4;
+    const int32_t* app = rec + 4 * hd.n_seqs;
+    const int32_t* tok = app + 3 * hd.n_appends;
+    const int W = hd.table_width, bs = hd.block_size;
+
+    // 1. block-table appends into the mirror
+    for (int a = threadIdx.x; a < hd.n_appends; a += kMetaThreads)
+        mirror[(int64_t)app[3 * a] * W + app[3 * a + 1]] = app[3 * a + 2];
+
+    // 2. cu_seqlens = exclusive scan of n_new over real sequences, then one token per padding sequence
+    int carry = 0;
+    for (int base = 0; base < PS; base += kMetaThreads) {
+        const int s = base + threadIdx.x;
+        const int n = s < S ? rec[4 * s + 2] : (s < PS ? 1 : 0);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        int inc = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (lane == 31) warp_sums[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            const int w = warp_sums[lane];
+            int winc = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, winc, o);
+                if (lane >= o) winc += v;
+            }
+            warp_sums[lane] = winc - w;
+            if (lane == 31) warp_sums[32] = winc;
+        }
+        __syncthreads();
+        if (s < PS) cu_sm[s] = carry + warp_sums[warp] + inc - n;
+        carry += warp_sums[32];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) cu_sm[PS] = carry;
+    __syncthreads();
+
+    // 3. per-sequence outputs
+    for (int s = threadIdx.x; s <= PS; s += kMetaThreads) {
+        cu_seqlens[s] = cu_sm[s];
+        if (s < PS) {
+            const bool real = s < S;
+            seq_lens[s] = real ? rec[4 * s + 1] + rec[4 * s + 2] : 1;
+            seat_of[s] = real ? rec[4 * s] : pad_seat;
+            last_rows[s] = cu_sm[s + 1] - 1;
+        }
+    }
+    // 4. per-token outputs (binary search of the owning sequence in shared memory)
+    const int covered = min(cu_sm[PS], PT);
+    const int64_t gslot = (int64_t)hd.garbage_block * bs;
+    for (int t = threadIdx.x; t < PT; t += kMetaThreads) {
+        int64_t token = 0, pos = 0, slot = gslot;
+        if (t < covered) {
+            int lo = 0, hi = PS;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (cu_sm[mid] <= t) lo = mid; else hi = mid;
+            }
+            if (lo < S) {
+                const int seat = rec[4 * lo], ctx = rec[4 * lo + 1], toff = rec[4 * lo + 3];
+                const int j = t - cu_sm[lo];
+                const int ps = ctx + j;
+                pos = ps;
+                slot = (int64_t)mirror[(int64_t)seat * W + ps / bs] * bs + ps % bs;
+                token = toff >= 0 ? (int64_t)tok[toff + j] : last_tokens[seat];
+            }
+        }
+        tokens[t] = token;
+        positions[t] = pos;
+        slot_mapping[t] = slot;
+    }
+}
+
+// Greedy sampling: one CTA per logits row; ties resolve to the lowest index. The token is stored to out[row]
+// and, when seat_of != NULL, to last_tokens[seat_of[row]] so the next step can read it without a host round trip.
+template <typename T>
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
+                                                           int64_t* __restrict__ out, const int32_t* __restrict__ seat_of,
+                                                           int64_t* __restrict__ last_tokens) {
+    constexpr int V = Vec16<T>::N;
+    const T* row = logits + (int64_t)blockIdx.x * row_stride;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    const int chunks = vocab / V;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        Vec16<T> v = load16(row + c * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float f = v.get(j);
+            if (f > best) { best = f; best_i = c * V + j; }
+        }
+    }
+    for (int i = chunks * V + threadIdx.x; i < vocab; i += blockDim.x) {
+        const float f = to_f32(row[i]);
+        if (f > best || (f == best && i < best_i)) { best = f; best_i = i; }
+    }
+    __shared__ float sv[32];
+    __shared__ int si[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = (blockDim.x + 31) / 32;
+        best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+        best_i = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        if (threadIdx.x == 0) {
+            const int64_t tokv = best_i == 0x7fffffff ? 0 : best_i;
+            out[blockIdx.x] = tokv;
+            if (seat_of != nullptr) last_tokens[seat_of[blockIdx.x]] = tokv;
+        }
+    }
+}
+
+}  // namespace ns
+
+using namespace ns;
+
+extern "C" int ns_build_step_metadata(const int32_t* packed, int32_t packed_ints, int32_t* table_mirror,
+                                      const int64_t* last_tokens, int32_t pad_seat, int64_t* tokens,
+                                      int64_t* positions, int64_t* slot_mapping, int32_t* cu_seqlens,
+                                      int32_t* seq_lens, int32_t* seat_of, int64_t* last_rows, int32_t max_seqs,
+                                      int32_t max_tokens, void* stream) {
+    NS_REQUIRE(packed && table_mirror && last_tokens && tokens && positions && slot_mapping && cu_seqlens && seq_lens &&
+                   seat_of && last_rows, NS_ERR_INVALID_ARG, "build_step_metadata: null pointer");
+    NS_REQUIRE(packed_ints >= (int)(sizeof(ns_step_header) / 4), NS_ERR_INVALID_ARG, "build_step_metadata: packed buffer too small");
+    NS_REQUIRE(max_seqs > 0 && max_tokens > 0, NS_ERR_INVALID_ARG, "build_step_metadata: bad capacity");
+    const size_t smem = 4 * (size_t)(max_seqs + 1);
+    NS_REQUIRE(smem <= 40 * 1024, NS_ERR_UNSUPPORTED, "build_step_metadata: max_seqs %d too large", max_seqs);
+    build_step_metadata_kernel<<<1, kMetaThreads, smem, (cudaStream_t)stream>>>(
+        packed, table_mirror, last_tokens, pad_seat, tokens, positions, slot_mapping, cu_seqlens, seq_lens, seat_of,
+        last_rows, max_seqs, max_tokens);
+    return check_launch("build_step_metadata");
+}
+
+extern "C" int ns_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t vocab, int64_t* out,
+                              const int32_t* seat_of, int64_t* last_tokens, int dtype, void* stream) {
+    NS_REQUIRE(logits && out, NS_ERR_INVALID_ARG, "argmax_rows: null pointer");
+    NS_REQUIRE(rows >= 0 && vocab > 0, NS_ERR_INVALID_ARG, "argmax_rows: bad shape");
+    NS_REQUIRE(seat_of == nullptr || last_tokens != nullptr, NS_ERR_INVALID_ARG, "argmax_rows: seat_of without last_tokens");
+    if (rows == 0) return NS_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == NS_BF16) {
+        NS_REQUIRE(row_stride % 8 == 0, NS_ERR_UNSUPPORTED, "argmax_rows: row stride must be a multiple of 16 bytes");
+        argmax_rows_kernel<__nv_bfloat16><<<rows, 1024, 0, st>>>((const __nv_bfloat16*)logits, row_stride, vocab, out, seat_of, last_tokens);
+    } else if (dtype == NS_F32) {
+        NS_REQUIRE(row_stride % 4 == 0, NS_ERR_UNSUPPORTED, "argmax_rows: row stride must be a multiple of 16 bytes");
+        argmax_rows_kernel<float><<<rows, 1024, 0, st>>>((const float*)logits, row_stride, vocab, out, seat_of, last_tokens);
+    } else {
+        return fail(NS_ERR_UNSUPPORTED, "argmax_rows: dtype %d", dtype);
+    }
+    return check_launch("argmax_rows");
+}

@@ -1,0 +1,99 @@
+"""Fused token-wise ops on sm_100a, under the names and signatures of the reference's Triton wrappers
+(nanoserve/kernels/fused.py:45 rms_norm, :75 silu_mul, :156 rope_qkv), plus rope_cos_sin, which does
+nanoserve/model.py:212-217 (Qwen2Model.rope) in one launch.
+
+Each function allocates its outputs with torch (so they live in PyTorch's caching allocator, or in the
+graph's private pool during capture) and launches one kernel of libnanoserve_b200.so on the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from nanoserve_b200 import _lib
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """RMSNorm over the last dim. With `residual`: r = residual + x (rounded to the dtype) and the result is
+    (rms_norm(r), r). Out of place, like the reference."""
+    _lib.require_cuda(x, weight, residual)
+    n = x.shape[-1]
+    x2 = x.reshape(-1, n)
+    assert x2.is_contiguous() and weight.is_contiguous() and weight.shape[-1] == n
+    out = torch.empty_like(x2)
+    res2 = res_out = None
+    if residual is not None:
+        res2 = residual.reshape(-1, n)
+        assert res2.is_contiguous() and res2.shape == x2.shape and res2.dtype == x2.dtype
+        res_out = torch.empty_like(x2)
+    _lib.call("ns_add_rmsnorm", x2.data_ptr(), _lib.ptr(res2), weight.data_ptr(), out.data_ptr(), _lib.ptr(res_out),
+              x2.shape[0], n, float(eps), _lib.dtype_code(x.dtype), _lib.stream_ptr())
+    if residual is None:
+        return out.view(x.shape)
+    return out.view(x.shape), res_out.view(x.shape)
+
+
+def silu_mul(x: torch.Tensor) -> torch.Tensor:
+    """x = [..., 2N] holding [gate | up] -> silu(gate) * up, [..., N]."""
+    _lib.require_cuda(x)
+    n = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * n)
+    assert x2.is_contiguous()
+    out = torch.empty(x2.shape[0], n, device=x.device, dtype=x.dtype)
+    _lib.call("ns_silu_mul", x2.data_ptr(), out.data_ptr(), x2.shape[0], n, _lib.dtype_code(x.dtype),
+              _lib.stream_ptr())
+    return out.view(*x.shape[:-1], n)
+
+
+def rope_cos_sin(positions: torch.Tensor, inv_freq: torch.Tensor, head_dim: int, dtype: torch.dtype):
+    """cos/sin tables [T, head_dim] in `dtype` for int64 positions [T] (angles in fp32, rounded once)."""
+    _lib.require_cuda(positions, inv_freq)
+    assert positions.dtype == torch.int64 and positions.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2 and inv_freq.is_contiguous()
+    t = positions.shape[0]
+    cos = torch.empty(t, head_dim, device=positions.device, dtype=dtype)
+    sin = torch.empty_like(cos)
+    _lib.call("ns_rope_cos_sin", positions.data_ptr(), inv_freq.data_ptr(), cos.data_ptr(), sin.data_ptr(), t, head_dim,
+              _lib.dtype_code(dtype), _lib.stream_ptr())
+    return cos, sin
+
+
+def rope_qkv(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+             k_cache: torch.Tensor | None = None, v_cache: torch.Tensor | None = None,
+             slots: torch.Tensor | None = None, dense_kv: bool = True):
+    """qkv: [N, (n_heads + 2*n_kv_heads) * head_dim]; cos/sin: [N, head_dim]. Returns rotated q
+    [N, n_heads, hd], rotated k and plain v [N, n_kv_heads, hd]; with a paged cache layer
+    (k_cache/v_cache [blocks, block_size, n_kv_heads, hd]) and int64 slots, also stores k and v there.
+    dense_kv=False skips the dense k/v outputs (returns None for them): the ragged attention kernel reads
+    keys and values from the pool only."""
+    _lib.require_cuda(qkv, cos, sin, k_cache, v_cache, slots)
+    n = qkv.shape[0]
+    assert qkv.is_contiguous() and cos.is_contiguous() and sin.is_contiguous()
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    if qkv.dtype not in (torch.bfloat16, torch.float32):
+        raise AssertionError("rope_qkv handles bfloat16 and float32")
+    assert cos.dtype == qkv.dtype and sin.dtype == qkv.dtype
+    q = torch.empty(n, n_heads, head_dim, device=qkv.device, dtype=qkv.dtype)
+    k = torch.empty(n, n_kv_heads, head_dim, device=qkv.device, dtype=qkv.dtype) if dense_kv else None
+    v = torch.empty_like(k) if dense_kv else None
+    write = k_cache is not None
+    if write:
+        assert v_cache is not None and slots is not None and slots.dtype == torch.int64 and slots.is_contiguous()
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == qkv.dtype
+        assert slots.shape[0] >= n
+    _lib.call("ns_rope_qkv_kvwrite", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), _lib.ptr(k),
+              _lib.ptr(v), _lib.ptr(k_cache) if write else None, _lib.ptr(v_cache) if write else None,
+              _lib.ptr(slots) if write else None, n, n_heads, n_kv_heads, head_dim, _lib.dtype_code(qkv.dtype),
+              _lib.stream_ptr())
+    return q, k, v
+
+
+def kv_write(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+             slots: torch.Tensor) -> None:
+    """pool.view(-1, kvh, hd)[slots[t]] = k_new[t] / v_new[t] (nanoserve/kv_cache.py:274-279)."""
+    _lib.require_cuda(k_new, v_new, k_cache, v_cache, slots)
+    assert k_new.is_contiguous() and v_new.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert slots.dtype == torch.int64 and slots.is_contiguous()
+    n = k_new.shape[0]
+    row = k_new[0].numel() if n else k_cache.shape[-1] * k_cache.shape[-2]
+    _lib.call("ns_kv_write", k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+              slots.data_ptr(), n, row, _lib.dtype_code(k_new.dtype), _lib.stream_ptr())
