@@ -92,11 +92,12 @@ int ns_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cac
 int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim);
 
 /* Build the per-step plan in the workspace (shared by every layer of the step): the decode rows' KV blocks
- * are cut into equal ranges, one per persistent decode CTA, and prefill chunks into query tiles.
+ * are cut into equal ranges, one per persistent decode CTA, and prefill chunks into query tiles. The
+ * attention calls that follow must be given the same seq_lens / cu_seqlens / table_rows.
  * No reference counterpart (the reference plans on the host, nanoserve/kv_manager.py:158-179). */
-int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int32_t n_seqs, int32_t block_size,
-                 int32_t n_heads, int32_t head_dim, void* workspace, int64_t workspace_bytes, int32_t ws_max_seqs,
-                 int32_t ws_max_tokens, void* stream);
+int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int32_t n_seqs,
+                 int32_t block_size, int32_t n_heads, int32_t head_dim, void* workspace, int64_t workspace_bytes,
+                 int32_t ws_max_seqs, int32_t ws_max_tokens, void* stream);
 
 /* One layer of attention over the batch described by the last ns_attn_plan call on this workspace.
  * q, out: [N, n_heads, head_dim], row strides q_stride / out_stride (head stride = head_dim).

@@ -1,10 +1,12 @@
 // Decode paged attention for sm_100a: HBM-bound GQA over 16-token KV blocks.
 //
-// Grid  : one persistent CTA per SM. The flattened list of (decode row, KV block) units is cut into equal
+// Grid  : CTAS_PER_SM persistent CTAs per SM (2 for head_dim 64: 16 warps per SM hide the MMA / shuffle latency). The flattened list of (decode row, KV block) units is cut into equal
 //         contiguous ranges (attn_plan.cuh), so every CTA streams the same number of bytes.
 // Warp  : owns one KV head and every (warps-per-head)-th block of the CTA's range. It runs its own
 //         cp.async ring (STAGES tiles of 16 tokens, K and V, 128-bit copies, XOR-swizzled rows) with no
 //         CTA-wide barrier in the steady state, so up to (STAGES-1) tiles per warp are always in flight.
+//         Block ids are fetched 32 at a time, and the next row's Q fragments are loaded into registers as soon
+//         as the prefetch cursor reaches that row, so no tile waits on a dependent load.
 // Math  : the GROUP (<= 8) query heads sharing the KV head are rows 0..GROUP-1 of an m16n8k16 bf16 MMA tile
 //         (rows 8..15 are zero); scores and the running max / sum are fp32, probabilities are rounded to
 //         bf16 before P.V, the row max is reduced with warp shuffles (online softmax).
@@ -15,6 +17,12 @@
 #include "common.cuh"
 
 namespace ns {
+
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -30,27 +38,30 @@ template <int HD> __device__ __forceinline__ uint32_t tile_off(int row, int chun
     (void)CPR;
 }
 
-template <int HD, int NWARPS, int STAGES>
-__global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const AttnParams p) {
+
+template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM>
+__global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(const AttnParams p) {
     constexpr int CPR = HD / 8;                       // 16-byte chunks per K/V row
     constexpr int KV_TILE = 16 * HD * 2;              // bytes of one K (or V) tile
-    constexpr int Q_TILE = 8 * HD * 2;                // 8 query rows
-    constexpr int STAGE_BYTES = 2 * KV_TILE + Q_TILE;
+    constexpr int STAGE_BYTES = 2 * KV_TILE;
     constexpr int RED_ROW = HD + 2;                   // floats: O[HD], m, l
+    constexpr int STAGE_PARTS = 16;                   // partials whose (m, l) are staged at once
     extern __shared__ __align__(128) uint8_t smem[];
 
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
+    const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
+    const int cta = blockIdx.x;
+    const int i_first = cta_first[cta];               // independent of the header load: both are in flight together
     const int per = hdr->dec_per_cta;
     const int total = hdr->dec_total;
-    const int cta = blockIdx.x;
     const long long start = (long long)cta * per;
     if (start >= total) return;
     const int u0 = (int)start;
     const int u1 = min(u0 + per, total);
 
-    const int32_t* __restrict__ dec_seq = reinterpret_cast<const int32_t*>(p.ws + p.L.dec_seq);
+    const int4* __restrict__ dec_info = reinterpret_cast<const int4*>(p.ws + p.L.dec_info);   // {seq, len, table row, q row}
     const int32_t* __restrict__ indptr = reinterpret_cast<const int32_t*>(p.ws + p.L.dec_indptr);
-    const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
     int32_t* counters = reinterpret_cast<int32_t*>(p.ws + p.L.counters);
     float* partials = reinterpret_cast<float*>(p.ws + p.L.partials);
 
@@ -62,59 +73,77 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
     const int GROUP = p.group;
     const int gt = stripe * 32 + lane;        // thread index inside the head group
     const int gthreads = wph * 32;
+    const int row8 = lane >> 2;               // MMA accumulator row of this lane
+    const int colp = (lane & 3) * 2;          // first of its two columns inside an 8-wide n-tile
 
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
-    float* red = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);   // [NWARPS][8][RED_ROW]
+    constexpr int ML_STRIDE = STAGE_PARTS * 16 + 16;  // floats per head group: (m, l) x 8 rows x parts, rowM[8], rowL[8]
+    float* ml_stage = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);
     __shared__ int last_flag[kMaxKvHeads];
-
-    const int i_first = cta_first[cta];
+    __shared__ int red_stage[NWARPS];         // which idle stage of each warp holds its (m, l, O) during a combine
+    int my_red = STAGES - 1;
+    auto red_of = [&](int w, int stage) -> float* {
+        return reinterpret_cast<float*>(smem + ((size_t)w * STAGES + stage) * STAGE_BYTES);   // [8][RED_ROW]
+    };
 
     // ---- prefetch cursor (runs STAGES-1 tiles ahead of the compute cursor) ------------------------------------
-    int pf_i = i_first, pf_hi = indptr[i_first + 1], pf_lo = indptr[i_first];
-    int pf_seq = dec_seq[pf_i], pf_len = p.seq_lens[pf_seq];
-    const int32_t* pf_table = p.block_tables + (int64_t)(p.table_rows ? p.table_rows[pf_seq] : pf_seq) * p.table_stride;
-    int pf_q_staged = -1;                     // decode row whose Q was last staged by this warp
+    int pf_i = i_first, pf_lo = indptr[i_first], pf_hi = indptr[i_first + 1];
+    int4 pf_info = dec_info[pf_i];
+    const int32_t* pf_table = p.block_tables + (int64_t)pf_info.z * p.table_stride;
+    int pf_bids = 0, pf_bt = -1000000;        // lane L holds the block id of this warp's tile pf_bt + L
+    uint32_t qn[HD / 16][2];                  // Q fragments of the row the prefetch cursor is in
+    int qn_row = -1;
+
+    // Q fragments (rows 0..7 = heads of the group; a0 = cols colp..+1, a2 = cols colp+8..+9 of each k-step)
+    auto load_q = [&](uint32_t (&dst)[HD / 16][2], int qrow) {
+        const __nv_bfloat16* qb = p.q + (int64_t)qrow * p.q_stride + (int64_t)(g * GROUP + row8) * HD + colp;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            dst[kk][0] = row8 < GROUP ? *reinterpret_cast<const uint32_t*>(qb + 16 * kk) : 0u;
+            dst[kk][1] = row8 < GROUP ? *reinterpret_cast<const uint32_t*>(qb + 16 * kk + 8) : 0u;
+        }
+    };
+
+    // per-lane constants of the tile copy: chunk q = it*32 + lane -> row = q / CPR, ch = q % CPR
+    const int cp_row0 = lane / CPR, cp_ch = lane % CPR;
+    constexpr int ROWS_PER_IT = 32 / CPR;
 
     auto issue = [&](int t) {
         const int u = u0 + stripe + wph * t;
         if (u < u1) {
+            bool moved = false;
             while (u >= pf_hi) {
                 ++pf_i;
                 pf_lo = pf_hi;
                 pf_hi = indptr[pf_i + 1];
-                pf_seq = dec_seq[pf_i];
-                pf_len = p.seq_lens[pf_seq];
-                pf_table = p.block_tables + (int64_t)(p.table_rows ? p.table_rows[pf_seq] : pf_seq) * p.table_stride;
+                moved = true;
             }
-            uint8_t* st = my_stages + (size_t)(t % STAGES) * STAGE_BYTES;
+            if (moved) {
+                pf_info = dec_info[pf_i];
+                pf_table = p.block_tables + (int64_t)pf_info.z * p.table_stride;
+            }
+            if (moved || t - pf_bt >= 32) {   // one coalesced load fetches the next 32 block ids of this row
+                pf_bt = t;
+                const int jj = (u - pf_lo) + wph * lane;
+                pf_bids = (pf_lo + jj < pf_hi) ? pf_table[jj] : 0;
+            }
+            if (qn_row != pf_i) {             // first tile of a row: start loading its Q now
+                qn_row = pf_i;
+                load_q(qn, pf_info.w);
+            }
             const int j = u - pf_lo;
-            const int blk = pf_table[j];
-            const int valid = min(16, pf_len - 16 * j);
-            const __nv_bfloat16* kb = p.k_pool + (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride;
-            const __nv_bfloat16* vb = p.v_pool + (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride;
-            const uint32_t ks = smem_u32(st), vs = ks + KV_TILE;
+            const int blk = __shfl_sync(0xffffffffu, pf_bids, t - pf_bt);
+            const int valid = min(16, pf_info.y - 16 * j);
+            const int64_t base = (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride + cp_ch * 8;
+            const uint32_t ks = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES), vs = ks + KV_TILE;
 #pragma unroll
-            for (int it = 0; it < (16 * CPR) / 32; ++it) {
-                const int qd = it * 32 + lane;
-                const int row = qd / CPR, ch = qd % CPR;
+            for (int it = 0; it < 16 / ROWS_PER_IT; ++it) {
+                const int row = it * ROWS_PER_IT + cp_row0;
                 const int nbytes = row < valid ? 16 : 0;
-                const int64_t goff = (int64_t)row * p.pos_stride + ch * 8;
-                cp_async16(ks + tile_off<HD>(row, ch), kb + goff, nbytes);
-                cp_async16(vs + tile_off<HD>(row, ch), vb + goff, nbytes);
-            }
-            if (pf_q_staged != pf_i) {
-                pf_q_staged = pf_i;
-                const int64_t qrow = p.cu_seqlens ? p.cu_seqlens[pf_seq] : pf_seq;
-                const __nv_bfloat16* qb = p.q + qrow * p.q_stride + (int64_t)g * GROUP * HD;
-                const uint32_t qs = vs + KV_TILE;
-#pragma unroll
-                for (int it = 0; it < (8 * CPR + 31) / 32; ++it) {
-                    const int qd = it * 32 + lane;
-                    if (qd < 8 * CPR) {
-                        const int row = qd / CPR, ch = qd % CPR;
-                        cp_async16(qs + tile_off<HD>(row, ch), qb + row * HD + ch * 8, row < GROUP ? 16 : 0);
-                    }
-                }
+                const int64_t goff = base + (int64_t)row * p.pos_stride;
+                const uint32_t so = tile_off<HD>(row, cp_ch);
+                cp_async16(ks + so, p.k_pool + goff, nbytes);
+                cp_async16(vs + so, p.v_pool + goff, nbytes);
             }
         }
         cp_async_commit();
@@ -125,17 +154,16 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
     float o[HD / 8][2];
 #pragma unroll
     for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = 0.f;
-    uint32_t qa[HD / 16][2];                  // A fragments (rows 0..7): [k-step][k-low, k-high]
-    int cc_i = i_first, cc_lo = indptr[i_first], cc_hi = indptr[i_first + 1];
-    int cc_len = p.seq_lens[dec_seq[i_first]];
+    uint32_t qa[HD / 16][2];                  // A fragments of the row being computed
     int qa_row = -1;
+    int cc_i = i_first, cc_lo = pf_lo, cc_hi = pf_hi;
+    int cc_len = pf_info.y, cc_qrow = pf_info.w;
 
-    const int row8 = lane >> 2;               // MMA accumulator row of this lane
-    const int colp = (lane & 3) * 2;          // first of its two columns inside an 8-wide n-tile
-
-    // Combine the warps of this head for decode row i, then write the final output or a partial.
-    auto flush = [&](int i) {
-        float* mine = red + (size_t)warp * 8 * RED_ROW;
+    // Combine the warps of this head for the current decode row [cc_lo, cc_hi), then write the final output or a
+    // partial. Every value it needs is already in registers: no dependent global load on this path.
+    auto flush = [&]() {
+        float* mine = red_of(warp, my_red);
+        if (lane == 0) red_stage[warp] = my_red;
         float lsum = l_run;
         lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
         lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
@@ -148,19 +176,18 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
         }
         named_barrier(1 + g, gthreads);
 
-        const int lo = indptr[i], hi = indptr[i + 1];
+        const int i = cc_i, lo = cc_lo, hi = cc_hi;
         const bool complete = lo >= u0 && hi <= u1;
-        const int s = dec_seq[i];
-        const int64_t qrow = p.cu_seqlens ? p.cu_seqlens[s] : s;
+        const int64_t qrow = cc_qrow;
         const int slot = (i == i_first) ? 0 : 1;
         float* part = partials + ((size_t)(cta * 2 + slot) * p.n_heads + (size_t)g * GROUP) * RED_ROW;
         for (int e = gt; e < GROUP * HD; e += gthreads) {
             const int r = e / HD, c = e - r * HD;
             float M = -INFINITY;
-            for (int w = 0; w < wph; ++w) M = fmaxf(M, red[((size_t)(g + NKV * w) * 8 + r) * RED_ROW + HD]);
+            for (int w = 0; w < wph; ++w) M = fmaxf(M, red_of(g + NKV * w, red_stage[g + NKV * w])[r * RED_ROW + HD]);
             float acc = 0.f, Ls = 0.f;
             for (int w = 0; w < wph; ++w) {
-                const float* rw = red + ((size_t)(g + NKV * w) * 8 + r) * RED_ROW;
+                const float* rw = red_of(g + NKV * w, red_stage[g + NKV * w]) + r * RED_ROW;
                 const float sc = fast_exp2(rw[HD] - M);
                 acc = fmaf(sc, rw[c], acc);
                 Ls = fmaf(sc, rw[HD + 1], Ls);
@@ -179,41 +206,116 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
             // Last-arriver reduction: publish the partial, count arrivals for (row, head); whoever completes the
             // count owns the final combine. Nobody waits.
             const int c_first = lo / per, c_last = (hi - 1) / per;
+            const int n_parts = c_last - c_first + 1;
             __threadfence();
             named_barrier(1 + g, gthreads);
             if (gt == 0) {
                 const int old = atomicAdd(&counters[i * kMaxKvHeads + g], 1);
-                last_flag[g] = (old == c_last - c_first);
+                last_flag[g] = (old == n_parts - 1);
             }
             named_barrier(1 + g, gthreads);
             if (last_flag[g]) {
                 __threadfence();
-                for (int e = gt; e < GROUP * HD; e += gthreads) {
-                    const int r = e / HD, c = e - r * HD;
-                    float M = -INFINITY;
-                    for (int cc = c_first; cc <= c_last; ++cc) {
-                        const int sl = (__ldcg(&cta_first[cc]) == i) ? 0 : 1;
-                        const float* pr = partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
-                        M = fmaxf(M, __ldcg(pr + HD));
+                float* st = ml_stage + (size_t)g * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
+                float* rowM = st + STAGE_PARTS * 16;                // [8]
+                float* rowL = rowM + 8;                             // [8]
+                // CTA cc holds this row in slot 0 unless the row begins inside cc's range (only possible for c_first)
+                auto part_row = [&](int cc, int r) -> const float* {
+                    const int sl = (cc == c_first && lo != cc * per) ? 1 : 0;
+                    return partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
+                };
+                auto stage_ml = [&](int base, int cnt) {
+                    for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                        const int pt = idx >> 3, r = idx & 7;
+                        float mv = -INFINITY, lv = 0.f;
+                        if (r < GROUP) {
+                            const float* pr = part_row(base + pt, r);
+                            mv = __ldcg(pr + HD);
+                            lv = __ldcg(pr + HD + 1);
+                        }
+                        st[idx * 2] = mv;
+                        st[idx * 2 + 1] = lv;
                     }
-                    float acc = 0.f, Ls = 0.f;
-                    for (int cc = c_first; cc <= c_last; ++cc) {
-                        const int sl = (__ldcg(&cta_first[cc]) == i) ? 0 : 1;
-                        const float* pr = partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
-                        const float sc = fast_exp2(__ldcg(pr + HD) - M);
-                        acc = fmaf(sc, __ldcg(pr + c), acc);
-                        Ls = fmaf(sc, __ldcg(pr + HD + 1), Ls);
+                    named_barrier(1 + g, gthreads);
+                };
+                // pass 1: row maxima over all partials
+                const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
+                float myM = -INFINITY;
+                for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
+                    const int cnt = min(STAGE_PARTS, c_last - base + 1);
+                    stage_ml(base, cnt);
+                    if (gt < 8)
+                        for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + gt) * 2]);
+                    if (!single) named_barrier(1 + g, gthreads);
+                }
+                if (gt < 8) rowM[gt] = myM;
+                named_barrier(1 + g, gthreads);
+                // m -> weight exp2(m - rowM) in place, and this row's share of the denominator
+                float myL = 0.f;
+                auto to_weights = [&](int cnt, bool add_l) {
+                    for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                        const int r = idx & 7;
+                        const float mv = st[idx * 2];
+                        st[idx * 2] = (r < GROUP && mv > -INFINITY) ? fast_exp2(mv - rowM[r]) : 0.f;
                     }
-                    p.out[qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c] = __float2bfloat16_rn(Ls > 0.f ? acc / Ls : 0.f);
+                    named_barrier(1 + g, gthreads);
+                    if (add_l && gt < 8)
+                        for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + gt) * 2], st[(pt * 8 + gt) * 2 + 1], myL);
+                };
+                if (single) to_weights(n_parts, true);
+                // pass 2: four output elements per thread at a time, their loads over the partials in flight together
+                for (int kg = 0; kg * 4 * gthreads < GROUP * HD; ++kg) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
+                        const int cnt = min(STAGE_PARTS, c_last - base + 1);
+                        if (!single) {
+                            stage_ml(base, cnt);
+                            to_weights(cnt, kg == 0);
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int e = gt + gthreads * (kg * 4 + kk);
+                            if (e < GROUP * HD) {
+                                const int r = e / HD, c = e - r * HD;
+#pragma unroll 4
+                                for (int pt = 0; pt < cnt; ++pt)
+                                    acc[kk] = fmaf(st[(pt * 8 + r) * 2], __ldcg(part_row(base + pt, r) + c), acc[kk]);
+                            }
+                        }
+                        if (!single) named_barrier(1 + g, gthreads);
+                    }
+                    if (kg == 0) {
+                        if (gt < 8) rowL[gt] = myL;
+                        named_barrier(1 + g, gthreads);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const int e = gt + gthreads * (kg * 4 + kk);
+                        if (e < GROUP * HD) {
+                            const int r = e / HD, c = e - r * HD;
+                            const float Ls = rowL[r];
+                            p.out[qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c] =
+                                __float2bfloat16_rn(Ls > 0.f ? acc[kk] / Ls : 0.f);
+                        }
+                    }
                 }
                 if (gt == 0) counters[i * kMaxKvHeads + g] = 0;
             }
         }
-        named_barrier(1 + g, gthreads);       // `red` may be overwritten after this point
+        named_barrier(1 + g, gthreads);       // the scratch may be overwritten after this point
         m_run = -INFINITY;
         l_run = 0.f;
 #pragma unroll
         for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = 0.f;
+    };
+
+    auto next_row = [&]() {
+        ++cc_i;
+        cc_lo = cc_hi;
+        cc_hi = indptr[cc_i + 1];
+        const int4 info = dec_info[cc_i];
+        cc_len = info.y;
+        cc_qrow = info.w;
     };
 
     // ---- pipeline ---------------------------------------------------------------------------------------------------
@@ -224,27 +326,27 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
     for (int t = 0; t < my_tiles; ++t) {
         cp_async_wait<STAGES - 2>();          // tile t has landed (one commit group per tile, empty or not)
         __syncwarp();
-        issue(t + STAGES - 1);                // refills the stage computed in iteration t-1
-
+        if (p.timeline && threadIdx.x == 0 && t == 0) p.timeline[blockIdx.x * 4 + 1] = global_ns();
         const int u = u0 + stripe + wph * t;
-        while (u >= cc_hi) {
-            flush(cc_i);
-            ++cc_i;
-            cc_lo = cc_hi;
-            cc_hi = indptr[cc_i + 1];
-            cc_len = p.seq_lens[dec_seq[cc_i]];
+        if (u >= cc_hi) {
+            // the stage consumed in iteration t-1 is idle: it is this warp's scratch for the combine
+            my_red = (t + STAGES - 1) % STAGES;
+            do {
+                flush();
+                next_row();
+            } while (u >= cc_hi);
         }
-        const uint8_t* st = my_stages + (size_t)(t % STAGES) * STAGE_BYTES;
-        const uint32_t ks = smem_u32(st), vs = ks + KV_TILE, qs = vs + KV_TILE;
-        if (qa_row != cc_i) {                 // first tile of this row for this warp: its Q came with this stage
+        if (qa_row != cc_i) {                 // first tile of this row for this warp
             qa_row = cc_i;
+            if (qn_row == cc_i) {
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; kk += 2) {
-                // matrices: (rows 0-7, chunk 2kk), (2kk+1), (2kk+2), (2kk+3)
-                const int ch = 2 * kk + (lane >> 3);
-                ldmatrix_x4(qs + tile_off<HD>(lane & 7, ch), qa[kk][0], qa[kk][1], qa[kk + 1][0], qa[kk + 1][1]);
+                for (int kk = 0; kk < HD / 16; ++kk) { qa[kk][0] = qn[kk][0]; qa[kk][1] = qn[kk][1]; }
+            } else {
+                load_q(qa, cc_qrow);          // the prefetch cursor is already rows ahead (very short rows)
             }
         }
+        issue(t + STAGES - 1);                // refills the stage computed in iteration t-1
+        const uint32_t ks = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES), vs = ks + KV_TILE;
         const int valid = min(16, cc_len - 16 * (u - cc_lo));
 
         // S = Q K^T : two n-tiles of 8 tokens
@@ -304,46 +406,49 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) paged_decode_kernel(const Attn
         }
     }
     cp_async_wait<0>();
+    __syncwarp();
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4 + 2] = global_ns();
     // Every warp of a head walks every decode row of the CTA's range, with or without tiles of its own, so the
-    // group barriers inside flush() always match.
+    // group barriers inside flush() always match. All stages are idle now: stage 0 is the scratch.
+    my_red = 0;
     while (cc_hi < u1) {
-        flush(cc_i);
-        ++cc_i;
-        cc_lo = cc_hi;
-        cc_hi = indptr[cc_i + 1];
+        flush();
+        next_row();
     }
-    flush(cc_i);
+    flush();
+    if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4 + 3] = global_ns();
 }
 
-template <int HD, int NWARPS, int STAGES> static int launch_decode_cfg(const AttnParams& p, int grid, cudaStream_t st) {
-    constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2 + 8 * HD * 2) + NWARPS * 8 * (HD + 2) * 4;
+template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM>
+static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
+    constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2) + kMaxKvHeads * (16 * 16 + 16) * 4;
+    static_assert(8 * (HD + 2) * 4 <= 2 * 16 * HD * 2, "the combine scratch must fit in one stage");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "decode attention: cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
         configured = true;
     }
-    paged_decode_kernel<HD, NWARPS, STAGES><<<grid, NWARPS * 32, smem, st>>>(p);
+    paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM><<<sms * CTAS_PER_SM, NWARPS * 32, smem, st>>>(p);
     return check_launch("paged_decode");
 }
 
-// Returns NS_ERR_UNSUPPORTED (without setting an error) when this layout has no fast kernel.
 bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_size) {
     if (block_size != 16 || n_heads % n_kv_heads != 0) return false;
     const int group = n_heads / n_kv_heads;
     if (group > 8) return false;
-    if (head_dim == 64) return n_kv_heads == 1 || n_kv_heads == 2 || n_kv_heads == 4 || n_kv_heads == 8;
-    if (head_dim == 128) return n_kv_heads == 1 || n_kv_heads == 2 || n_kv_heads == 3 || n_kv_heads == 6 ||
-                                n_kv_heads == 4 || n_kv_heads == 8;
-    return false;
+    if (head_dim != 64 && head_dim != 128) return false;
+    return n_kv_heads == 1 || n_kv_heads == 2 || n_kv_heads == 4 || n_kv_heads == 8;
 }
 
-int launch_paged_decode(const AttnParams& p, int head_dim, int grid, cudaStream_t st) {
-    if (head_dim == 64) return launch_decode_cfg<64, 8, 4>(p, grid, st);
-    if (p.n_kv_heads == 4 || p.n_kv_heads == 8) return launch_decode_cfg<128, 8, 2>(p, grid, st);
-    return launch_decode_cfg<128, 6, 3>(p, grid, st);
+// Number of persistent decode CTAs for this head_dim on a device with `sms` SMs (the plan must be built for it).
+int decode_grid(int head_dim, int sms) { return head_dim == 64 ? 2 * sms : sms; }
+
+int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t st) {
+    if (head_dim == 64) return launch_decode_cfg<64, 8, 3, 2>(p, sms, st);
+    return launch_decode_cfg<128, 8, 3, 1>(p, sms, st);
 }
 
 }  // namespace ns

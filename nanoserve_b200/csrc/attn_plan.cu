@@ -37,12 +37,15 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& 
 }
 
 __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* __restrict__ seq_lens,
-                                                                 const int32_t* __restrict__ cu_seqlens, int n_seqs,
+                                                                 const int32_t* __restrict__ cu_seqlens,
+                                                                 const int32_t* __restrict__ table_rows, int n_seqs,
                                                                  int block_size, int decode_ctas, uint8_t* ws,
                                                                  WsLayout L, int max_items) {
+    constexpr int kSmemRows = 2048;            // decode rows whose prefix is mirrored in shared memory
     __shared__ int warp_sums[33];
+    __shared__ int indptr_sm[kSmemRows + 1];
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + L.header);
-    int32_t* dec_seq = reinterpret_cast<int32_t*>(ws + L.dec_seq);
+    int4* dec_info = reinterpret_cast<int4*>(ws + L.dec_info);
     int32_t* dec_indptr = reinterpret_cast<int32_t*>(ws + L.dec_indptr);
     int32_t* cta_first = reinterpret_cast<int32_t*>(ws + L.cta_first);
     int2* items = reinterpret_cast<int2*>(ws + L.prefill_items);
@@ -50,10 +53,15 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     int n_dec = 0, dec_blocks = 0, n_items = 0;
     for (int base = 0; base < n_seqs; base += kPlanThreads) {
         const int s = base + threadIdx.x;
-        int is_dec = 0, nb = 0, tiles = 0, T = 0;
+        int is_dec = 0, nb = 0, tiles = 0, T = 0, len = 0, qrow = s;
         if (s < n_seqs) {
-            T = cu_seqlens ? cu_seqlens[s + 1] - cu_seqlens[s] : 1;
-            const int len = seq_lens[s];
+            if (cu_seqlens) {
+                qrow = cu_seqlens[s];
+                T = cu_seqlens[s + 1] - qrow;
+            } else {
+                T = 1;
+            }
+            len = seq_lens[s];
             if (T == 1) {
                 is_dec = 1;
                 nb = (len + block_size - 1) / block_size;
@@ -69,8 +77,9 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         const int ioff = block_exclusive_scan(tiles, warp_sums, tot);
         const int i_tot = tot;
         if (is_dec) {
-            dec_seq[n_dec + pos] = s;
+            dec_info[n_dec + pos] = make_int4(s, len, table_rows ? table_rows[s] : s, qrow);
             dec_indptr[n_dec + pos] = dec_blocks + boff;
+            if (n_dec + pos <= kSmemRows) indptr_sm[n_dec + pos] = dec_blocks + boff;
         }
         // Latest query tile first: under the causal mask it attends to the most keys, so the heaviest items
         // start earliest.
@@ -82,8 +91,12 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         dec_blocks += b_tot;
         n_items += i_tot;
     }
-    if (threadIdx.x == 0) dec_indptr[n_dec] = dec_blocks;
+    if (threadIdx.x == 0) {
+        dec_indptr[n_dec] = dec_blocks;
+        if (n_dec <= kSmemRows) indptr_sm[n_dec] = dec_blocks;
+    }
     __syncthreads();
+    const int* ip = n_dec <= kSmemRows ? indptr_sm : dec_indptr;
 
     int per = (dec_blocks + decode_ctas - 1) / decode_ctas;
     if (per < 1) per = 1;
@@ -97,7 +110,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         } else {
             while (hi - lo > 1) {             // invariant: dec_indptr[lo] <= u < dec_indptr[hi]
                 const int mid = (lo + hi) >> 1;
-                if (dec_indptr[mid] <= u) lo = mid; else hi = mid;
+                if (ip[mid] <= u) lo = mid; else hi = mid;
             }
         }
         cta_first[c] = lo;
@@ -114,9 +127,10 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     }
 }
 
-int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int n_seqs, int block_size, int decode_ctas,
+int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
+                     int block_size, int decode_ctas,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
-    attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, n_seqs, block_size, decode_ctas,
+    attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, decode_ctas,
                                                  (uint8_t*)ws, L, max_items);
     return check_launch("attn_plan");
 }

@@ -29,7 +29,7 @@ struct PlanHeader {
 // Byte offsets inside the workspace; everything 256-byte aligned.
 struct WsLayout {
     int64_t header;         // PlanHeader
-    int64_t dec_seq;        // int32[max_seqs]    batch index of decode row i
+    int64_t dec_info;       // int4[max_seqs]     decode row i: {batch index, seq_len, table row, query row}
     int64_t dec_indptr;     // int32[max_seqs+1]  first block-unit of decode row i
     int64_t cta_first;      // int32[kMaxDecodeCtas+1] decode row holding the first block-unit of each CTA
     int64_t counters;       // int32[max_seqs*kMaxKvHeads] arrivals per (decode row, kv head); zero between launches
@@ -44,7 +44,7 @@ __host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int 
     WsLayout L;
     int64_t o = 0;
     L.header = o;         o = align256(o + (int64_t)sizeof(PlanHeader));
-    L.dec_seq = o;        o = align256(o + 4 * (int64_t)max_seqs);
+    L.dec_info = o;       o = align256(o + 16 * (int64_t)max_seqs);
     L.dec_indptr = o;     o = align256(o + 4 * (int64_t)(max_seqs + 1));
     L.cta_first = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
     L.counters = o;       o = align256(o + 4 * (int64_t)max_seqs * kMaxKvHeads);
@@ -70,6 +70,7 @@ struct AttnParams {
     int64_t table_stride, q_stride, out_stride, blk_stride, pos_stride, head_stride;
     int n_heads, n_kv_heads, group;
     float scale_log2;              // softmax scale * log2(e)
+    long long* timeline;           // profiling hook, normally null: 4 globaltimer stamps per decode CTA
 };
 
 }  // namespace ns

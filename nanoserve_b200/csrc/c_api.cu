@@ -25,13 +25,16 @@ int check_launch(const char* what) {
 }
 
 // attn_plan.cu / attn_decode.cu / attn_prefill_mma.cu
-int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int n_seqs, int block_size, int decode_ctas,
+int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
+                     int block_size, int decode_ctas,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st);
 bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
-int launch_paged_decode(const AttnParams& p, int head_dim, int grid, cudaStream_t st);
+int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t st);
+int decode_grid(int head_dim, int sms);
 bool prefill_mma_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
 
+static long long* g_timeline = nullptr;
 static int g_sm_count = 0;
 static int sm_count() {
     if (g_sm_count <= 0) {
@@ -50,13 +53,14 @@ using namespace ns;
 extern "C" int ns_version(void) { return 100; }
 extern "C" const char* ns_last_error(void) { return g_err; }
 extern "C" int ns_sm_count(void) { return sm_count(); }
+extern "C" void ns_debug_decode_timeline(long long* device_buffer) { g_timeline = device_buffer; }
 
 extern "C" int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim) {
     if (max_seqs <= 0 || max_tokens < 0 || n_heads <= 0 || head_dim <= 0) return -1;
     return ws_layout(max_seqs, max_tokens, n_heads, head_dim).total;
 }
 
-static int plan_impl(const int32_t* seq_lens, const int32_t* cu_seqlens, int n_seqs, int block_size, void* ws,
+static int plan_impl(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs, int block_size, void* ws,
                      int64_t ws_bytes, int ws_max_seqs, int ws_max_tokens, int n_heads, int head_dim, cudaStream_t st) {
     NS_REQUIRE(seq_lens && ws, NS_ERR_INVALID_ARG, "attn_plan: null pointer");
     NS_REQUIRE(n_seqs >= 0 && n_seqs <= ws_max_seqs, NS_ERR_WORKSPACE, "attn_plan: %d sequences > workspace capacity %d",
@@ -66,18 +70,20 @@ static int plan_impl(const int32_t* seq_lens, const int32_t* cu_seqlens, int n_s
     NS_REQUIRE(ws_bytes >= L.total, NS_ERR_WORKSPACE, "attn_plan: workspace of %lld bytes < %lld needed", (long long)ws_bytes,
                (long long)L.total);
     NS_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255) == 0, NS_ERR_INVALID_ARG, "attn_plan: workspace not 256-byte aligned");
-    int ctas = sm_count();
-    NS_REQUIRE(ctas > 0, NS_ERR_CUDA, "attn_plan: cannot query the SM count");
-    if (ctas > kMaxDecodeCtas) ctas = kMaxDecodeCtas;
+    const int sms = sm_count();
+    NS_REQUIRE(sms > 0, NS_ERR_CUDA, "attn_plan: cannot query the SM count");
+    const int ctas = decode_grid(head_dim, sms);
+    NS_REQUIRE(ctas <= kMaxDecodeCtas, NS_ERR_UNSUPPORTED, "attn_plan: %d decode CTAs exceed the workspace layout", ctas);
     const int max_items = ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
-    return launch_attn_plan(seq_lens, cu_seqlens, n_seqs, block_size, ctas, ws, L, max_items, st);
+    return launch_attn_plan(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, ctas, ws, L, max_items, st);
 }
 
-extern "C" int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, int32_t n_seqs, int32_t block_size,
+extern "C" int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows,
+                            int32_t n_seqs, int32_t block_size,
                             int32_t n_heads, int32_t head_dim, void* workspace, int64_t workspace_bytes,
                             int32_t ws_max_seqs, int32_t ws_max_tokens, void* stream) {
-    return plan_impl(seq_lens, cu_seqlens, n_seqs, block_size, workspace, workspace_bytes, ws_max_seqs, ws_max_tokens,
-                     n_heads, head_dim, (cudaStream_t)stream);
+    return plan_impl(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, workspace, workspace_bytes, ws_max_seqs,
+                     ws_max_tokens, n_heads, head_dim, (cudaStream_t)stream);
 }
 
 extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
@@ -116,8 +122,8 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
                NS_ERR_INVALID_ARG, "ragged_paged_attn: q / pools must be 16-byte aligned");
     NS_REQUIRE((reinterpret_cast<uintptr_t>(out) & 3) == 0, NS_ERR_INVALID_ARG, "ragged_paged_attn: out must be 4-byte aligned");
     const float kLog2e = 1.4426950408889634f;
-    int ctas = sm_count();
-    if (ctas > kMaxDecodeCtas) ctas = kMaxDecodeCtas;
+    const int sms = sm_count();
+    NS_REQUIRE(sms > 0 && decode_grid(head_dim, sms) <= kMaxDecodeCtas, NS_ERR_CUDA, "ragged_paged_attn: bad SM count");
 
     AttnParams a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
@@ -126,7 +132,8 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     a.table_stride = table_stride; a.q_stride = q_stride; a.out_stride = out_stride; a.blk_stride = pool_block_stride;
     a.pos_stride = pool_pos_stride; a.head_stride = pool_head_stride;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads; a.scale_log2 = scale * kLog2e;
-    int rc = launch_paged_decode(a, head_dim, ctas, st);
+    a.timeline = g_timeline;
+    int rc = launch_paged_decode(a, head_dim, sms, st);
     if (rc != NS_OK) return rc;
     if (cu_seqlens != nullptr && n_tokens > n_seqs) {
         // Upper bound on prefill tiles from sizes the host knows (graph-safe).
@@ -150,7 +157,7 @@ extern "C" int ns_paged_attn_decode(const void* q, const void* k_pool, const voi
     const bool fast = dtype == NS_BF16 && decode_fast_supported(n_heads, n_kv_heads, head_dim, block_size) &&
                       prefill_mma_supported(n_heads, n_kv_heads, head_dim, block_size) && n_kv_heads <= kMaxKvHeads;
     if (fast) {
-        const int rc = plan_impl(context_lens, nullptr, batch, block_size, workspace, workspace_bytes, ws_max_seqs,
+        const int rc = plan_impl(context_lens, nullptr, nullptr, batch, block_size, workspace, workspace_bytes, ws_max_seqs,
                                  ws_max_tokens, n_heads, head_dim, (cudaStream_t)stream);
         if (rc != NS_OK) return rc;
     }

@@ -1,0 +1,302 @@
+"""CUDA-graph runners for engine steps, and the device-side step buffers they replay over.
+
+Class names, buckets, padding rules and the garbage-block convention follow the reference
+(nanoserve/cuda_graphs.py:28-259): `BUCKETS`, `PIECEWISE_CAP`, `piecewise_buckets`, `DecodeGraphRunner`,
+`PiecewiseGraphRunner`, `captured_buckets`, `garbage_block`, `run(...)`.
+
+What changed underneath:
+  * the reference copies five host-built tensors into static buffers before every replay
+    (cuda_graphs.py:112-117). Here ONE packed int32 buffer goes up (a few hundred bytes for a decode step) and the
+    graph itself starts with the metadata kernel that expands it into token ids, positions, slot mapping,
+    cu_seqlens, seq_lens and table rows, padded to the bucket with rows that only touch the garbage block;
+  * attention is ragged and graph-safe, so a MIXED step (prefill chunks + decodes) is one full graph per token
+    bucket. The reference had to cut such a step into L+1 graph pieces with eager attention in between
+    (cuda_graphs.py:130-147); `PiecewiseGraphRunner` keeps its name and `run` signature for drop-in use;
+  * LM head and greedy argmax are inside the graph; the sampled token also stays on the device for the next step.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from nanoserve_b200 import _lib
+from nanoserve_b200.kernels.paged_attention import AttnWorkspace
+from nanoserve_b200.model import StepMeta
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+PIECEWISE_CAP = 512
+_HEADER_INTS = 8
+
+_SIDE_STREAM = None
+
+
+def _capture_stream() -> torch.cuda.Stream:
+    """One warm-up stream for every capture in the process (a fresh stream per capture keeps a cuBLAS workspace
+    alive each, cuda_graphs.py:33-39)."""
+    global _SIDE_STREAM
+    if _SIDE_STREAM is None:
+        _SIDE_STREAM = torch.cuda.Stream()
+    return _SIDE_STREAM
+
+
+def piecewise_buckets(max_tokens: int, cap: int = PIECEWISE_CAP) -> list[int]:
+    """Token-count buckets for mixed steps: every 16 up to 256, then every 32; the budget itself (or the cap) is
+    the last bucket. Steps above it run without a graph."""
+    top = min(max_tokens, cap)
+    grid = [b for b in range(16, 256, 16)] + [b for b in range(256, cap + 1, 32)]
+    return [b for b in grid if b < top] + [top]
+
+
+class StepBuffers:
+    """Static device buffers of one engine: the block-table mirror (one row per seat), the last sampled token per
+    seat, and the per-step arrays the metadata kernel fills. One instance is shared by both runners."""
+
+    def __init__(self, model, pool, max_seqs: int, max_tokens: int, max_seq_len: int, garbage_block: int,
+                 max_seats: int = 256):
+        cfg, dev = model.cfg, model.device
+        self.model, self.pool = model, pool
+        self.max_seqs, self.max_tokens = int(max_seqs), int(max(max_tokens, max_seqs))
+        self.block_size = pool.block_size
+        self.table_width = -(-max_seq_len // pool.block_size)
+        self.garbage_block = garbage_block
+        self.max_seats = max_seats
+        self.pad_seat = max_seats                                   # mirror row of every padding sequence
+        self.mirror = torch.zeros(max_seats + 1, self.table_width, dtype=torch.int32, device=dev)
+        self.mirror[self.pad_seat, 0] = garbage_block
+        self.last_tokens = torch.zeros(max_seats + 1, dtype=torch.int64, device=dev)
+        i64 = dict(dtype=torch.int64, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(self.max_tokens, **i64)
+        self.positions = torch.zeros(self.max_tokens, **i64)
+        self.slots = torch.zeros(self.max_tokens, **i64)
+        self.cu_seqlens = torch.zeros(self.max_seqs + 1, **i32)
+        self.seq_lens = torch.ones(self.max_seqs, **i32)
+        self.seat_of = torch.full((self.max_seqs,), self.pad_seat, **i32)
+        self.last_rows = torch.zeros(self.max_seqs, **i64)
+        self.sampled = torch.zeros(self.max_seqs, **i64)
+        self.sampled_host = torch.zeros(self.max_seqs, dtype=torch.int64, pin_memory=True)
+        self.capacity = _HEADER_INTS + 4 * self.max_seqs + 3 * self.max_seqs * self.table_width + self.max_tokens
+        self.host_packed = torch.zeros(self.capacity, dtype=torch.int32, pin_memory=True)
+        self._np = self.host_packed.numpy()
+        self.dev_packed = torch.zeros(self.capacity, **i32)
+        nh = cfg.n_heads // getattr(model, "tp_size", 1)
+        self.workspace = AttnWorkspace(self.max_seqs, self.max_tokens, nh, cfg.head_dim, dev)
+
+    def upload(self, records: list[int], appends: list[int], token_ids: list[int], pad_seqs: int, pad_tokens: int) -> None:
+        """Fill the pinned staging buffer and start its copy to the device (stream-ordered before the graph)."""
+        n_seqs, n_app = len(records) // 4, len(appends) // 3
+        n_tokens = self._count_tokens(records)
+        if pad_seqs > self.max_seqs or pad_tokens > self.max_tokens:
+            raise ValueError(f"step of {pad_seqs} sequences / {pad_tokens} tokens exceeds the buffers "
+                             f"({self.max_seqs} / {self.max_tokens})")
+        a = self._np
+        a[:_HEADER_INTS] = (n_seqs, n_tokens, pad_seqs, pad_tokens, n_app, self.garbage_block, self.block_size,
+                            self.table_width)
+        o = _HEADER_INTS
+        n = o + len(records) + len(appends) + len(token_ids)
+        if n > self.capacity:
+            raise ValueError("packed step does not fit the staging buffer")
+        a[o:o + len(records)] = records
+        o += len(records)
+        if appends:
+            a[o:o + len(appends)] = appends
+            o += len(appends)
+        if token_ids:
+            a[o:o + len(token_ids)] = token_ids
+        self.packed_ints = n
+        self.dev_packed[:n].copy_(self.host_packed[:n], non_blocking=True)
+
+    @staticmethod
+    def _count_tokens(records: list[int]) -> int:
+        return sum(records[2::4])
+
+    def build(self) -> None:
+        """Launch the metadata kernel over the uploaded packed buffer (graph-capturable: sizes are read on the
+        device from the packed header)."""
+        _lib.call("ns_build_step_metadata", self.dev_packed.data_ptr(), self.capacity, self.mirror.data_ptr(),
+                  self.last_tokens.data_ptr(), self.pad_seat, self.tokens.data_ptr(), self.positions.data_ptr(),
+                  self.slots.data_ptr(), self.cu_seqlens.data_ptr(), self.seq_lens.data_ptr(), self.seat_of.data_ptr(),
+                  self.last_rows.data_ptr(), self.max_seqs, self.max_tokens, _lib.stream_ptr())
+
+    def meta(self, n_tokens: int, n_seqs: int, decode_only: bool) -> StepMeta:
+        return StepMeta(tokens=self.tokens[:n_tokens], positions=self.positions[:n_tokens],
+                        slot_mapping=self.slots[:n_tokens], cu_seqlens=self.cu_seqlens[:n_seqs + 1],
+                        seq_lens=self.seq_lens[:n_seqs], table_rows=self.seat_of[:n_seqs], block_tables=self.mirror,
+                        last_rows=self.last_rows[:n_seqs], n_seqs=n_seqs, workspace=self.workspace,
+                        decode_only=decode_only)
+
+    def sample(self, logits: torch.Tensor, n_seqs: int) -> None:
+        """Greedy token per row into `sampled`, and into last_tokens[seat] for the next step."""
+        _lib.call("ns_argmax_rows", logits.data_ptr(), logits.stride(0), n_seqs, logits.shape[1], self.sampled.data_ptr(),
+                  self.seat_of.data_ptr(), self.last_tokens.data_ptr(), _lib.dtype_code(logits.dtype), _lib.stream_ptr())
+
+    def step(self, n_tokens: int, n_seqs: int, decode_only: bool) -> torch.Tensor:
+        """metadata kernel -> forward -> argmax over the first n_tokens / n_seqs rows; returns the logits."""
+        self.build()
+        logits = self.model.forward_step(self.meta(n_tokens, n_seqs, decode_only), self.pool)
+        self.sample(logits, n_seqs)
+        return logits
+
+    def fetch_sampled(self, n: int) -> list[int]:
+        """The step's only device->host sync: n sampled token ids."""
+        self.sampled_host[:n].copy_(self.sampled[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.sampled_host[:n].tolist()
+
+
+class _GraphRunner:
+    """Capture / replay of StepBuffers.step for fixed (token rows, sequences) shapes."""
+
+    def __init__(self, buffers: StepBuffers):
+        self.buffers = buffers
+        self.graphs: dict = {}
+        self.outputs: dict = {}
+        self.mempool = None
+
+    def _capture(self, key, n_tokens: int, n_seqs: int, decode_only: bool) -> None:
+        buf = self.buffers
+        # warm-up and capture run on an all-padding step: nothing but the garbage block is written
+        buf.upload([], [], [], pad_seqs=n_seqs, pad_tokens=n_tokens)
+        side = _capture_stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                buf.step(n_tokens, n_seqs, decode_only)
+        torch.cuda.current_stream().wait_stream(side)
+        if self.mempool is None:
+            self.mempool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self.mempool):
+            out = buf.step(n_tokens, n_seqs, decode_only)
+        self.graphs[key], self.outputs[key] = graph, out
+
+
+class DecodeGraphRunner(_GraphRunner):
+    """One full-step graph per decode batch bucket (every sequence feeds exactly one token)."""
+
+    def __init__(self, model, pool, max_seq_len: int, max_batch: int = BUCKETS[-1], buffers: StepBuffers | None = None):
+        self.model, self.pool = model, pool
+        self.buckets = [b for b in BUCKETS if b <= max_batch] or [max_batch]
+        self.max_bucket = self.buckets[-1]
+        self.max_blocks = -(-max_seq_len // pool.block_size)
+        if buffers is None:
+            garbage = pool.allocator.allocate()              # padding rows read / write only this block
+            buffers = StepBuffers(model, pool, self.max_bucket, self.max_bucket, max_seq_len, garbage,
+                                  max_seats=max(self.max_bucket, 1))
+        self.garbage_block = buffers.garbage_block
+        super().__init__(buffers)
+
+    @property
+    def captured_buckets(self) -> list[int]:
+        return sorted(self.graphs)
+
+    def bucket_for(self, n: int) -> int | None:
+        return next((b for b in self.buckets if b >= n), None)
+
+    def capture_all(self, max_batch: int) -> None:
+        top = self.bucket_for(min(max_batch, self.max_bucket))
+        for b in self.buckets:
+            if b <= top and b not in self.graphs:
+                self._capture(b, b, b, True)
+
+    def run_packed(self, records: list[int], appends: list[int], token_ids: list[int]) -> torch.Tensor:
+        """Engine entry: one decode step from packed records. Returns logits [n, vocab] (a view of the graph's
+        output, valid until the next replay of that bucket); the sampled tokens are in buffers.sampled."""
+        n = len(records) // 4
+        B = self.bucket_for(n)
+        if B is None:
+            raise ValueError(f"batch of {n} exceeds the largest graph bucket ({self.max_bucket})")
+        if B not in self.graphs:
+            self._capture(B, B, B, True)
+        self.buffers.upload(records, appends, token_ids, pad_seqs=B, pad_tokens=B)
+        self.graphs[B].replay()
+        return self.outputs[B][:n]
+
+    def run(self, tokens: list[int], positions: list[int], slots: list[int], block_tables: list[list[int]],
+            context_lens: list[int]) -> torch.Tensor:
+        """Reference signature (cuda_graphs.py:99-119): host lists in, logits [n, vocab] out. Row i uses seat i;
+        positions and slots are implied by context_lens and the tables (the device recomputes them)."""
+        records, appends = [], []
+        for i, (table, length) in enumerate(zip(block_tables, context_lens)):
+            records += (i, length - 1, 1, i)
+            for j, b in enumerate(table):
+                appends += (i, j, b)
+        return self.run_packed(records, appends, list(tokens))
+
+
+class PiecewiseGraphRunner(_GraphRunner):
+    """Graphs for MIXED steps, one per token bucket. The name is the reference's: there a mixed step was L+1 graph
+    pieces around eager attention; here the ragged kernel makes the whole step one graph."""
+
+    def __init__(self, model, pool, garbage_block: int, max_tokens: int = PIECEWISE_CAP,
+                 buckets: list[int] | None = None, buffers: StepBuffers | None = None, max_seqs: int | None = None,
+                 max_seq_len: int = 2048):
+        self.model, self.pool, self.garbage_block = model, pool, garbage_block
+        self.buckets = sorted(buckets) if buckets else piecewise_buckets(max_tokens)
+        self.max_tokens = self.buckets[-1]
+        if buffers is None:
+            seqs = max_seqs or min(self.max_tokens, BUCKETS[-1])
+            buffers = StepBuffers(model, pool, seqs, self.max_tokens, max_seq_len, garbage_block, max_seats=seqs)
+        # every mixed graph carries the same number of sequence rows: padding sequences are one-token decodes on
+        # the garbage block, so a fixed count costs next to nothing and keeps one graph per token bucket
+        self.seq_rows = max_seqs or buffers.max_seqs
+        self.gslot = garbage_block * pool.block_size
+        super().__init__(buffers)
+
+    @property
+    def captured_buckets(self) -> list[int]:
+        return sorted(self.graphs)
+
+    def bucket_for(self, n: int) -> int | None:
+        return next((b for b in self.buckets if b >= n), None)
+
+    def fits(self, n_tokens: int, n_seqs: int) -> bool:
+        return n_seqs <= self.seq_rows and n_tokens + (self.seq_rows - n_seqs) <= self.max_tokens
+
+    @torch.inference_mode()
+    def capture_all(self) -> None:
+        for b in reversed(self.buckets):          # largest first: its temporaries carve the pool once
+            if b >= self.seq_rows and b not in self.graphs:
+                self._capture(b, b, self.seq_rows, False)
+
+    @torch.inference_mode()
+    def run_packed(self, records: list[int], appends: list[int], token_ids: list[int]) -> torch.Tensor:
+        n_seqs = len(records) // 4
+        n_tokens = StepBuffers._count_tokens(records)
+        need = n_tokens + (self.seq_rows - n_seqs)       # padding sequences bring one token row each
+        B = self.bucket_for(need)
+        if B is None or n_seqs > self.seq_rows:
+            raise ValueError(f"step of {n_tokens} tokens / {n_seqs} sequences exceeds the largest bucket "
+                             f"({self.max_tokens} / {self.seq_rows})")
+        if B not in self.graphs:
+            self._capture(B, B, self.seq_rows, False)
+        self.buffers.upload(records, appends, token_ids, pad_seqs=self.seq_rows, pad_tokens=B)
+        self.graphs[B].replay()
+        return self.outputs[B][:n_seqs]
+
+    @torch.inference_mode()
+    def run(self, tokens: list[int], positions: list[int], slots: list[int], seqs, decode_meta, rows=None) -> torch.Tensor:
+        """Reference signature (cuda_graphs.py:239-259). Sequence i uses seat i; block tables come from the
+        SeqInput objects (decode rows: from decode_meta). Returns logits of each sequence's last token."""
+        records, appends, off, d = [], [], 0, 0
+        for i, s in enumerate(seqs):
+            table = s.block_table
+            if s.use_kernel and decode_meta is not None:
+                if table is None:
+                    table = decode_meta.block_tables[d]
+                d += 1
+            if table is None:
+                # a fresh prefill: its slots are its only blocks
+                bs = self.pool.block_size
+                table = [slots[off + j] // bs for j in range(0, s.n_tokens, 1) if (s.ctx_len + j) % bs == 0 or j == 0]
+            table = [int(b) for b in (table.tolist() if hasattr(table, "tolist") else table)]
+            need = -(-(s.ctx_len + s.n_tokens) // self.pool.block_size)
+            for j, b in enumerate(table[:need]):
+                appends += (i, j, b)
+            records += (i, s.ctx_len, s.n_tokens, off)
+            off += s.n_tokens
+        if rows is not None:
+            ends = np.cumsum([s.n_tokens for s in seqs]) - 1
+            if rows.tolist() != ends.tolist():
+                raise NotImplementedError("the graphs score each sequence's last token only")
+        return self.run_packed(records, appends, list(tokens))

@@ -35,9 +35,11 @@ class AttnWorkspace:
         return (n_seqs <= self.max_seqs and n_tokens <= self.max_tokens and n_heads == self.n_heads
                 and head_dim == self.head_dim)
 
-    def plan(self, seq_lens: torch.Tensor, cu_seqlens: torch.Tensor | None, n_seqs: int, block_size: int) -> None:
+    def plan(self, seq_lens: torch.Tensor, cu_seqlens: torch.Tensor | None, n_seqs: int, block_size: int,
+             table_rows: torch.Tensor | None = None) -> None:
         """Build this step's plan (call once per step, before the first layer's attention)."""
-        _lib.call("ns_attn_plan", seq_lens.data_ptr(), _lib.ptr(cu_seqlens), n_seqs, block_size, self.n_heads,
+        _lib.call("ns_attn_plan", seq_lens.data_ptr(), _lib.ptr(cu_seqlens), _lib.ptr(table_rows), n_seqs, block_size,
+                  self.n_heads,
                   self.head_dim, self.buf.data_ptr(), self.nbytes, self.max_seqs, self.max_tokens, _lib.stream_ptr())
 
 
@@ -115,7 +117,7 @@ def ragged_paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         return out
     ws = workspace or _workspace_for(q.device, S, N, n_heads, head_dim)
     if not planned:
-        ws.plan(seq_lens, cu_seqlens, S, block_size)
+        ws.plan(seq_lens, cu_seqlens, S, block_size, table_rows)
     _lib.call("ns_ragged_paged_attn", *common, ws.buf.data_ptr(), ws.nbytes, ws.max_seqs, ws.max_tokens,
               _lib.stream_ptr())
     return out
