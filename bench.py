@@ -1,0 +1,342 @@
+"""Benchmark of the continuous-batching forward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config 2): Qwen2.5-0.5B architecture, bf16, random-init weights; 64 requests with uniform random
+prompt ids, prompt lengths uniform in 64-1024, seeded output lengths uniform in 16-256; closed loop at concurrency
+32, chunked prefill 2048 tokens/step, CUDA graphs. One "step" of this benchmark = one pass over the 64 requests.
+
+Reported on one JSON line:
+  value     output tok/s of the device-resident replay: every step's packed inputs already in HBM, no host round trip
+            between steps (CUDA events, max over ranks);
+  e2e       the same metric through the public API (LLMEngine.add_request / step): host token lists in, per-step
+            upload of the packed step records from pinned memory, per-step device->host read of the sampled tokens;
+  roofline  decode paged attention on BASELINE config 1 (48 decode rows, contexts 128-8192, 14/2 heads, hd 64):
+            algorithmic bytes / CUDA-event time per launch, against the measured HBM copy bandwidth;
+  cpu_baseline  the CPU oracle (a port of the reference's torch path, fp32) on a bounded sample of the same request
+            stream, timed on this box's host cores (rank 0, N=1 only).
+With --gpus N (torchrun, one rank per GPU) every rank runs an independent replica of the engine on its own copy of
+the workload (request-level replicas, no collective on the data path): weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+CONCURRENCY = 32
+N_REQUESTS = 64
+METRIC = "output_tok_per_s_c32_qwen2.5-0.5b"
+UNIT = "tok/s"
+CPU_SAMPLE_REQUESTS, CPU_SAMPLE_MAX_NEW = 6, 16
+HBM_FALLBACK_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch on the config-1 batch, from the ncu
+# capture summarised in profiles/ (None until captured for the current kernel)
+DECODE_DRAM_TRAFFIC_BYTES = None
+
+
+def workload():
+    from nanoserve_b200.synthetic import serving_requests
+    return serving_requests(N_REQUESTS, prompt_range=(64, 1024), output_range=(16, 256), vocab=151936, seed=0)
+
+
+def config_dict(n_gpus: int) -> dict:
+    return {"workload": "BASELINE config 2: Qwen2.5-0.5B shape, 64 requests, prompts U[64,1024], outputs U[16,256], "
+                        "closed loop c=32, chunked prefill 2048, CUDA graphs",
+            "concurrency": CONCURRENCY, "requests_per_gpu": N_REQUESTS, "parallelism": f"replicas x{n_gpus}",
+            "l2": "inputs larger than L2 (988 MB of weights stream every step; roofline leg rotates 4 KV pools)"}
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_reference_pass(sd32, cfg, reqs) -> tuple[float, int]:
+    """One pass of the CPU oracle engine over the bounded sample; returns (seconds, output tokens)."""
+    from oracle.engine import OracleEngine, OracleModel, run_requests
+    eng = OracleEngine(OracleModel(cfg, sd32), max_seq_len=2048, max_num_seqs=len(reqs), max_num_batched_tokens=2048)
+    t0 = time.perf_counter()
+    outs = run_requests(eng, reqs)
+    return time.perf_counter() - t0, sum(len(v) for v in outs.values())
+
+
+def cpu_sample_requests():
+    return [(p, min(n, CPU_SAMPLE_MAX_NEW)) for p, n in workload()[:CPU_SAMPLE_REQUESTS]]
+
+
+def cpu_sample_text() -> str:
+    return (f"first {CPU_SAMPLE_REQUESTS} requests of the same stream, outputs capped at {CPU_SAMPLE_MAX_NEW} tokens, "
+            f"c={CPU_SAMPLE_REQUESTS}, fp32 (the reference's CPU path is fp32), oracle port of the reference's torch path")
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from nanoserve_b200.synthetic import random_state_dict
+    sd32, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
+    reqs = cpu_sample_requests()
+    for _ in range(args.warmup):
+        cpu_reference_pass(sd32, cfg, reqs)
+    total_s, total_tok = 0.0, 0
+    for _ in range(args.steps):
+        s, n = cpu_reference_pass(sd32, cfg, reqs)
+        total_s += s
+        total_tok += n
+    value = total_tok / total_s
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": cpu_sample_text()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "host_cpus": os.cpu_count()}))
+
+
+# ------------------------------------------------------------------------------------------------ roofline leg
+def decode_attention_roofline(device) -> dict:
+    """Decode paged attention on BASELINE config 1, timed alone: R launches rotating over 4 KV pools (inputs larger
+    than the 126 MB L2) inside one CUDA graph, CUDA events around the replay on the launching stream."""
+    from nanoserve_b200.kernels.fused import kv_write
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    w = attention_workload(n_decode=48, n_prefill=0, device=device)
+    S = w.seq_lens.shape[0]
+    ws = AttnWorkspace(64, 4096, w.q.shape[1], w.q.shape[2], device)
+    pools = [(w.k_pool, w.v_pool)] + [(torch.randn_like(w.k_pool), torch.randn_like(w.v_pool)) for _ in range(3)]
+    for k, v in pools:
+        kv_write(w.k_new, w.v_new, k, v, w.slot_mapping)
+    ws.plan(w.seq_lens, w.cu_seqlens, S, 16)
+    out = torch.empty_like(w.q)
+    reps = 5
+
+    def body():
+        for _ in range(reps):
+            for k, v in pools:
+                ragged_paged_attention(w.q, k, v, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale, workspace=ws,
+                                       planned=True, out=out)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        body()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(10):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3 / (reps * len(pools)))
+    per_launch = sum(times) / len(times)
+    nbytes = w.decode_bytes()
+    peak, which = HBM_FALLBACK_GBS, "fallback"
+    mp = ROOT / "MEASURED_PEAKS.json"
+    if mp.exists():
+        try:
+            peak, which = float(json.loads(mp.read_text())["hbm_gbs"]), "measured"
+        except (ValueError, KeyError):
+            pass
+    achieved = nbytes / per_launch / 1e9
+    del pools
+    return {"bound": "hbm", "kernel": "paged_decode_kernel (decode rows of ns_ragged_paged_attn)", "achieved": achieved,
+            "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": DECODE_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": nbytes, "us_per_launch": per_launch * 1e6,
+            "workload": "BASELINE config 1 decode rows: 48 rows, contexts U[128,8192], 14q/2kv heads, hd 64, bf16"}
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def closed_loop(eng, reqs, concurrency: int) -> int:
+    """The reference's bare-loop shape (bench/runs/m11_loop_profile.py:41-59): keep `concurrency` requests in flight,
+    refill when one finishes. Returns the number of output tokens."""
+    nxt, tokens = 0, 0
+    while nxt < len(reqs) and nxt < concurrency:
+        eng.add_request(reqs[nxt][0], reqs[nxt][1], ignore_eos=True)
+        nxt += 1
+    while eng.has_unfinished():
+        for o in eng.step():
+            tokens += 1
+            if o.finished and nxt < len(reqs):
+                eng.add_request(reqs[nxt][0], reqs[nxt][1], ignore_eos=True)
+                nxt += 1
+    return tokens
+
+
+def run_gpu_arm(args) -> None:
+    import torch.distributed as dist
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.model import ModelConfig, Qwen2Model
+    from nanoserve_b200.synthetic import random_state_dict
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.bfloat16, device=device)
+    model = Qwen2Model(ModelConfig(**cfg), sd)
+    eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY, max_num_batched_tokens=2048)
+    eng.capture_graphs()
+    reqs = workload()
+
+    for _ in range(args.warmup):
+        closed_loop(eng, reqs, CONCURRENCY)
+
+    # ---- e2e: public API, host inputs, per-step H2D + D2H, wall clock between synchronised barriers
+    eng.reset_stats()
+    h2d = 0
+    orig_upload = eng.buffers.upload
+
+    def counting_upload(*a, **k):
+        nonlocal h2d
+        orig_upload(*a, **k)
+        h2d += eng.buffers.packed_ints * 4
+
+    eng.buffers.upload = counting_upload
+    launches0 = _lib.launch_count
+    with ClockSampler(local) as clocks:
+        barrier()
+        t0 = time.perf_counter()
+        tokens = 0
+        for _ in range(args.steps):
+            tokens += closed_loop(eng, reqs, CONCURRENCY)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        engine_steps = eng.stats["steps"]
+        launches_e2e = _lib.launch_count - launches0
+        # ---- value: device-resident replay of one recorded pass, K times
+        eng.buffers.upload = orig_upload
+        eng.step_log = []
+        pass_tokens = closed_loop(eng, reqs, CONCURRENCY)
+        log, eng.step_log = eng.step_log, None
+        eng.replay_on_device(log)                       # warm
+        barrier()
+        launches1 = _lib.launch_count
+        dev_s = 0.0
+        for _ in range(args.steps):
+            dev_s += eng.replay_on_device(log)
+        launches_dev = _lib.launch_count - launches1
+        barrier()
+    stats = eng.stats
+    # every engine step reads back one int64 per scheduled sequence
+    d2h_per_pass = 8 * sum(len(p[8:8 + 4 * int(p[0])]) // 4 for _, p in log)
+
+    t = torch.tensor([e2e_s, dev_s], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_max, dev_max = t.tolist()
+    total_tokens = tokens * world
+    line = {
+        "metric": METRIC, "value": pass_tokens * args.steps * world / dev_max, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dev_max / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
+        "e2e": {"value": total_tokens / e2e_max, "unit": UNIT, "h2d_bytes_per_step": h2d // args.steps,
+                "d2h_bytes_per_step": d2h_per_pass, "ms_per_step": 1e3 * e2e_max / args.steps,
+                "engine_steps_per_pass": engine_steps // args.steps,
+                "ms_per_engine_step": 1e3 * e2e_max / max(engine_steps, 1)},
+        "gpu_launches": launches_dev, "gpu_launches_e2e": launches_e2e,
+        "output_tokens_per_pass": pass_tokens, "engine": {k: stats[k] for k in ("graph_steps", "piecewise_steps", "steps",
+                                                                                 "num_preemptions", "peak_running")},
+        "clocks": clocks.summary(), "host_cpus": os.cpu_count(),
+    }
+    if rank == 0:
+        if world == 1:
+            line["roofline"] = decode_attention_roofline(device)
+            sd32, cfg32 = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
+            secs, n = cpu_reference_pass(sd32, cfg32, cpu_sample_requests())
+            line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": cpu_sample_text(), "seconds": secs}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -38,6 +38,11 @@ SIGNATURES: dict[str, tuple] = {
 
 _lib = None
 
+# Kernel launches issued through this binding (eager calls and, via note_graph_replay, launches replayed from CUDA
+# graphs). Benchmarks read it to report how many of this library's kernels ran in a timed region.
+launch_count = 0
+_LAUNCHES_PER_CALL = {"ns_paged_attn_decode": 2}       # plan + decode; ns_ragged_paged_attn is counted by its wrapper
+
 
 class NanoserveB200Error(RuntimeError):
     """A C-ABI call returned a non-zero status."""
@@ -61,10 +66,18 @@ def load() -> ctypes.CDLL:
 
 def call(name: str, *args) -> None:
     """Invoke a status-returning entry point; raise with the library's message on failure."""
+    global launch_count
     lib = load()
     status = getattr(lib, name)(*args)
+    launch_count += _LAUNCHES_PER_CALL.get(name, 1)
     if status != 0:
         raise NanoserveB200Error(f"{name} failed (status {status}): {lib.ns_last_error().decode()}")
+
+
+def note_launches(n: int) -> None:
+    """Account for launches that did not go through call(): graph replays, a second kernel behind one entry point."""
+    global launch_count
+    launch_count += n
 
 
 def dtype_code(dtype) -> int:

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     constexpr int CPR = HD / 8;                       // 16-byte chunks per K/V row
     constexpr int KV_TILE = 16 * HD * 2;              // bytes of one K (or V) tile
     constexpr int STAGE_BYTES = 2 * KV_TILE;
-    constexpr int RED_ROW = HD + 2;                   // floats: O[HD], m, l
+    constexpr int RED_ROW = HD + 4;                   // floats: O[HD], m, l, pad (rows stay 16-byte aligned)
     constexpr int STAGE_PARTS = 16;                   // partials whose (m, l) are staged at once
     extern __shared__ __align__(128) uint8_t smem[];
 
@@ -52,15 +52,14 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
     const int cta = blockIdx.x;
-    const int i_first = cta_first[cta];               // independent of the header load: both are in flight together
-    const int per = hdr->dec_per_cta;
-    const int total = hdr->dec_total;
-    const long long start = (long long)cta * per;
-    if (start >= total) return;
-    const int u0 = (int)start;
-    const int u1 = min(u0 + per, total);
+    const int32_t* __restrict__ cta_start = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_start);
+    const int u0 = cta_start[cta], u1 = cta_start[cta + 1];   // independent loads: all in flight together
+    const int i_first = cta_first[cta];
+    if (u0 >= u1) return;
+    (void)hdr;
 
     const int4* __restrict__ dec_info = reinterpret_cast<const int4*>(p.ws + p.L.dec_info);   // {seq, len, table row, q row}
+    const int2* __restrict__ dec_span = reinterpret_cast<const int2*>(p.ws + p.L.dec_span);   // {first CTA, CTAs} per row
     const int32_t* __restrict__ indptr = reinterpret_cast<const int32_t*>(p.ws + p.L.dec_indptr);
     int32_t* counters = reinterpret_cast<int32_t*>(p.ws + p.L.counters);
     float* partials = reinterpret_cast<float*>(p.ws + p.L.partials);
@@ -79,7 +78,6 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
     constexpr int ML_STRIDE = STAGE_PARTS * 16 + 16;  // floats per head group: (m, l) x 8 rows x parts, rowM[8], rowL[8]
     float* ml_stage = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);
-    __shared__ int last_flag[kMaxKvHeads];
     __shared__ int red_stage[NWARPS];         // which idle stage of each warp holds its (m, l, O) during a combine
     int my_red = STAGES - 1;
     auto red_of = [&](int w, int stage) -> float* {
@@ -158,6 +156,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     int qa_row = -1;
     int cc_i = i_first, cc_lo = pf_lo, cc_hi = pf_hi;
     int cc_len = pf_info.y, cc_qrow = pf_info.w;
+    int2 cc_span = dec_span[i_first];
 
     // Combine the warps of this head for the current decode row [cc_lo, cc_hi), then write the final output or a
     // partial. Every value it needs is already in registers: no dependent global load on this path.
@@ -202,30 +201,31 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 }
             }
         }
-        if (!complete) {
-            // Last-arriver reduction: publish the partial, count arrivals for (row, head); whoever completes the
-            // count owns the final combine. Nobody waits.
-            const int c_first = lo / per, c_last = (hi - 1) / per;
-            const int n_parts = c_last - c_first + 1;
-            __threadfence();
-            named_barrier(1 + g, gthreads);
-            if (gt == 0) {
-                const int old = atomicAdd(&counters[i * kMaxKvHeads + g], 1);
-                last_flag[g] = (old == n_parts - 1);
-            }
-            named_barrier(1 + g, gthreads);
-            if (last_flag[g]) {
+        named_barrier(1 + g, gthreads);       // every warp's scratch has been consumed: the others stream on
+        if (!complete && stripe == 0) {
+            // Last-arriver reduction, by the head's leader warp alone. The partial was stored by all warps of the
+            // group before the barrier above; the leader's fence publishes it (fences are cumulative over what the
+            // barrier ordered before it). Whoever completes the arrival count owns the final combine. Nobody waits.
+            const int c_first = cc_span.x, n_parts = cc_span.y, c_last = c_first + n_parts - 1;
+            int is_last = 0;
+            if (lane == 0) {
                 __threadfence();
+                is_last = atomicAdd(&counters[i * kMaxKvHeads + g], 1) == n_parts - 1;
+                if (is_last) __threadfence();
+            }
+            is_last = __shfl_sync(0xffffffffu, is_last, 0);
+            if (is_last) {
                 float* st = ml_stage + (size_t)g * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
                 float* rowM = st + STAGE_PARTS * 16;                // [8]
                 float* rowL = rowM + 8;                             // [8]
                 // CTA cc holds this row in slot 0 unless the row begins inside cc's range (only possible for c_first)
+                const int first_cut = __ldcg(&cta_start[c_first]);
                 auto part_row = [&](int cc, int r) -> const float* {
-                    const int sl = (cc == c_first && lo != cc * per) ? 1 : 0;
+                    const int sl = (cc == c_first && lo != first_cut) ? 1 : 0;
                     return partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
                 };
                 auto stage_ml = [&](int base, int cnt) {
-                    for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                    for (int idx = lane; idx < cnt * 8; idx += 32) {
                         const int pt = idx >> 3, r = idx & 7;
                         float mv = -INFINITY, lv = 0.f;
                         if (r < GROUP) {
@@ -236,73 +236,84 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                         st[idx * 2] = mv;
                         st[idx * 2 + 1] = lv;
                     }
-                    named_barrier(1 + g, gthreads);
+                    __syncwarp();
                 };
-                // pass 1: row maxima over all partials
                 const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
-                float myM = -INFINITY;
+                float myM = -INFINITY;                             // lanes 0..7: row maxima over all partials
                 for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
                     const int cnt = min(STAGE_PARTS, c_last - base + 1);
                     stage_ml(base, cnt);
-                    if (gt < 8)
-                        for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + gt) * 2]);
-                    if (!single) named_barrier(1 + g, gthreads);
+                    if (lane < 8)
+                        for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + lane) * 2]);
+                    __syncwarp();
                 }
-                if (gt < 8) rowM[gt] = myM;
-                named_barrier(1 + g, gthreads);
-                // m -> weight exp2(m - rowM) in place, and this row's share of the denominator
+                if (lane < 8) rowM[lane] = myM;
+                __syncwarp();
                 float myL = 0.f;
-                auto to_weights = [&](int cnt, bool add_l) {
-                    for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                auto to_weights = [&](int cnt, bool add_l) {       // m -> exp2(m - rowM) in place
+                    for (int idx = lane; idx < cnt * 8; idx += 32) {
                         const int r = idx & 7;
                         const float mv = st[idx * 2];
                         st[idx * 2] = (r < GROUP && mv > -INFINITY) ? fast_exp2(mv - rowM[r]) : 0.f;
                     }
-                    named_barrier(1 + g, gthreads);
-                    if (add_l && gt < 8)
-                        for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + gt) * 2], st[(pt * 8 + gt) * 2 + 1], myL);
+                    __syncwarp();
+                    if (add_l && lane < 8)
+                        for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + lane) * 2], st[(pt * 8 + lane) * 2 + 1], myL);
                 };
                 if (single) to_weights(n_parts, true);
-                // pass 2: four output elements per thread at a time, their loads over the partials in flight together
-                for (int kg = 0; kg * 4 * gthreads < GROUP * HD; ++kg) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                // each lane owns float4 columns of the [GROUP x HD] output; loads over the partials are independent
+                // and unrolled so that many are in flight
+                constexpr int V4_PER_ROW = HD / 4;
+                for (int kg = 0; kg * 128 < GROUP * V4_PER_ROW; ++kg) {
+                    float4 acc[4];
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
                         const int cnt = min(STAGE_PARTS, c_last - base + 1);
                         if (!single) {
                             stage_ml(base, cnt);
                             to_weights(cnt, kg == 0);
                         }
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const int e = gt + gthreads * (kg * 4 + kk);
-                            if (e < GROUP * HD) {
-                                const int r = e / HD, c = e - r * HD;
 #pragma unroll 4
-                                for (int pt = 0; pt < cnt; ++pt)
-                                    acc[kk] = fmaf(st[(pt * 8 + r) * 2], __ldcg(part_row(base + pt, r) + c), acc[kk]);
+                        for (int pt = 0; pt < cnt; ++pt) {
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                const int e = lane + 32 * (kg * 4 + kk);
+                                if (e < GROUP * V4_PER_ROW) {
+                                    const int r = e / V4_PER_ROW, c4 = e - r * V4_PER_ROW;
+                                    const float wgt = st[(pt * 8 + r) * 2];
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(part_row(base + pt, r)) + c4);
+                                    acc[kk].x = fmaf(wgt, v.x, acc[kk].x);
+                                    acc[kk].y = fmaf(wgt, v.y, acc[kk].y);
+                                    acc[kk].z = fmaf(wgt, v.z, acc[kk].z);
+                                    acc[kk].w = fmaf(wgt, v.w, acc[kk].w);
+                                }
                             }
                         }
-                        if (!single) named_barrier(1 + g, gthreads);
+                        __syncwarp();
                     }
                     if (kg == 0) {
-                        if (gt < 8) rowL[gt] = myL;
-                        named_barrier(1 + g, gthreads);
+                        if (lane < 8) rowL[lane] = myL;
+                        __syncwarp();
                     }
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const int e = gt + gthreads * (kg * 4 + kk);
-                        if (e < GROUP * HD) {
-                            const int r = e / HD, c = e - r * HD;
+                        const int e = lane + 32 * (kg * 4 + kk);
+                        if (e < GROUP * V4_PER_ROW) {
+                            const int r = e / V4_PER_ROW, c4 = e - r * V4_PER_ROW;
                             const float Ls = rowL[r];
-                            p.out[qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c] =
-                                __float2bfloat16_rn(Ls > 0.f ? acc[kk] / Ls : 0.f);
+                            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+                            uint2 packed;
+                            packed.x = pack_bf16x2(acc[kk].x * inv, acc[kk].y * inv);
+                            packed.y = pack_bf16x2(acc[kk].z * inv, acc[kk].w * inv);
+                            *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + 4 * c4) = packed;
                         }
                     }
                 }
-                if (gt == 0) counters[i * kMaxKvHeads + g] = 0;
+                if (lane == 0) counters[i * kMaxKvHeads + g] = 0;
+                __syncwarp();
             }
         }
-        named_barrier(1 + g, gthreads);       // the scratch may be overwritten after this point
         m_run = -INFINITY;
         l_run = 0.f;
 #pragma unroll
@@ -316,6 +327,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         const int4 info = dec_info[cc_i];
         cc_len = info.y;
         cc_qrow = info.w;
+        cc_span = dec_span[cc_i];
     };
 
     // ---- pipeline ---------------------------------------------------------------------------------------------------
@@ -422,7 +434,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
 template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM>
 static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
     constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2) + kMaxKvHeads * (16 * 16 + 16) * 4;
-    static_assert(8 * (HD + 2) * 4 <= 2 * 16 * HD * 2, "the combine scratch must fit in one stage");
+    static_assert(8 * (HD + 4) * 4 <= 2 * 16 * HD * 2, "the combine scratch must fit in one stage");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM>,

@@ -99,21 +99,59 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     const int* ip = n_dec <= kSmemRows ? indptr_sm : dec_indptr;
 
     int per = (dec_blocks + decode_ctas - 1) / decode_ctas;
-    if (per < 1) per = 1;
+    if (per < kMinBlocksPerCta) per = kMinBlocksPerCta;
     const int used = (dec_blocks + per - 1) / per;
-    // cta_first[c] = decode row containing block-unit c*per (binary search over dec_indptr).
+    const int slack = per <= 2 * kMinBlocksPerCta ? per / 2 : per / 8;   // how far a cut may move to reach a row boundary
+    int32_t* cta_start = reinterpret_cast<int32_t*>(ws + L.cta_start);
+    int2* dec_span = reinterpret_cast<int2*>(ws + L.dec_span);
+    __shared__ int cuts_sm[kMaxDecodeCtas + 1];
+    // row containing block-unit u (u < dec_blocks): the last row whose first unit is <= u
+    auto row_of = [&](int u) {
+        int lo = 0, hi = n_dec;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ip[mid] <= u) lo = mid; else hi = mid;
+        }
+        return lo;
+    };
     for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) {
-        const int64_t u = (int64_t)c * per;
-        int lo = 0, hi = n_dec;               // answer in [0, n_dec]; n_dec when u >= dec_blocks
-        if (u >= dec_blocks) {
-            lo = n_dec;
-        } else {
-            while (hi - lo > 1) {             // invariant: dec_indptr[lo] <= u < dec_indptr[hi]
-                const int mid = (lo + hi) >> 1;
-                if (ip[mid] <= u) lo = mid; else hi = mid;
+        long long u = (long long)c * per;
+        int cut = u >= dec_blocks ? dec_blocks : (int)u;
+        if (cut > 0 && cut < dec_blocks) {
+            const int r = row_of(cut);
+            const int below = ip[r], above = ip[r + 1];
+            if (cut - below <= above - cut) {
+                if (cut - below <= slack) cut = below;
+            } else if (above - cut <= slack) {
+                cut = above;
             }
         }
-        cta_first[c] = lo;
+        cuts_sm[c] = cut;
+        cta_start[c] = cut;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads)
+        cta_first[c] = cuts_sm[c] >= dec_blocks ? n_dec : row_of(cuts_sm[c]);
+    // CTAs touching each row: the last CTA starting at or before the row's first unit .. the last CTA starting
+    // before its end (CTAs between two equal cuts are empty and sit on a row boundary, never inside a row)
+    for (int i = threadIdx.x; i < n_dec; i += kPlanThreads) {
+        const int lo_u = ip[i], hi_u = ip[i + 1];
+        int first = 0, last = 0;
+        if (hi_u > lo_u) {
+            int a = 0, b2 = decode_ctas;             // last c with cuts[c] <= lo_u
+            while (b2 - a > 1) {
+                const int mid = (a + b2) >> 1;
+                if (cuts_sm[mid] <= lo_u) a = mid; else b2 = mid;
+            }
+            first = a;
+            a = 0; b2 = decode_ctas;                 // last c with cuts[c] < hi_u
+            while (b2 - a > 1) {
+                const int mid = (a + b2) >> 1;
+                if (cuts_sm[mid] < hi_u) a = mid; else b2 = mid;
+            }
+            last = a;
+        }
+        dec_span[i] = make_int2(first, last - first + 1);
     }
     if (threadIdx.x == 0) {
         hdr->n_dec = n_dec;

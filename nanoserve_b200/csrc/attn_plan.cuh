@@ -2,8 +2,10 @@
 //
 // The plan is built once per engine step (ns_attn_plan) and reused by every layer:
 //   * decode rows (one query token) are listed in batch order; their KV blocks form one flattened list of
-//     `dec_total` block-units that is cut into equal contiguous ranges, one per persistent decode CTA
-//     (stream-K style): every CTA reads the same number of bytes whatever the mix of context lengths;
+//     `dec_total` block-units that is cut into contiguous ranges of (nearly) equal size, one per persistent
+//     decode CTA (stream-K style): every CTA reads about the same number of bytes whatever the mix of context
+//     lengths. A cut that falls close to a row boundary is moved onto it, and ranges are never smaller than
+//     kMinBlocksPerCta, so short rows stay whole (no partials, no cross-CTA reduce);
 //   * prefill rows are cut into query tiles, heaviest (latest) tile first.
 #pragma once
 #include <cuda_bf16.h>
@@ -14,6 +16,8 @@ namespace ns {
 constexpr int kMaxDecodeCtas = 1024;      // upper bound on the persistent decode grid
 constexpr int kMaxKvHeads = 8;            // counters per decode row
 constexpr int kPrefillTileTokens = 16;    // query tokens per prefill work item
+constexpr int kMinBlocksPerCta = 32;      // a decode CTA's range is never cut below this many 16-token blocks: splitting
+                                          // a row costs a partial write + a cross-CTA reduce (~ the time to stream 32 blocks)
 
 struct PlanHeader {
     int32_t n_dec;          // decode rows
@@ -31,10 +35,12 @@ struct WsLayout {
     int64_t header;         // PlanHeader
     int64_t dec_info;       // int4[max_seqs]     decode row i: {batch index, seq_len, table row, query row}
     int64_t dec_indptr;     // int32[max_seqs+1]  first block-unit of decode row i
+    int64_t cta_start;      // int32[kMaxDecodeCtas+1] first block-unit of each decode CTA (cut points)
     int64_t cta_first;      // int32[kMaxDecodeCtas+1] decode row holding the first block-unit of each CTA
+    int64_t dec_span;       // int2[max_seqs] decode row i: {first CTA touching it, number of CTAs touching it}
     int64_t counters;       // int32[max_seqs*kMaxKvHeads] arrivals per (decode row, kv head); zero between launches
     int64_t prefill_items;  // int2[max_prefill_items] (batch index, first query token of the tile)
-    int64_t partials;       // float[kMaxDecodeCtas*2][n_heads][head_dim+2]
+    int64_t partials;       // float[kMaxDecodeCtas*2][n_heads][head_dim+4]
     int64_t total;
 };
 
@@ -46,11 +52,13 @@ __host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int 
     L.header = o;         o = align256(o + (int64_t)sizeof(PlanHeader));
     L.dec_info = o;       o = align256(o + 16 * (int64_t)max_seqs);
     L.dec_indptr = o;     o = align256(o + 4 * (int64_t)(max_seqs + 1));
+    L.cta_start = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
     L.cta_first = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
+    L.dec_span = o;       o = align256(o + 8 * (int64_t)max_seqs);
     L.counters = o;       o = align256(o + 4 * (int64_t)max_seqs * kMaxKvHeads);
     const int64_t max_items = (int64_t)max_tokens / kPrefillTileTokens + max_seqs + 1;
     L.prefill_items = o;  o = align256(o + 8 * max_items);
-    L.partials = o;       o = align256(o + 4 * (int64_t)kMaxDecodeCtas * 2 * n_heads * (head_dim + 2));
+    L.partials = o;       o = align256(o + 4 * (int64_t)kMaxDecodeCtas * 2 * n_heads * (head_dim + 4));
     L.total = o;
     return L;
 }

@@ -120,7 +120,8 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
                    pool_block_stride % 8 == 0, NS_ERR_INVALID_ARG, "ragged_paged_attn: strides must keep 16-byte alignment");
     NS_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0,
                NS_ERR_INVALID_ARG, "ragged_paged_attn: q / pools must be 16-byte aligned");
-    NS_REQUIRE((reinterpret_cast<uintptr_t>(out) & 3) == 0, NS_ERR_INVALID_ARG, "ragged_paged_attn: out must be 4-byte aligned");
+    NS_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7) == 0 && out_stride % 4 == 0, NS_ERR_INVALID_ARG,
+               "ragged_paged_attn: out must be 8-byte aligned with a row stride that is a multiple of 4 elements");
     const float kLog2e = 1.4426950408889634f;
     const int sms = sm_count();
     NS_REQUIRE(sms > 0 && decode_grid(head_dim, sms) <= kMaxDecodeCtas, NS_ERR_CUDA, "ragged_paged_attn: bad SM count");

@@ -151,6 +151,7 @@ class _GraphRunner:
         self.buffers = buffers
         self.graphs: dict = {}
         self.outputs: dict = {}
+        self.launches: dict = {}         # kernels of this library inside each captured graph
         self.mempool = None
 
     def _capture(self, key, n_tokens: int, n_seqs: int, decode_only: bool) -> None:
@@ -166,9 +167,16 @@ class _GraphRunner:
         if self.mempool is None:
             self.mempool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
+        before = _lib.launch_count
         with torch.cuda.graph(graph, pool=self.mempool):
             out = buf.step(n_tokens, n_seqs, decode_only)
+        self.launches[key] = _lib.launch_count - before
+        _lib.note_launches(-self.launches[key])       # captured, not executed
         self.graphs[key], self.outputs[key] = graph, out
+
+    def replay(self, key) -> None:
+        self.graphs[key].replay()
+        _lib.note_launches(self.launches[key])
 
 
 class DecodeGraphRunner(_GraphRunner):
@@ -209,7 +217,8 @@ class DecodeGraphRunner(_GraphRunner):
         if B not in self.graphs:
             self._capture(B, B, B, True)
         self.buffers.upload(records, appends, token_ids, pad_seqs=B, pad_tokens=B)
-        self.graphs[B].replay()
+        self.replay(B)
+        self.last_key = B
         return self.outputs[B][:n]
 
     def run(self, tokens: list[int], positions: list[int], slots: list[int], block_tables: list[list[int]],
@@ -271,7 +280,8 @@ class PiecewiseGraphRunner(_GraphRunner):
         if B not in self.graphs:
             self._capture(B, B, self.seq_rows, False)
         self.buffers.upload(records, appends, token_ids, pad_seqs=self.seq_rows, pad_tokens=B)
-        self.graphs[B].replay()
+        self.replay(B)
+        self.last_key = B
         return self.outputs[B][:n_seqs]
 
     @torch.inference_mode()

@@ -179,12 +179,17 @@ class LLMEngine:
         if runner is not None and n_tokens == n_seqs and n_seqs <= runner.max_bucket:
             runner.run_packed(records, appends, token_ids)           # every sequence feeds one token
             self._stats["graph_steps"] += 1
+            path = ("decode", runner.last_key)
         elif pw is not None and pw.fits(n_tokens, n_seqs):
             pw.run_packed(records, appends, token_ids)
             self._stats["piecewise_steps"] += 1
+            path = ("mixed", pw.last_key)
         else:
             buf.upload(records, appends, token_ids, pad_seqs=n_seqs, pad_tokens=n_tokens)
             buf.step(n_tokens, n_seqs, decode_only=False)
+            path = ("eager", (n_tokens, n_seqs))
+        if self.step_log is not None:                                # device-resident replay (see replay_on_device)
+            self.step_log.append((path, buf.host_packed[:buf.packed_ints].clone()))
         self._mark("launch", gpu_end=True)
         next_tokens = buf.fetch_sampled(n_seqs)                      # greedy; one sync for the whole batch
         self._mark("wait")
@@ -209,6 +214,34 @@ class LLMEngine:
             outputs.append(StepOutput(seq.seq_id, tok, finished))
         self._mark("post")
         return outputs
+
+    # ---- device-resident replay -------------------------------------------------------------------------------------
+    step_log: list | None = None      # set to [] to record (path, packed step buffer) of every step
+
+    def replay_on_device(self, log: list) -> float:
+        """Re-run recorded steps with every input already in HBM and no host round trip: the packed step buffers are
+        uploaded beforehand, each step copies its buffer device-to-device and replays its graph; sampled tokens stay on
+        the device (last_tokens). Returns the elapsed device time in seconds (CUDA events). The KV pool is overwritten
+        exactly as in the recorded run. Used to separate kernel throughput from host overhead."""
+        buf = self.buffers
+        sizes = [p.numel() for _, p in log]
+        resident = torch.cat([p for _, p in log]).to(buf.dev_packed.device)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        off = 0
+        for (kind, key), n in zip((p for p, _ in log), sizes):
+            buf.dev_packed[:n].copy_(resident[off:off + n], non_blocking=True)
+            off += n
+            if kind == "decode":
+                self.graph_runner.replay(key)
+            elif kind == "mixed":
+                self.piecewise_runner.replay(key)
+            else:
+                buf.step(key[0], key[1], decode_only=False)
+        ev1.record()
+        torch.cuda.synchronize()
+        return ev0.elapsed_time(ev1) / 1e3
 
     # ---- optional per-phase timing (off unless `engine.timing = {}`) ----------------------------------------------
     timing: dict | None = None

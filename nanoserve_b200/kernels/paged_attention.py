@@ -120,4 +120,6 @@ def ragged_paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         ws.plan(seq_lens, cu_seqlens, S, block_size, table_rows)
     _lib.call("ns_ragged_paged_attn", *common, ws.buf.data_ptr(), ws.nbytes, ws.max_seqs, ws.max_tokens,
               _lib.stream_ptr())
+    if cu_seqlens is not None and N > S:
+        _lib.note_launches(1)          # the prefill-tile kernel is launched next to the decode kernel
     return out
