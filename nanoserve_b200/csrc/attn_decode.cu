@@ -78,6 +78,12 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
     constexpr int ML_STRIDE = STAGE_PARTS * 16 + 16;  // floats per head group: (m, l) x 8 rows x parts, rowM[8], rowL[8]
     float* ml_stage = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);
+    __shared__ int4 pend[kMaxKvHeads][2];     // rows this CTA holds only in part: {row, first unit, query row, -}
+    __shared__ int2 pend_span[kMaxKvHeads][2];
+    __shared__ int pend_n[kMaxKvHeads];
+    __shared__ int pend_last[kMaxKvHeads][2];
+    if (threadIdx.x < kMaxKvHeads) pend_n[threadIdx.x] = 0;
+    __syncthreads();
     __shared__ int red_stage[NWARPS];         // which idle stage of each warp holds its (m, l, O) during a combine
     int my_red = STAGES - 1;
     auto red_of = [&](int w, int stage) -> float* {
@@ -201,119 +207,12 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 }
             }
         }
-        named_barrier(1 + g, gthreads);       // every warp's scratch has been consumed: the others stream on
-        if (!complete && stripe == 0) {
-            // Last-arriver reduction, by the head's leader warp alone. The partial was stored by all warps of the
-            // group before the barrier above; the leader's fence publishes it (fences are cumulative over what the
-            // barrier ordered before it). Whoever completes the arrival count owns the final combine. Nobody waits.
-            const int c_first = cc_span.x, n_parts = cc_span.y, c_last = c_first + n_parts - 1;
-            int is_last = 0;
-            if (lane == 0) {
-                __threadfence();
-                is_last = atomicAdd(&counters[i * kMaxKvHeads + g], 1) == n_parts - 1;
-                if (is_last) __threadfence();
-            }
-            is_last = __shfl_sync(0xffffffffu, is_last, 0);
-            if (is_last) {
-                float* st = ml_stage + (size_t)g * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
-                float* rowM = st + STAGE_PARTS * 16;                // [8]
-                float* rowL = rowM + 8;                             // [8]
-                // CTA cc holds this row in slot 0 unless the row begins inside cc's range (only possible for c_first)
-                const int first_cut = __ldcg(&cta_start[c_first]);
-                auto part_row = [&](int cc, int r) -> const float* {
-                    const int sl = (cc == c_first && lo != first_cut) ? 1 : 0;
-                    return partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
-                };
-                auto stage_ml = [&](int base, int cnt) {
-                    for (int idx = lane; idx < cnt * 8; idx += 32) {
-                        const int pt = idx >> 3, r = idx & 7;
-                        float mv = -INFINITY, lv = 0.f;
-                        if (r < GROUP) {
-                            const float* pr = part_row(base + pt, r);
-                            mv = __ldcg(pr + HD);
-                            lv = __ldcg(pr + HD + 1);
-                        }
-                        st[idx * 2] = mv;
-                        st[idx * 2 + 1] = lv;
-                    }
-                    __syncwarp();
-                };
-                const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
-                float myM = -INFINITY;                             // lanes 0..7: row maxima over all partials
-                for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
-                    const int cnt = min(STAGE_PARTS, c_last - base + 1);
-                    stage_ml(base, cnt);
-                    if (lane < 8)
-                        for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + lane) * 2]);
-                    __syncwarp();
-                }
-                if (lane < 8) rowM[lane] = myM;
-                __syncwarp();
-                float myL = 0.f;
-                auto to_weights = [&](int cnt, bool add_l) {       // m -> exp2(m - rowM) in place
-                    for (int idx = lane; idx < cnt * 8; idx += 32) {
-                        const int r = idx & 7;
-                        const float mv = st[idx * 2];
-                        st[idx * 2] = (r < GROUP && mv > -INFINITY) ? fast_exp2(mv - rowM[r]) : 0.f;
-                    }
-                    __syncwarp();
-                    if (add_l && lane < 8)
-                        for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + lane) * 2], st[(pt * 8 + lane) * 2 + 1], myL);
-                };
-                if (single) to_weights(n_parts, true);
-                // each lane owns float4 columns of the [GROUP x HD] output; loads over the partials are independent
-                // and unrolled so that many are in flight
-                constexpr int V4_PER_ROW = HD / 4;
-                for (int kg = 0; kg * 128 < GROUP * V4_PER_ROW; ++kg) {
-                    float4 acc[4];
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
-                        const int cnt = min(STAGE_PARTS, c_last - base + 1);
-                        if (!single) {
-                            stage_ml(base, cnt);
-                            to_weights(cnt, kg == 0);
-                        }
-#pragma unroll 4
-                        for (int pt = 0; pt < cnt; ++pt) {
-#pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                const int e = lane + 32 * (kg * 4 + kk);
-                                if (e < GROUP * V4_PER_ROW) {
-                                    const int r = e / V4_PER_ROW, c4 = e - r * V4_PER_ROW;
-                                    const float wgt = st[(pt * 8 + r) * 2];
-                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(part_row(base + pt, r)) + c4);
-                                    acc[kk].x = fmaf(wgt, v.x, acc[kk].x);
-                                    acc[kk].y = fmaf(wgt, v.y, acc[kk].y);
-                                    acc[kk].z = fmaf(wgt, v.z, acc[kk].z);
-                                    acc[kk].w = fmaf(wgt, v.w, acc[kk].w);
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
-                    if (kg == 0) {
-                        if (lane < 8) rowL[lane] = myL;
-                        __syncwarp();
-                    }
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const int e = lane + 32 * (kg * 4 + kk);
-                        if (e < GROUP * V4_PER_ROW) {
-                            const int r = e / V4_PER_ROW, c4 = e - r * V4_PER_ROW;
-                            const float Ls = rowL[r];
-                            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-                            uint2 packed;
-                            packed.x = pack_bf16x2(acc[kk].x * inv, acc[kk].y * inv);
-                            packed.y = pack_bf16x2(acc[kk].z * inv, acc[kk].w * inv);
-                            *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + 4 * c4) = packed;
-                        }
-                    }
-                }
-                if (lane == 0) counters[i * kMaxKvHeads + g] = 0;
-                __syncwarp();
-            }
+        if (!complete && gt == 0) {           // cross-CTA work for this row is deferred to the end of the CTA
+            const int k = pend_n[g]++;
+            pend[g][k] = make_int4(i, lo, (int)qrow, 0);
+            pend_span[g][k] = cc_span;
         }
+        named_barrier(1 + g, gthreads);       // every warp's scratch has been consumed
         m_run = -INFINITY;
         l_run = 0.f;
 #pragma unroll
@@ -428,6 +327,114 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         next_row();
     }
     flush();
+
+    // ---- cross-CTA combine of the rows this CTA saw only a part of (at most its first and its last row) ------------
+    // The partials were stored by every thread of the group before the barrier that ends flush(); the leader's fence
+    // publishes them (fences are cumulative over what the barrier ordered before it). Whoever completes a row's
+    // arrival count combines it. Nobody waits.
+    const int n_pend = pend_n[g];
+    if (n_pend > 0) {
+        if (gt == 0) {
+            __threadfence();
+            for (int k = 0; k < n_pend; ++k)
+                pend_last[g][k] = atomicAdd(&counters[pend[g][k].x * kMaxKvHeads + g], 1) == pend_span[g][k].y - 1;
+            __threadfence();
+        }
+        named_barrier(1 + g, gthreads);
+        for (int k = 0; k < n_pend; ++k) {
+            if (!pend_last[g][k]) continue;
+            const int i = pend[g][k].x, lo = pend[g][k].y;
+            const int64_t qrow = pend[g][k].z;
+            const int c_first = pend_span[g][k].x, n_parts = pend_span[g][k].y, c_last = c_first + n_parts - 1;
+            float* st = ml_stage + (size_t)g * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
+            float* rowM = st + STAGE_PARTS * 16;                // [8]
+            float* rowL = rowM + 8;                             // [8]
+            const int first_cut = __ldcg(&cta_start[c_first]);
+            // CTA cc holds this row in slot 0 unless the row begins inside cc's range (only possible for c_first)
+            auto part_row = [&](int cc, int r) -> const float* {
+                const int sl = (cc == c_first && lo != first_cut) ? 1 : 0;
+                return partials + ((size_t)(cc * 2 + sl) * p.n_heads + (size_t)g * GROUP + r) * RED_ROW;
+            };
+            auto stage_ml = [&](int base, int cnt) {
+                for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                    const int pt = idx >> 3, r = idx & 7;
+                    float mv = -INFINITY, lv = 0.f;
+                    if (r < GROUP) {
+                        const float* pr = part_row(base + pt, r);
+                        mv = __ldcg(pr + HD);
+                        lv = __ldcg(pr + HD + 1);
+                    }
+                    st[idx * 2] = mv;
+                    st[idx * 2 + 1] = lv;
+                }
+                named_barrier(1 + g, gthreads);
+            };
+            const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
+            float myM = -INFINITY;                             // threads 0..7 of the group: row maxima
+            for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
+                const int cnt = min(STAGE_PARTS, c_last - base + 1);
+                stage_ml(base, cnt);
+                if (gt < 8)
+                    for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + gt) * 2]);
+                if (!single) named_barrier(1 + g, gthreads);
+            }
+            if (gt < 8) rowM[gt] = myM;
+            named_barrier(1 + g, gthreads);
+            float myL = 0.f;
+            auto to_weights = [&](int cnt, bool add_l) {       // m -> exp2(m - rowM) in place
+                for (int idx = gt; idx < cnt * 8; idx += gthreads) {
+                    const int r = idx & 7;
+                    const float mv = st[idx * 2];
+                    st[idx * 2] = (r < GROUP && mv > -INFINITY) ? fast_exp2(mv - rowM[r]) : 0.f;
+                }
+                named_barrier(1 + g, gthreads);
+                if (add_l && gt < 8)
+                    for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + gt) * 2], st[(pt * 8 + gt) * 2 + 1], myL);
+            };
+            if (single) to_weights(n_parts, true);
+            // each thread owns float4 columns of the [GROUP x HD] output; the loads over the partials are independent
+            constexpr int V4_PER_ROW = HD / 4;
+            for (int kg = 0; kg * gthreads < GROUP * V4_PER_ROW; ++kg) {
+                const int e = gt + gthreads * kg;
+                const bool mine = e < GROUP * V4_PER_ROW;
+                const int r = mine ? e / V4_PER_ROW : 0, c4 = mine ? e - r * V4_PER_ROW : 0;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
+                    const int cnt = min(STAGE_PARTS, c_last - base + 1);
+                    if (!single) {
+                        stage_ml(base, cnt);
+                        to_weights(cnt, kg == 0);
+                    }
+                    if (mine) {
+#pragma unroll 8
+                        for (int pt = 0; pt < cnt; ++pt) {
+                            const float wgt = st[(pt * 8 + r) * 2];
+                            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_row(base + pt, r)) + c4);
+                            acc.x = fmaf(wgt, v.x, acc.x);
+                            acc.y = fmaf(wgt, v.y, acc.y);
+                            acc.z = fmaf(wgt, v.z, acc.z);
+                            acc.w = fmaf(wgt, v.w, acc.w);
+                        }
+                    }
+                    if (!single) named_barrier(1 + g, gthreads);
+                }
+                if (kg == 0) {
+                    if (gt < 8) rowL[gt] = myL;
+                    named_barrier(1 + g, gthreads);
+                }
+                if (mine) {
+                    const float Ls = rowL[r];
+                    const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+                    uint2 packed;
+                    packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+                    packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+                    *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + 4 * c4) = packed;
+                }
+            }
+            if (gt == 0) counters[i * kMaxKvHeads + g] = 0;
+            named_barrier(1 + g, gthreads);               // the staging area is reused by the next pending row
+        }
+    }
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4 + 3] = global_ns();
 }
 
