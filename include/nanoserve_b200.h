@@ -122,6 +122,23 @@ int ns_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool, 
                          int64_t pool_head_stride, float scale, int dtype, void* workspace,
                          int64_t workspace_bytes, int32_t ws_max_seqs, int32_t ws_max_tokens, void* stream);
 
+/* ns_paged_attn_decode for callers that must not allocate device memory (code running inside someone else's
+ * stream capture, plugins whose host forbids allocation after start-up, processes whose memory pool belongs to
+ * another runtime): the plan and the split-KV partials live in a fixed array inside the library image instead of a
+ * caller-owned workspace. It has no counterpart in the reference. The array costs
+ * ns_paged_attn_decode_static_bytes() (11 MiB) on every GPU that loads the library. Limits: batch <= 64,
+ * n_heads <= 32, head_dim <= 128, tensor-core layouts only (bf16, block size 16, head_dim 64 / 128, GQA group <= 8);
+ * anything larger returns NS_ERR_WORKSPACE and launches nothing. Calls on one GPU share the array, so calls that
+ * overlap on the device race: keep them on one stream or order them. The first call on each device resolves the
+ * array's address with that device current; make it before any stream capture. */
+int64_t ns_paged_attn_decode_static_bytes(void);
+int ns_paged_attn_decode_static(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
+                                const int32_t* context_lens, void* out, int32_t batch, int32_t n_heads,
+                                int32_t n_kv_heads, int32_t head_dim, int32_t block_size, int64_t table_stride,
+                                int64_t q_stride, int64_t out_stride, int64_t pool_block_stride,
+                                int64_t pool_pos_stride, int64_t pool_head_stride, float scale, int dtype,
+                                void* stream);
+
 /* Scalar implementation of the same ragged attention (fp32 accumulation, one warp per (query token, head));
  * any head layout, bf16 or fp32. Serves fp32 models and on-device cross-checks.
  * Replaces: nanoserve/kernels/paged_attention.py:108-121 paged_attention_reference (gather + SDPA). */

@@ -30,6 +30,9 @@ SIGNATURES: dict[str, tuple] = {
                                      _I64, _I64, _I64, _I64, _F, c_int, _P, _I64, _I32, _I32, _P]),
     "ns_paged_attn_decode": (c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I64, _I64, _I64, _I64,
                                      _I64, _I64, _F, c_int, _P, _I64, _I32, _I32, _P]),
+    "ns_paged_attn_decode_static_bytes": (_I64, []),
+    "ns_paged_attn_decode_static": (c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I64, _I64, _I64, _I64,
+                                            _I64, _I64, _F, c_int, _P]),
     "ns_ragged_paged_attn_simple": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _I32, _I64,
                                             _I64, _I64, _I64, _I64, _I64, _F, c_int, _P]),
     "ns_build_step_metadata": (c_int, [_P, _I32, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P]),
@@ -41,7 +44,7 @@ _lib = None
 # Kernel launches issued through this binding (eager calls and, via note_graph_replay, launches replayed from CUDA
 # graphs). Benchmarks read it to report how many of this library's kernels ran in a timed region.
 launch_count = 0
-_LAUNCHES_PER_CALL = {"ns_paged_attn_decode": 2}       # plan + decode; ns_ragged_paged_attn is counted by its wrapper
+_LAUNCHES_PER_CALL = {"ns_paged_attn_decode": 2, "ns_paged_attn_decode_static": 2}       # plan + decode; ns_ragged_paged_attn is counted by its wrapper
 
 
 class NanoserveB200Error(RuntimeError):

@@ -46,19 +46,20 @@ struct WsLayout {
 
 __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
-__host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int n_heads, int head_dim) {
+__host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int n_heads, int head_dim,
+                                              int max_ctas = kMaxDecodeCtas) {
     WsLayout L;
     int64_t o = 0;
     L.header = o;         o = align256(o + (int64_t)sizeof(PlanHeader));
     L.dec_info = o;       o = align256(o + 16 * (int64_t)max_seqs);
     L.dec_indptr = o;     o = align256(o + 4 * (int64_t)(max_seqs + 1));
-    L.cta_start = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
-    L.cta_first = o;      o = align256(o + 4 * (int64_t)(kMaxDecodeCtas + 1));
+    L.cta_start = o;      o = align256(o + 4 * (int64_t)(max_ctas + 1));
+    L.cta_first = o;      o = align256(o + 4 * (int64_t)(max_ctas + 1));
     L.dec_span = o;       o = align256(o + 8 * (int64_t)max_seqs);
     L.counters = o;       o = align256(o + 4 * (int64_t)max_seqs * kMaxKvHeads);
     const int64_t max_items = (int64_t)max_tokens / kPrefillTileTokens + max_seqs + 1;
     L.prefill_items = o;  o = align256(o + 8 * max_items);
-    L.partials = o;       o = align256(o + 4 * (int64_t)kMaxDecodeCtas * 2 * n_heads * (head_dim + 4));
+    L.partials = o;       o = align256(o + 4 * (int64_t)max_ctas * 2 * n_heads * (head_dim + 4));
     L.total = o;
     return L;
 }

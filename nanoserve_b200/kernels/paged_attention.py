@@ -84,6 +84,28 @@ def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     return out
 
 
+def paged_attention_decode_static(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                                  block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float,
+                                  out: torch.Tensor) -> torch.Tensor:
+    """paged_attention_decode for callers that may not allocate on the device: `out` is supplied by the caller and
+    the kernels' scratch is a fixed array inside the library (no workspace tensor, no torch allocation here).
+    Limits: at most 64 rows, 32 query heads, head_dim 64 or 128, bf16, block size 16; larger inputs raise. All
+    calls on a GPU share that scratch, so keep them on one stream; make the first call on each device outside any
+    CUDA-graph capture (it resolves the scratch address)."""
+    _lib.require_cuda(q, k_pool, v_pool, block_tables, context_lens, out)
+    _check_pool(q, k_pool, v_pool)
+    assert block_tables.dtype == torch.int32 and context_lens.dtype == torch.int32
+    assert block_tables.stride(-1) == 1 and context_lens.is_contiguous()
+    assert out.shape == q.shape and out.dtype == q.dtype and out.stride(-1) == 1 and out.stride(1) == q.shape[2]
+    B, n_heads, head_dim = q.shape
+    _, block_size, n_kv_heads, _ = k_pool.shape
+    _lib.call("ns_paged_attn_decode_static", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
+              context_lens.data_ptr(), out.data_ptr(), B, n_heads, n_kv_heads, head_dim, block_size,
+              block_tables.stride(0), q.stride(0), out.stride(0), k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
+              float(scale), _lib.dtype_code(q.dtype), _lib.stream_ptr())
+    return out
+
+
 def ragged_paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                            seq_lens: torch.Tensor, cu_seqlens: torch.Tensor | None, scale: float, *,
                            n_seqs: int | None = None, table_rows: torch.Tensor | None = None,
