@@ -42,8 +42,8 @@ UNIT = "tok/s"
 CPU_SAMPLE_REQUESTS, CPU_SAMPLE_MAX_NEW = 6, 16
 HBM_FALLBACK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch on the config-1 batch, from the ncu
-# capture summarised in profiles/ (None until captured for the current kernel)
-DECODE_DRAM_TRAFFIC_BYTES = None
+# capture summarised in profiles/paged_decode_kernel_config1.md
+DECODE_DRAM_TRAFFIC_BYTES = 116_500_000
 
 
 def workload():
@@ -270,12 +270,14 @@ def run_gpu_arm(args) -> None:
     launches0 = _lib.launch_count
     with ClockSampler(local) as clocks:
         barrier()
+        torch.cuda.cudart().cudaProfilerStart()      # lets `ncu --profile-from-start off` list exactly the timed launches
         t0 = time.perf_counter()
         tokens = 0
         for _ in range(args.steps):
             tokens += closed_loop(eng, reqs, CONCURRENCY)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+        torch.cuda.cudart().cudaProfilerStop()
         engine_steps = eng.stats["steps"]
         launches_e2e = _lib.launch_count - launches0
         # ---- value: device-resident replay of one recorded pass, K times
@@ -325,14 +327,54 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def launch_probe() -> None:
+    """A few engine steps of the benchmark's engine inside a profiler range (cudaProfilerStart/Stop): two pure-decode
+    steps at c=32 (contexts ~500) and one mixed step (a 300-token prefill chunk joining 31 decodes)."""
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.model import ModelConfig, Qwen2Model
+    from nanoserve_b200.synthetic import random_state_dict, serving_requests
+    torch.cuda.set_device(0)
+    sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.bfloat16, device="cuda")
+    eng = LLMEngine(Qwen2Model(ModelConfig(**cfg), sd), eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY)
+    reqs = serving_requests(33, prompt_range=(400, 600), output_range=(64, 64))
+    for p, n in reqs[:31]:
+        eng.add_request(p, n, ignore_eos=True)
+    for _ in range(12):
+        eng.step()
+    eng.add_request(reqs[31][0][:300], 8, ignore_eos=True)
+    eng.step()                                    # captures the mixed bucket outside the range
+    for _ in range(3):
+        eng.step()
+    assert eng.last_step.n_prefill == 0
+    eng.add_request(reqs[32][0][:300], 8, ignore_eos=True)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    kinds = []
+    for _ in range(3):
+        eng.step()
+        kinds.append((eng.last_step.n_prefill, eng.last_step.n_decode, eng.last_step.n_tokens))
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    print(json.dumps({"probe_steps": kinds, "engine": {k: eng.stats[k] for k in ("graph_steps", "piecewise_steps", "steps")}}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--launch-probe", action="store_true",
+                    help="short run for `ncu --profile-from-start off` launch lists: 2 decode steps at c=32 + 1 mixed step")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="run only the decode-attention roofline leg (the small case used for ncu captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.launch_probe:
+        launch_probe()
+    elif args.roofline_only:
+        torch.cuda.set_device(0)
+        print(json.dumps({"roofline": decode_attention_roofline(torch.device("cuda", 0))}))
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
