@@ -72,6 +72,23 @@ int ns_rope_qkv_kvwrite(const void* qkv, const void* cos, const void* sin, void*
 int ns_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int64_t* slots,
                 int64_t n_tokens, int32_t row_elems, int dtype, void* stream);
 
+/* Weight-streaming GEMM for decode-sized batches, with the neighbouring token-wise ops fused in (bf16 only):
+ *   out = epilogue( prologue(x) . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation.
+ * prologue (ln_w != NULL): r = residual + x rounded to bf16 (r = x when residual == NULL), stored to residual_out
+ *   when given; the GEMM input is ln_w * bf16(r * rsqrt(mean(r^2) + eps)).
+ * epilogue 0: out[M, N] = bf16(acc + bias) (bias may be NULL);
+ * epilogue 1: w = [gate; up] (N = 2*inter rows), out[M, inter] = bf16(bf16(silu(bf16(gate))) * bf16(up));
+ * epilogue 2: w = merged QKV of 64-wide heads with bias; rotates q and k heads with cos/sin [M, 64] (every product
+ *   and sum rounded to bf16), writes q to out [M, n_heads*64] and k / v into one layer's paged pool at slots[m].
+ * split_k (1, 2, 4, 8) spreads K over a thread-block cluster whose partial tiles are summed through distributed
+ * shared memory in a fixed order. K must be a multiple of 16*split_k.
+ * Replaces, fused: nanoserve/model.py:231 (rms_norm + merged QKV F.linear + rope_qkv), :256 (o_proj), :256-257
+ * (add + rms_norm + gate/up F.linear + silu_mul) and :257 (down_proj) for steps of at most 64 token rows. */
+int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const void* w,
+                   const void* bias, void* out, int32_t M, int32_t N, int32_t K, int32_t split_k, float eps,
+                   int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache, void* v_cache,
+                   const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Ragged paged attention.
  *

@@ -1,0 +1,330 @@
+// Weight-streaming GEMM for decode-sized batches (M <= 64 token rows) with the layer's token-wise ops fused in.
+//
+// At M <= 64 a transformer GEMM is a weight read: Y[M,N] = X[M,K] . W[N,K]^T moves N*K*2 bytes of weights and
+// next to nothing else, so the kernel is built like the other HBM-bound kernels here, not like a tensor-core GEMM:
+//   * a CTA owns 64 weight rows and a K-slice; W streams through a 4-stage cp.async ring (64 rows x 64 k = 8 KB
+//     per stage, 128-bit copies, XOR-swizzled) while the activations of the slice sit in shared memory;
+//   * 4 warps x (16 weight rows x all token rows) of mma.sync m16n8k16 bf16 -> fp32;
+//   * narrow-N GEMMs (o_proj, down_proj, QKV) are split over K across a thread-block cluster; the partial tiles are
+//     summed through distributed shared memory in rank order (deterministic, no atomics, no second kernel);
+//   * prologue (optional): r = residual + a rounded to bf16, X = ln_w * bf16(r * rsqrt(mean(r^2) + eps)) computed on
+//     the fly (replaces a separate add+RMSNorm kernel; r is stored once for the residual stream);
+//   * epilogue: bias; or SiLU(gate)*up (the CTA's 64 weight rows are 32 gate rows + the matching 32 up rows); or
+//     RoPE + paged KV write (one CTA tile = one 64-wide head of the merged QKV projection).
+// Rounding points are those of the unfused ops: GEMM result (+bias) rounded to bf16 first, then every elementwise op
+// rounded to bf16 as the framework would.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ns {
+
+enum GemmEpilogue { kEpiBias = 0, kEpiSiluMul = 1, kEpiRopeKv = 2 };
+
+struct GemmParams {
+    const __nv_bfloat16* x;          // [M, K] activations (without prologue) or the pre-norm input `a`
+    const __nv_bfloat16* residual;   // prologue: added to x before the norm (may be null: plain norm of x)
+    const __nv_bfloat16* ln_w;       // prologue: RMSNorm weight [K]; null = no prologue
+    __nv_bfloat16* residual_out;     // prologue: r = residual + x, [M, K] (may be null)
+    const __nv_bfloat16* w;          // [N, K] row-major weights
+    const __nv_bfloat16* bias;       // [N] or null
+    __nv_bfloat16* out;              // kEpiBias: [M, N]; kEpiSiluMul: [M, inter]; kEpiRopeKv: q [M, n_heads*64]
+    const __nv_bfloat16* cos;        // kEpiRopeKv: [M, 64]
+    const __nv_bfloat16* sin;
+    __nv_bfloat16* k_cache;          // kEpiRopeKv: one layer's pool, rows of n_kv_heads*64
+    __nv_bfloat16* v_cache;
+    const int64_t* slots;            // kEpiRopeKv: [M]
+    int M, N, K, k_slice;            // k_slice = K / cluster size
+    int inter;                       // kEpiSiluMul: columns of gate (= rows of W / 2)
+    int n_heads, n_kv_heads;         // kEpiRopeKv
+    float eps;
+};
+
+constexpr int kBN = 64;              // weight rows per CTA
+constexpr int kKS = 64;              // k per pipeline stage
+constexpr int kGemmStages = 4;
+constexpr int kGemmThreads = 128;
+
+__device__ __forceinline__ uint32_t w_off(int row, int chunk) {      // [64][64] bf16 stage, 16-byte chunks swizzled
+    return (uint32_t)(row * 128 + (((chunk ^ row) & 7) << 4));
+}
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmParams p) {
+    constexpr int MP = 16 * MT;                         // padded token rows
+    extern __shared__ __align__(128) uint8_t smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();         // K-slice of this CTA
+    const int csize = (int)cluster.num_blocks();
+    const int tile = blockIdx.x;                        // which 64 weight rows
+    const int k0 = rank * p.k_slice, ks = p.k_slice;
+    const int a_stride = ks * 2 + 16;                   // bytes per activation row in shared memory (+16: no bank conflicts)
+    uint8_t* a_sm = smem;
+    uint8_t* w_sm = smem + (size_t)MP * a_stride;       // kGemmStages x 16 KB
+    w_sm += (128 - (reinterpret_cast<uintptr_t>(w_sm) & 127)) & 127;
+    float* c_sm = reinterpret_cast<float*>(w_sm + kGemmStages * kBN * kKS * 2);   // [MP][64] fp32
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // weight row of the CTA's local row t
+    auto w_row = [&](int t) -> int {
+        if (EPI == kEpiSiluMul) return t < 32 ? tile * 32 + t : p.inter + tile * 32 + (t - 32);
+        return tile * kBN + t;
+    };
+    const int n_stages = (ks + kKS - 1) / kKS;
+    auto load_stage = [&](int s) {
+        if (s < n_stages) {
+            const uint32_t base = smem_u32(w_sm + (size_t)(s % kGemmStages) * kBN * kKS * 2);
+            const int kk0 = s * kKS;
+#pragma unroll
+            for (int it = 0; it < (kBN * 8) / kGemmThreads; ++it) {
+                const int q = it * kGemmThreads + tid;
+                const int row = q >> 3, ch = q & 7;
+                const int k = kk0 + ch * 8;
+                const int wr = w_row(row);
+                const bool ok = k < ks && wr < p.N;
+                cp_async16(base + w_off(row, ch), p.w + (int64_t)(ok ? wr : 0) * p.K + k0 + (ok ? k : 0), ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+    if (p.ln_w == nullptr) {
+        // plain activations: asynchronous copy, in the same commit group as the first weight stage
+        const uint32_t ab = smem_u32(a_sm);
+        for (int q = tid; q < MP * (ks / 8); q += kGemmThreads) {
+            const int m = q / (ks / 8), c = q - m * (ks / 8);
+            const bool ok = m < p.M;
+            cp_async16(ab + m * a_stride + c * 16, p.x + (int64_t)(ok ? m : 0) * p.K + k0 + c * 8, ok ? 16 : 0);
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < kGemmStages - 1; ++s) load_stage(s);     // weights start streaming before the prologue runs
+
+    // ---- activations of this K-slice into shared memory --------------------------------------------------------
+    if (p.ln_w != nullptr) {
+        // r = residual + x (bf16), inv = rsqrt(mean(r^2) + eps) over the FULL row, X = ln_w * bf16(r * inv)
+        for (int m = warp; m < MP; m += kGemmThreads / 32) {
+            if (m < p.M) {
+                const __nv_bfloat16* xr = p.x + (int64_t)m * p.K;
+                const __nv_bfloat16* rr = p.residual ? p.residual + (int64_t)m * p.K : nullptr;
+                float ss = 0.f;
+                for (int c = lane; c < p.K / 8; c += 32) {
+                    Vec16<__nv_bfloat16> v = load16(xr + c * 8);
+                    if (rr) {
+                        Vec16<__nv_bfloat16> r = load16(rr + c * 8);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v.set(j, r.get(j) + v.get(j));
+                        if (p.residual_out && tile == 0 && c * 8 >= k0 && c * 8 < k0 + ks)
+                            store16(p.residual_out + (int64_t)m * p.K + c * 8, v);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = fmaf(v.get(j), v.get(j), ss);
+                }
+                ss = warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+                for (int c = lane; c < ks / 8; c += 32) {
+                    const int k = k0 + c * 8;
+                    Vec16<__nv_bfloat16> v = load16(xr + k);
+                    if (rr) {
+                        Vec16<__nv_bfloat16> r = load16(rr + k);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v.set(j, r.get(j) + v.get(j));
+                    }
+                    Vec16<__nv_bfloat16> wv = load16(p.ln_w + k);
+                    Vec16<__nv_bfloat16> o;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o.set(j, wv.get(j) * round_to<__nv_bfloat16>(v.get(j) * inv));
+                    *reinterpret_cast<uint4*>(a_sm + (size_t)m * a_stride + c * 16) = o.raw;
+                }
+            } else {
+                for (int c = lane; c < ks / 8; c += 32)
+                    *reinterpret_cast<uint4*>(a_sm + (size_t)m * a_stride + c * 16) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+
+    // ---- main loop: warp w owns weight rows [16w, 16w+16) x all token rows ---------------------------------------
+    float acc[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
+    const uint32_t a_base = smem_u32(a_sm);
+    for (int s = 0; s < n_stages; ++s) {
+        cp_async_wait<kGemmStages - 2>();
+        __syncthreads();                                 // stage s landed; stage s-1 is free; (s == 0) activations visible
+        load_stage(s + kGemmStages - 1);
+        const uint32_t wb = smem_u32(w_sm + (size_t)(s % kGemmStages) * kBN * kKS * 2);
+        const int steps = min(kKS, ks - s * kKS) / 16;
+        for (int kk = 0; kk < steps; ++kk) {
+            uint32_t b00, b01, b10, b11;
+            {
+                const int row = 16 * warp + (lane & 7) + ((lane >> 4) << 3);
+                const int ch = 2 * kk + ((lane >> 3) & 1);
+                ldmatrix_x4(wb + w_off(row, ch), b00, b01, b10, b11);
+            }
+            const int kcol = s * kKS + kk * 16;          // k offset inside the slice
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t a[4];
+                const int row = 16 * mt + (lane & 7) + (((lane >> 3) & 1) << 3);
+                const int kb = (kcol + ((lane >> 4) << 3)) * 2;
+                ldmatrix_x4(a_base + row * a_stride + kb, a[0], a[1], a[2], a[3]);
+                mma_bf16_16816(acc[mt][0], a, b00, b01);
+                mma_bf16_16816(acc[mt][1], a, b10, b11);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- partial tile to shared memory, cluster reduction -----------------------------------------------------------
+    {
+        const int r0 = lane >> 2, cp = (lane & 3) * 2;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int col = 16 * warp + 8 * j + cp;
+                *reinterpret_cast<float2*>(c_sm + (16 * mt + r0) * kBN + col) = make_float2(acc[mt][j][0], acc[mt][j][1]);
+                *reinterpret_cast<float2*>(c_sm + (16 * mt + r0 + 8) * kBN + col) = make_float2(acc[mt][j][2], acc[mt][j][3]);
+            }
+    }
+    cluster.sync();
+    // rank r finishes token rows r, r + csize, ...: sum the partial tiles in rank order, then the epilogue
+    for (int m = rank; m < p.M; m += csize) {
+        // every thread gets one pair (n, n + 32) of the row, or with 128 threads: threads 0..31 -> pairs, 4 rows at a time
+        // simpler: each warp takes one row of this rank's share at a time
+        if (((m - rank) / csize) % (kGemmThreads / 32) != warp) continue;
+        float lo = 0.f, hi = 0.f;                       // columns lane and lane + 32 of the tile
+        for (int r = 0; r < csize; ++r) {
+            const float* peer = cluster.map_shared_rank(c_sm, r);
+            lo += peer[m * kBN + lane];
+            hi += peer[m * kBN + lane + 32];
+        }
+        if (EPI == kEpiBias) {
+            const int n_lo = tile * kBN + lane, n_hi = n_lo + 32;
+            if (n_lo < p.N) p.out[(int64_t)m * p.N + n_lo] = __float2bfloat16_rn(lo + (p.bias ? __bfloat162float(p.bias[n_lo]) : 0.f));
+            if (n_hi < p.N) p.out[(int64_t)m * p.N + n_hi] = __float2bfloat16_rn(hi + (p.bias ? __bfloat162float(p.bias[n_hi]) : 0.f));
+        } else if (EPI == kEpiSiluMul) {
+            const int n = tile * 32 + lane;
+            if (n < p.inter) {
+                const float g = round_to<__nv_bfloat16>(lo), u = round_to<__nv_bfloat16>(hi);
+                const float sg = round_to<__nv_bfloat16>(g / (1.0f + expf(-g)));
+                p.out[(int64_t)m * p.inter + n] = __float2bfloat16_rn(sg * u);
+            }
+        } else {
+            // tile = one head of the merged QKV row: lane holds x_lo = col lane, x_hi = col lane + 32
+            const int h = tile;
+            float xl = lo, xh = hi;
+            if (p.bias) {
+                xl += __bfloat162float(p.bias[h * 64 + lane]);
+                xh += __bfloat162float(p.bias[h * 64 + lane + 32]);
+            }
+            xl = round_to<__nv_bfloat16>(xl);
+            xh = round_to<__nv_bfloat16>(xh);
+            if (h < p.n_heads + p.n_kv_heads) {
+                const float cl = __bfloat162float(p.cos[m * 64 + lane]), ch = __bfloat162float(p.cos[m * 64 + 32 + lane]);
+                const float sl = __bfloat162float(p.sin[m * 64 + lane]), sh = __bfloat162float(p.sin[m * 64 + 32 + lane]);
+                const float a = round_to<__nv_bfloat16>(__fmul_rn(xl, cl)), b = round_to<__nv_bfloat16>(__fmul_rn(xh, sl));
+                const float d = round_to<__nv_bfloat16>(__fmul_rn(xh, ch)), e = round_to<__nv_bfloat16>(__fmul_rn(xl, sh));
+                xl = round_to<__nv_bfloat16>(__fadd_rn(a, -b));
+                xh = round_to<__nv_bfloat16>(__fadd_rn(d, e));
+            }
+            __nv_bfloat16* dst;
+            if (h < p.n_heads) {
+                dst = p.out + ((int64_t)m * p.n_heads + h) * 64;
+            } else if (h < p.n_heads + p.n_kv_heads) {
+                dst = p.k_cache + (p.slots[m] * p.n_kv_heads + (h - p.n_heads)) * 64;
+            } else {
+                dst = p.v_cache + (p.slots[m] * p.n_kv_heads + (h - p.n_heads - p.n_kv_heads)) * 64;
+            }
+            dst[lane] = __float2bfloat16_rn(xl);
+            dst[lane + 32] = __float2bfloat16_rn(xh);
+        }
+    }
+    cluster.sync();                                      // peers may still be reading this CTA's tile
+}
+
+}  // namespace ns
+
+namespace ns {
+
+template <int MT, int EPI>
+static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
+    const size_t smem = (size_t)16 * MT * (p.k_slice * 2 + 16) + 128 + (size_t)kGemmStages * kBN * kKS * 2 +
+                        (size_t)16 * MT * kBN * 4;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
+                                          cudaGetErrorString(e));
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles, (unsigned)split_k, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)split_k;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<MT, EPI>, p);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: launch failed: %s", cudaGetErrorString(e));
+    return NS_OK;
+}
+
+template <int EPI> static int dispatch_mt(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
+    if (p.M <= 16) return launch_skinny<1, EPI>(p, tiles, split_k, st);
+    if (p.M <= 32) return launch_skinny<2, EPI>(p, tiles, split_k, st);
+    return launch_skinny<4, EPI>(p, tiles, split_k, st);
+}
+
+}  // namespace ns
+
+using namespace ns;
+
+extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const void* w,
+                              const void* bias, void* out, int32_t M, int32_t N, int32_t K, int32_t split_k, float eps,
+                              int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache,
+                              void* v_cache, const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream) {
+    NS_REQUIRE(M >= 0 && N > 0 && K > 0, NS_ERR_INVALID_ARG, "skinny_gemm: bad shape");
+    if (M == 0) return NS_OK;
+    NS_REQUIRE(x && w && out, NS_ERR_INVALID_ARG, "skinny_gemm: null pointer");
+    NS_REQUIRE(M <= 64, NS_ERR_UNSUPPORTED, "skinny_gemm: %d token rows > 64 (use the library GEMM for large batches)", M);
+    NS_REQUIRE(split_k == 1 || split_k == 2 || split_k == 4 || split_k == 8, NS_ERR_INVALID_ARG,
+               "skinny_gemm: split_k must be 1, 2, 4 or 8");
+    NS_REQUIRE(K % (16 * split_k) == 0, NS_ERR_UNSUPPORTED, "skinny_gemm: K=%d is not a multiple of 16*split_k", K);
+    NS_REQUIRE(residual == nullptr || ln_w != nullptr, NS_ERR_INVALID_ARG, "skinny_gemm: residual needs the norm prologue");
+    NS_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0, NS_ERR_INVALID_ARG,
+               "skinny_gemm: x / w must be 16-byte aligned");
+    GemmParams p;
+    p.x = (const __nv_bfloat16*)x; p.residual = (const __nv_bfloat16*)residual; p.ln_w = (const __nv_bfloat16*)ln_w;
+    p.residual_out = (__nv_bfloat16*)residual_out; p.w = (const __nv_bfloat16*)w; p.bias = (const __nv_bfloat16*)bias;
+    p.out = (__nv_bfloat16*)out; p.cos = (const __nv_bfloat16*)cos; p.sin = (const __nv_bfloat16*)sin;
+    p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache; p.slots = slots;
+    p.M = M; p.N = N; p.K = K; p.k_slice = K / split_k; p.inter = inter; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
+    p.eps = eps;
+    const size_t a_bytes = (size_t)64 * (p.k_slice * 2 + 16);
+    NS_REQUIRE(a_bytes + kGemmStages * kBN * kKS * 2 + 64 * kBN * 4 + 128 <= 220 * 1024, NS_ERR_UNSUPPORTED,
+               "skinny_gemm: K slice of %d does not fit shared memory (raise split_k)", p.k_slice);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (epilogue == kEpiBias) return dispatch_mt<kEpiBias>(p, (N + kBN - 1) / kBN, split_k, st);
+    if (epilogue == kEpiSiluMul) {
+        NS_REQUIRE(inter > 0 && N == 2 * inter && inter % 32 == 0 && bias == nullptr, NS_ERR_INVALID_ARG,
+                   "skinny_gemm: SiLU*mul wants W = [gate; up] with 2*inter rows, inter a multiple of 32, no bias");
+        return dispatch_mt<kEpiSiluMul>(p, inter / 32, split_k, st);
+    }
+    if (epilogue == kEpiRopeKv) {
+        NS_REQUIRE(n_heads > 0 && n_kv_heads > 0 && N == (n_heads + 2 * n_kv_heads) * 64, NS_ERR_UNSUPPORTED,
+                   "skinny_gemm: the RoPE + KV-write epilogue handles head_dim 64 only");
+        NS_REQUIRE(cos && sin && k_cache && v_cache && slots, NS_ERR_INVALID_ARG, "skinny_gemm: RoPE epilogue needs cos, sin, caches, slots");
+        return dispatch_mt<kEpiRopeKv>(p, n_heads + 2 * n_kv_heads, split_k, st);
+    }
+    return fail(NS_ERR_INVALID_ARG, "skinny_gemm: unknown epilogue %d", epilogue);
+}

@@ -97,3 +97,35 @@ def kv_write(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_
     row = k_new[0].numel() if n else k_cache.shape[-1] * k_cache.shape[-2]
     _lib.call("ns_kv_write", k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
               slots.data_ptr(), n, row, _lib.dtype_code(k_new.dtype), _lib.stream_ptr())
+
+
+EPI_BIAS, EPI_SILU_MUL, EPI_ROPE_KV = 0, 1, 2
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, split_k: int = 1,
+                ln_w: torch.Tensor | None = None, residual: torch.Tensor | None = None, eps: float = 1e-6,
+                want_residual: bool = False, epilogue: int = EPI_BIAS, cos: torch.Tensor | None = None,
+                sin: torch.Tensor | None = None, k_cache: torch.Tensor | None = None,
+                v_cache: torch.Tensor | None = None, slots: torch.Tensor | None = None, n_heads: int = 0,
+                n_kv_heads: int = 0):
+    """Decode-sized GEMM x[M<=64, K] @ w[N, K]^T with fused prologue / epilogue (see ns_skinny_gemm in the header).
+    Returns `out`, or `(out, r)` when want_residual is set (r = residual + x, the new residual stream)."""
+    _lib.require_cuda(x, w, bias, ln_w, residual, cos, sin, k_cache, v_cache, slots)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    M, K = x.shape
+    N = w.shape[0]
+    inter = 0
+    if epilogue == EPI_SILU_MUL:
+        inter = N // 2
+        out = torch.empty(M, inter, device=x.device, dtype=x.dtype)
+    elif epilogue == EPI_ROPE_KV:
+        out = torch.empty(M, n_heads, 64, device=x.device, dtype=x.dtype)
+    else:
+        out = torch.empty(M, N, device=x.device, dtype=x.dtype)
+    r_out = torch.empty_like(x) if (want_residual and ln_w is not None and residual is not None) else None
+    _lib.call("ns_skinny_gemm", x.data_ptr(), _lib.ptr(residual), _lib.ptr(ln_w), _lib.ptr(r_out), w.data_ptr(),
+              _lib.ptr(bias), out.data_ptr(), M, N, K, split_k, float(eps), epilogue, inter, _lib.ptr(cos), _lib.ptr(sin),
+              _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slots), n_heads, n_kv_heads, _lib.stream_ptr())
+    return (out, r_out) if want_residual else out

@@ -1,0 +1,83 @@
+"""Fused skinny GEMM (ns_skinny_gemm) vs the unfused oracle ops: F.linear in fp32 on the same bf16 values rounded to
+bf16, then the token-wise op of the oracle. Tolerance: the GEMM sums K products in another order than the CPU, so the
+bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values (BASELINE's bf16
+bound for fused ops), and >= 98 % of the elements bitwise equal."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+
+def lin(x, w, b=None):
+    y = F.linear(x.float(), w.float(), None if b is None else b.float())
+    return y.to(torch.bfloat16)
+
+
+def close(got, want, min_same=0.98):
+    got, want = got.cpu(), want.cpu()
+    assert got.shape == want.shape
+    same = (got == want).float().mean().item()
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 and same >= min_same, (err, same)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 32, 33, 64])
+@pytest.mark.parametrize("N,K,split", [(896, 896, 4), (896, 4864, 8), (1152, 896, 1), (200, 256, 2)])
+def test_plain_gemm_with_and_without_bias(M, N, K, split):
+    from nanoserve_b200.kernels.fused import skinny_gemm
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.03).to(torch.bfloat16)
+    b = torch.randn(N, generator=g).to(torch.bfloat16)
+    close(skinny_gemm(x.cuda(), w.cuda(), split_k=split), lin(x, w))
+    close(skinny_gemm(x.cuda(), w.cuda(), b.cuda(), split_k=split), lin(x, w, b))
+
+
+@pytest.mark.parametrize("M", [5, 32])
+def test_norm_prologue_and_silu_epilogue(M):
+    from nanoserve_b200.kernels.fused import EPI_SILU_MUL, skinny_gemm
+    g = torch.Generator().manual_seed(M)
+    H, I = 896, 4864
+    a = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    ln = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    out, r = skinny_gemm(a.cuda(), w.cuda(), ln_w=ln.cuda(), residual=res.cuda(), want_residual=True, epilogue=EPI_SILU_MUL)
+    h, r_ref = O.add_rms_norm(a, ln, 1e-6, res)
+    assert torch.equal(r.cpu(), r_ref)
+    close(out, O.silu_mul(lin(h, w)), min_same=0.97)
+    # norm without a residual
+    out2 = skinny_gemm(a.cuda(), w.cuda(), ln_w=ln.cuda(), epilogue=EPI_SILU_MUL)
+    close(out2, O.silu_mul(lin(O.rms_norm(a, ln, 1e-6), w)), min_same=0.97)
+
+
+@pytest.mark.parametrize("M", [3, 32, 64])
+def test_qkv_rope_kv_write_epilogue(M):
+    from nanoserve_b200.kernels.fused import EPI_ROPE_KV, skinny_gemm
+    g = torch.Generator().manual_seed(100 + M)
+    H, NH, NKV, HD = 896, 14, 2, 64
+    a = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    ln = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = (torch.randn((NH + 2 * NKV) * HD, H, generator=g) * 0.03).to(torch.bfloat16)
+    b = torch.randn((NH + 2 * NKV) * HD, generator=g).to(torch.bfloat16)
+    cos, sin = O.rope_cos_sin(torch.randint(0, 4000, (M,), generator=g), HD, 1_000_000.0, torch.bfloat16)
+    slots = torch.randperm(16 * 16, generator=g)[:M]
+    kc = torch.zeros(16, 16, NKV, HD, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q, r = skinny_gemm(a.cuda(), w.cuda(), b.cuda(), split_k=4, ln_w=ln.cuda(), residual=res.cuda(), want_residual=True,
+                       epilogue=EPI_ROPE_KV, cos=cos.cuda(), sin=sin.cuda(), k_cache=kc, v_cache=vc, slots=slots.cuda(),
+                       n_heads=NH, n_kv_heads=NKV)
+    h, r_ref = O.add_rms_norm(a, ln, 1e-6, res)
+    assert torch.equal(r.cpu(), r_ref)
+    rq, rk, rv = O.rope_qkv(lin(h, w, b), cos, sin, NH, NKV, HD)
+    close(q, rq, min_same=0.97)
+    fk, fv = kc.view(-1, NKV, HD).cpu(), vc.view(-1, NKV, HD).cpu()
+    close(fk[slots], rk, min_same=0.97)
+    close(fv[slots], rv, min_same=0.97)
+    untouched = torch.ones(16 * 16, dtype=torch.bool)
+    untouched[slots] = False
+    assert not fk[untouched].any() and not fv[untouched].any()
