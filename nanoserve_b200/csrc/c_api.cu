@@ -33,6 +33,9 @@ int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t
 int decode_grid(int head_dim, int sms);
 bool prefill_mma_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
+bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
+int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
+static int g_prefill_impl = 0;          // 0 = tcgen05 where supported, 1 = always the mma.sync kernel
 
 static long long* g_timeline = nullptr;
 static int g_sm_count = 0;
@@ -54,6 +57,7 @@ extern "C" int ns_version(void) { return 100; }
 extern "C" const char* ns_last_error(void) { return g_err; }
 extern "C" int ns_sm_count(void) { return sm_count(); }
 extern "C" void ns_debug_decode_timeline(long long* device_buffer) { g_timeline = device_buffer; }
+extern "C" void ns_debug_prefill_impl(int impl) { g_prefill_impl = impl; }
 
 extern "C" int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim) {
     if (max_seqs <= 0 || max_tokens < 0 || n_heads <= 0 || head_dim <= 0) return -1;
@@ -141,7 +145,10 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
         int64_t max_items = n_tokens / kPrefillTileTokens + n_seqs;
         const int64_t cap = (int64_t)ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
         if (max_items > cap) max_items = cap;
-        rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
+        if (g_prefill_impl == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size))
+            rc = launch_prefill_tc(a, (int)max_items, st);
+        else
+            rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
     }
     return rc;
 }
