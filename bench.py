@@ -297,10 +297,8 @@ def run_gpu_arm(args) -> None:
     # every engine step reads back one int64 per scheduled sequence
     d2h_per_pass = 8 * sum(len(p[8:8 + 4 * int(p[0])]) // 4 for _, p in log)
 
-    t = torch.tensor([e2e_s, dev_s], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_max, dev_max = t.tolist()
+    from nanoserve_b200.replicas import max_over_ranks
+    e2e_max, dev_max = max_over_ranks([e2e_s, dev_s], device)
     total_tokens = tokens * world
     line = {
         "metric": METRIC, "value": pass_tokens * args.steps * world / dev_max, "unit": UNIT, "n_gpus": world,

@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     constexpr int STAGE_PARTS = 16;                   // partials whose (m, l) are staged at once
     extern __shared__ __align__(128) uint8_t smem[];
 
+    pdl_wait();
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
@@ -450,7 +451,7 @@ static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
                                           smem, cudaGetErrorString(e));
         configured = true;
     }
-    paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM><<<sms * CTAS_PER_SM, NWARPS * 32, smem, st>>>(p);
+    launch_pdl(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM>, dim3(sms * CTAS_PER_SM), dim3(NWARPS * 32), smem, st, p);
     return check_launch("paged_decode");
 }
 

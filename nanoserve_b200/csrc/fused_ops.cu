@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const T* __restrict__
     constexpr int V = Vec16<T>::N;
     const int64_t row = blockIdx.x;
     const int chunks = hidden / V;
+    pdl_wait();
     const T* xr = x + row * hidden;
     Vec16<T> vals[MAXC];
     float ss = 0.f;
@@ -81,11 +82,11 @@ static int launch_add_rmsnorm(const void* x, const void* res, const void* w, voi
     if (rows == 0) return NS_OK;
     dim3 grid((unsigned)rows);
     if (res != nullptr)
-        add_rmsnorm_kernel<T, true, MAXC><<<grid, threads, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (T*)out,
-                                                                    (T*)res_out, hidden, eps);
+        launch_pdl(add_rmsnorm_kernel<T, true, MAXC>, grid, dim3(threads), 0, st, (const T*)x, (const T*)res, (const T*)w,
+                   (T*)out, (T*)res_out, hidden, eps);
     else
-        add_rmsnorm_kernel<T, false, MAXC><<<grid, threads, 0, st>>>((const T*)x, nullptr, (const T*)w, (T*)out,
-                                                                     nullptr, hidden, eps);
+        launch_pdl(add_rmsnorm_kernel<T, false, MAXC>, grid, dim3(threads), 0, st, (const T*)x, (const T*)nullptr,
+                   (const T*)w, (T*)out, (T*)nullptr, hidden, eps);
     return check_launch("add_rmsnorm");
 }
 
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
     constexpr int V = Vec16<T>::N;
     const int cpr = inter / V;                       // chunks per row
     const int64_t total = rows * cpr;
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / cpr;
         const int c = (int)(i - r * cpr);
@@ -151,6 +153,7 @@ __global__ void __launch_bounds__(256) rope_qkv_kernel(const T* __restrict__ qkv
     const int heads = NH + 2 * NKV;
     const int64_t total = n_tokens * heads * cph;
     const int W = heads * HD;
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int c = (int)(i % cph);
         const int64_t th = i / cph;
@@ -231,7 +234,7 @@ static int launch_silu_mul(const void* gu, void* out, int64_t rows, int inter, c
     constexpr int V = Vec16<T>::N;
     NS_REQUIRE(inter % V == 0, NS_ERR_UNSUPPORTED, "silu_mul: width %d is not a multiple of %d", inter, V);
     if (rows == 0) return NS_OK;
-    silu_mul_kernel<T><<<grid_for(rows * (inter / V), 256), 256, 0, st>>>((const T*)gu, (T*)out, rows, inter);
+    launch_pdl(silu_mul_kernel<T>, dim3(grid_for(rows * (inter / V), 256)), dim3(256), 0, st, (const T*)gu, (T*)out, rows, inter);
     return check_launch("silu_mul");
 }
 
@@ -242,8 +245,8 @@ static int launch_rope(const void* qkv, const void* c, const void* s, void* q, v
     NS_REQUIRE(HD % (2 * V) == 0, NS_ERR_UNSUPPORTED, "rope_qkv: head_dim=%d is not a multiple of %d", HD, 2 * V);
     if (n == 0) return NS_OK;
     const int64_t work = n * (NH + 2 * NKV) * (HD / 2 / V);
-    rope_qkv_kernel<T><<<grid_for(work, 256), 256, 0, st>>>((const T*)qkv, (const T*)c, (const T*)s, (T*)q, (T*)k,
-                                                            (T*)v, (T*)kc, (T*)vc, slots, n, NH, NKV, HD);
+    launch_pdl(rope_qkv_kernel<T>, dim3(grid_for(work, 256)), dim3(256), 0, st, (const T*)qkv, (const T*)c, (const T*)s,
+               (T*)q, (T*)k, (T*)v, (T*)kc, (T*)vc, slots, n, NH, NKV, HD);
     return check_launch("rope_qkv_kvwrite");
 }
 
