@@ -54,10 +54,12 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
     const int cta = blockIdx.x;
     const int32_t* __restrict__ cta_start = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_start);
-    const int u0 = cta_start[cta], u1 = cta_start[cta + 1];   // independent loads: all in flight together
-    const int i_first = cta_first[cta];
+    // one 32-byte record holds the CTA's range and its first row's description: a single load before the block ids
+    const int4* __restrict__ rec = reinterpret_cast<const int4*>(p.ws + p.L.cta_rec) + 2 * cta;
+    const int4 rec_a = rec[0], rec_b = rec[1];
+    const int u0 = rec_a.x, u1 = rec_a.y, i_first = rec_a.z;
     if (u0 >= u1) return;
-    (void)hdr;
+    (void)hdr; (void)cta_first;
 
     const int4* __restrict__ dec_info = reinterpret_cast<const int4*>(p.ws + p.L.dec_info);   // {seq, len, table row, q row}
     const int2* __restrict__ dec_span = reinterpret_cast<const int2*>(p.ws + p.L.dec_span);   // {first CTA, CTAs} per row
@@ -92,8 +94,8 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     };
 
     // ---- prefetch cursor (runs STAGES-1 tiles ahead of the compute cursor) ------------------------------------
-    int pf_i = i_first, pf_lo = indptr[i_first], pf_hi = indptr[i_first + 1];
-    int4 pf_info = dec_info[pf_i];
+    int pf_i = i_first, pf_lo = rec_a.w, pf_hi = rec_b.x;
+    int4 pf_info = make_int4(0, rec_b.y, rec_b.z, rec_b.w);
     const int32_t* pf_table = p.block_tables + (int64_t)pf_info.z * p.table_stride;
     int pf_bids = 0, pf_bt = -1000000;        // lane L holds the block id of this warp's tile pf_bt + L
     uint32_t qn[HD / 16][2];                  // Q fragments of the row the prefetch cursor is in
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     int qa_row = -1;
     int cc_i = i_first, cc_lo = pf_lo, cc_hi = pf_hi;
     int cc_len = pf_info.y, cc_qrow = pf_info.w;
-    int2 cc_span = dec_span[i_first];
+    int2 cc_span = dec_span[i_first];         // only needed at the first flush: off the critical path
 
     // Combine the warps of this head for the current decode row [cc_lo, cc_hi), then write the final output or a
     // partial. Every value it needs is already in registers: no dependent global load on this path.

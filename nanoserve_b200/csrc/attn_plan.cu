@@ -130,8 +130,22 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         cta_start[c] = cut;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads)
-        cta_first[c] = cuts_sm[c] >= dec_blocks ? n_dec : row_of(cuts_sm[c]);
+    int4* cta_rec = reinterpret_cast<int4*>(ws + L.cta_rec);
+    for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) {
+        const int first = cuts_sm[c] >= dec_blocks ? n_dec : row_of(cuts_sm[c]);
+        cta_first[c] = first;
+        if (c < decode_ctas) {
+            // everything a decode CTA needs before its first K/V load, in one 32-byte record
+            int4 a = make_int4(cuts_sm[c], cuts_sm[c + 1], first, 0), b = make_int4(0, 0, 0, 0);
+            if (first < n_dec) {
+                const int4 info = dec_info[first];
+                a.w = ip[first];
+                b = make_int4(ip[first + 1], info.y, info.z, info.w);
+            }
+            cta_rec[2 * c] = a;
+            cta_rec[2 * c + 1] = b;
+        }
+    }
     // CTAs touching each row: the last CTA starting at or before the row's first unit .. the last CTA starting
     // before its end (CTAs between two equal cuts are empty and sit on a row boundary, never inside a row)
     for (int i = threadIdx.x; i < n_dec; i += kPlanThreads) {

@@ -38,6 +38,7 @@ struct WsLayout {
     int64_t cta_start;      // int32[kMaxDecodeCtas+1] first block-unit of each decode CTA (cut points)
     int64_t cta_first;      // int32[kMaxDecodeCtas+1] decode row holding the first block-unit of each CTA
     int64_t dec_span;       // int2[max_seqs] decode row i: {first CTA touching it, number of CTAs touching it}
+    int64_t cta_rec;        // int4[2*max_ctas] per decode CTA: {u0, u1, first row, its first unit} {its end unit, len, table row, q row}
     int64_t counters;       // int32[max_seqs*kMaxKvHeads] arrivals per (decode row, kv head); zero between launches
     int64_t prefill_items;  // int2[max_prefill_items] (batch index, first query token of the tile)
     int64_t partials;       // float[kMaxDecodeCtas*2][n_heads][head_dim+4]
@@ -56,6 +57,7 @@ __host__ __device__ inline WsLayout ws_layout(int max_seqs, int max_tokens, int 
     L.cta_start = o;      o = align256(o + 4 * (int64_t)(max_ctas + 1));
     L.cta_first = o;      o = align256(o + 4 * (int64_t)(max_ctas + 1));
     L.dec_span = o;       o = align256(o + 8 * (int64_t)max_seqs);
+    L.cta_rec = o;        o = align256(o + 32 * (int64_t)max_ctas);
     L.counters = o;       o = align256(o + 4 * (int64_t)max_seqs * kMaxKvHeads);
     const int64_t max_items = (int64_t)max_tokens / kPrefillTileTokens + max_seqs + 1;
     L.prefill_items = o;  o = align256(o + 8 * max_items);
