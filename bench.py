@@ -356,6 +356,82 @@ def launch_probe() -> None:
     print(json.dumps({"probe_steps": kinds, "engine": {k: eng.stats[k] for k in ("graph_steps", "piecewise_steps", "steps")}}))
 
 
+def timed_pass(eng, reqs, concurrency) -> tuple[float, int]:
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = closed_loop(eng, reqs, concurrency)
+    torch.cuda.synchronize()
+    return time.perf_counter() - t0, n
+
+
+def extra_workload(args) -> None:
+    """The other BASELINE configurations, end to end through the public API (wall clock between synchronisations):
+    sweep  = config 2 at concurrency 1/4/8/16/32/128/256;
+    prefix = config 3, Qwen2.5-1.5B shape, shared 1024-token prefix, c=32, prefix caching on vs off;
+    tp     = config 4, Qwen2.5-7B shape, tensor parallel over all ranks of the torchrun job (c=64)."""
+    import torch.distributed as dist
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.model import ModelConfig, Qwen2Model
+    from nanoserve_b200.synthetic import random_state_dict, serving_requests
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    res = {"workload": args.workload, "n_gpus": world}
+    if args.workload == "sweep":
+        sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.bfloat16, device=device)
+        model = Qwen2Model(ModelConfig(**cfg), sd)
+        reqs = workload()
+        for c in (1, 4, 8, 16, 32, 128, 256):
+            eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=c, max_num_batched_tokens=2048,
+                            kv_cache_tokens=max(65536, c * 1280))
+            eng.capture_graphs()
+            timed_pass(eng, reqs, c)
+            secs, n = min(timed_pass(eng, reqs, c) for _ in range(args.steps))
+            res[f"c{c}"] = {"tok_per_s": n / secs, "steps": eng.stats["steps"], "preemptions": eng.stats["num_preemptions"]}
+            del eng
+            torch.cuda.empty_cache()
+    elif args.workload == "prefix":
+        sd, cfg = random_state_dict("qwen2.5-1.5b", dtype=torch.bfloat16, device=device)
+        model = Qwen2Model(ModelConfig(**cfg), sd)
+        reqs = serving_requests(N_REQUESTS, prompt_range=(100, 320), output_range=(128, 128), vocab=cfg["vocab_size"], seed=3,
+                                shared_prefix=1024)
+        for on in (False, True):
+            eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY, max_num_batched_tokens=2048,
+                            prefix_caching=on)
+            eng.capture_graphs()
+            timed_pass(eng, reqs, CONCURRENCY)
+            eng.reset_stats()
+            secs, n = min(timed_pass(eng, reqs, CONCURRENCY) for _ in range(args.steps))
+            st = eng.stats
+            res["prefix_on" if on else "prefix_off"] = {"tok_per_s": n / secs, "hit_tokens": st["prefix_hit_tokens"],
+                                                        "query_tokens": st["prefix_query_tokens"]}
+            del eng
+            torch.cuda.empty_cache()
+    else:
+        from nanoserve_b200.tensor_parallel import random_tp_model
+        if world > 1:
+            dist.init_process_group("nccl", device_id=device)
+        else:
+            dist.init_process_group("gloo", rank=0, world_size=1, init_method="tcp://127.0.0.1:29533")
+        model = random_tp_model("qwen2.5-7b", device=device)
+        reqs = serving_requests(args.requests or 256, prompt_range=(256, 4096), output_range=(64, 512), vocab=152064, seed=4)
+        eng = LLMEngine(model, eos_token_ids=[], max_seq_len=4608, max_num_seqs=64, max_num_batched_tokens=2048,
+                        kv_cache_tokens=64 * 4608)
+        eng.capture_graphs()
+        timed_pass(eng, reqs[:64], 64)
+        secs, n = timed_pass(eng, reqs, 64)
+        t = torch.tensor([secs], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["tp"] = {"tp_degree": world, "tok_per_s": n / t.item(), "requests": len(reqs), "engine_steps": eng.stats["steps"]}
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        torch.cuda.synchronize()
+        os._exit(0)          # graphs hold captured NCCL work: leave without tearing the group down
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -366,8 +442,13 @@ def main() -> None:
                     help="short run for `ncu --profile-from-start off` launch lists: 2 decode steps at c=32 + 1 mixed step")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the decode-attention roofline leg (the small case used for ncu captures)")
+    ap.add_argument("--workload", default="serve", choices=["serve", "sweep", "prefix", "tp"],
+                    help="serve = the benchmark contract's line (default); the others print one JSON object of extras")
+    ap.add_argument("--requests", type=int, default=0)
     args = ap.parse_args()
-    if args.launch_probe:
+    if args.workload != "serve":
+        extra_workload(args)
+    elif args.launch_probe:
         launch_probe()
     elif args.roofline_only:
         torch.cuda.set_device(0)
