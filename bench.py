@@ -394,15 +394,16 @@ def extra_workload(args) -> None:
     elif args.workload == "prefix":
         sd, cfg = random_state_dict("qwen2.5-1.5b", dtype=torch.bfloat16, device=device)
         model = Qwen2Model(ModelConfig(**cfg), sd)
-        reqs = serving_requests(N_REQUESTS, prompt_range=(100, 320), output_range=(128, 128), vocab=cfg["vocab_size"], seed=3,
-                                shared_prefix=1024)
+        def fresh(seed):       # same 1024-token prefix, new suffixes: only the prefix can hit across passes
+            return serving_requests(N_REQUESTS, prompt_range=(100, 320), output_range=(128, 128), vocab=cfg["vocab_size"],
+                                    seed=seed, shared_prefix=1024)
         for on in (False, True):
             eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY, max_num_batched_tokens=2048,
                             prefix_caching=on)
             eng.capture_graphs()
-            timed_pass(eng, reqs, CONCURRENCY)
+            timed_pass(eng, fresh(3), CONCURRENCY)
             eng.reset_stats()
-            secs, n = min(timed_pass(eng, reqs, CONCURRENCY) for _ in range(args.steps))
+            secs, n = min(timed_pass(eng, fresh(10 + k), CONCURRENCY) for k in range(args.steps))
             st = eng.stats
             res["prefix_on" if on else "prefix_off"] = {"tok_per_s": n / secs, "hit_tokens": st["prefix_hit_tokens"],
                                                         "query_tokens": st["prefix_query_tokens"]}

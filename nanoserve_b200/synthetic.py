@@ -143,7 +143,8 @@ def serving_requests(n: int, prompt_range=(64, 1024), output_range=(16, 256), vo
     (the reference's harness draws lengths from its own RNG: bench/prompts.py:49,58). shared_prefix > 0
     prepends one seeded common prefix of that many tokens to every prompt (prefix-caching workload)."""
     rp, ro = random.Random(seed), random.Random(seed + 1)
-    prefix = [rp.randrange(vocab) for _ in range(shared_prefix)]
+    rprefix = random.Random(424242)              # the shared prefix does not depend on `seed`: new suffixes, same prefix
+    prefix = [rprefix.randrange(vocab) for _ in range(shared_prefix)]
     reqs = []
     for _ in range(n):
         plen = rp.randint(*prompt_range)
