@@ -2,8 +2,10 @@
 //
 // At M <= 64 a transformer GEMM is a weight read: Y[M,N] = X[M,K] . W[N,K]^T moves N*K*2 bytes of weights and
 // next to nothing else, so the kernel is built like the other HBM-bound kernels here, not like a tensor-core GEMM:
-//   * a CTA owns 64 weight rows and a K-slice; W streams through a 4-stage cp.async ring (64 rows x 64 k = 8 KB
-//     per stage, 128-bit copies, XOR-swizzled) while the activations of the slice sit in shared memory;
+//   * a CTA owns 64 weight rows and a K-slice; rows arrive by TMA bulk copies (cp.async.bulk, one per row: the
+//     k-slice of a row is one contiguous run) completing on mbarriers - one per warp for its own 16 weight rows, one
+//     for the activations - so a CTA issues ~100 copy instructions instead of ~10,000 16-byte ones; rows are padded
+//     by 16 bytes in shared memory so ldmatrix is conflict-free without a swizzle;
 //   * 4 warps x (16 weight rows x all token rows) of mma.sync m16n8k16 bf16 -> fp32;
 //   * narrow-N GEMMs (o_proj, down_proj, QKV) are split over K across a thread-block cluster; the partial tiles are
 //     summed through distributed shared memory in rank order (deterministic, no atomics, no second kernel);
@@ -42,14 +44,37 @@ struct GemmParams {
     float eps;
 };
 
-constexpr int kBN = 64;              // weight rows per CTA
-constexpr int kKS = 64;              // k per pipeline stage
-constexpr int kGemmStages = 4;
-constexpr int kGemmThreads = 128;
-
-__device__ __forceinline__ uint32_t w_off(int row, int chunk) {      // [64][64] bf16 stage, 16-byte chunks swizzled
-    return (uint32_t)(row * 128 + (((chunk ^ row) & 7) << 4));
+// ---- TMA bulk copy (1-D, no tensor map) completing on an mbarrier; every wait is bounded -----------------------
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(mbar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+constexpr int kBN = 64;              // weight rows per CTA
+constexpr int kGemmThreads = 128;
 
 template <int MT, int EPI>
 __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmParams p) {
@@ -62,9 +87,9 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     const int k0 = rank * p.k_slice, ks = p.k_slice;
     const int a_stride = ks * 2 + 16;                   // bytes per activation row in shared memory (+16: no bank conflicts)
     uint8_t* a_sm = smem;
-    uint8_t* w_sm = smem + (size_t)MP * a_stride;       // kGemmStages x 16 KB
+    uint8_t* w_sm = smem + (size_t)MP * a_stride;       // 4 warps x [16 weight rows][k-slice], rows padded like a_sm
     w_sm += (128 - (reinterpret_cast<uintptr_t>(w_sm) & 127)) & 127;
-    float* c_sm = reinterpret_cast<float*>(w_sm + kGemmStages * kBN * kKS * 2);   // [MP][64] fp32
+    float* c_sm = reinterpret_cast<float*>(w_sm + (size_t)kBN * a_stride);          // [MP][64] fp32
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -73,34 +98,49 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
         if (EPI == kEpiSiluMul) return t < 32 ? tile * 32 + t : p.inter + tile * 32 + (t - 32);
         return tile * kBN + t;
     };
-    const int n_stages = (ks + kKS - 1) / kKS;
-    auto load_stage = [&](int s) {
-        if (s < n_stages) {
-            const uint32_t base = smem_u32(w_sm + (size_t)(s % kGemmStages) * kBN * kKS * 2);
-            const int kk0 = s * kKS;
+    // Loads: one TMA bulk copy per row (the k-slice of a row is one contiguous run), completing on mbarriers: one
+    // barrier for the activations, one per warp for its own 16 weight rows. ~100 copy instructions per CTA.
+    __shared__ __align__(8) uint64_t mbars[5];
+    const uint32_t mb_a = smem_u32(&mbars[4]), mb_w = smem_u32(&mbars[warp]);
+    if (tid == 0) {
 #pragma unroll
-            for (int it = 0; it < (kBN * 8) / kGemmThreads; ++it) {
-                const int q = it * kGemmThreads + tid;
-                const int row = q >> 3, ch = q & 7;
-                const int k = kk0 + ch * 8;
-                const int wr = w_row(row);
-                const bool ok = k < ks && wr < p.N;
-                cp_async16(base + w_off(row, ch), p.w + (int64_t)(ok ? wr : 0) * p.K + k0 + (ok ? k : 0), ok ? 16 : 0);
+        for (int i = 0; i < 5; ++i) mbar_init(smem_u32(&mbars[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t row_bytes = (uint32_t)ks * 2;
+    const uint32_t my_w = smem_u32(w_sm) + (uint32_t)(16 * warp) * a_stride;
+    {
+        // this warp's weight rows
+        int valid = 0;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) valid += w_row(16 * warp + r) < p.N;
+        if (lane == 0) mbar_expect_tx(mb_w, valid * row_bytes);
+        __syncwarp();
+        if (lane < 16) {
+            const int wr = w_row(16 * warp + lane);
+            if (wr < p.N) {
+                bulk_g2s(my_w + lane * a_stride, p.w + (int64_t)wr * p.K + k0, row_bytes, mb_w);
+            } else {
+                for (uint32_t c = 0; c < row_bytes; c += 16)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(my_w + lane * a_stride + c), "r"(0) : "memory");
             }
         }
-        cp_async_commit();
-    };
-    if (p.ln_w == nullptr) {
-        // plain activations: asynchronous copy, in the same commit group as the first weight stage
+    }
+    if (p.ln_w == nullptr && warp == 0) {
+        // plain activations: bulk copies of the valid rows, zeros for the padding rows
+        if (lane == 0) mbar_expect_tx(mb_a, (uint32_t)p.M * row_bytes);
+        __syncwarp();
         const uint32_t ab = smem_u32(a_sm);
-        for (int q = tid; q < MP * (ks / 8); q += kGemmThreads) {
-            const int m = q / (ks / 8), c = q - m * (ks / 8);
-            const bool ok = m < p.M;
-            cp_async16(ab + m * a_stride + c * 16, p.x + (int64_t)(ok ? m : 0) * p.K + k0 + c * 8, ok ? 16 : 0);
+        for (int m = lane; m < MP; m += 32) {
+            if (m < p.M) {
+                bulk_g2s(ab + m * a_stride, p.x + (int64_t)m * p.K + k0, row_bytes, mb_a);
+            } else {
+                for (uint32_t c = 0; c < row_bytes; c += 16)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(ab + m * a_stride + c), "r"(0) : "memory");
+            }
         }
     }
-#pragma unroll
-    for (int s = 0; s < kGemmStages - 1; ++s) load_stage(s);     // weights start streaming before the prologue runs
 
     // ---- activations of this K-slice into shared memory --------------------------------------------------------
     if (p.ln_w != nullptr) {
@@ -152,32 +192,30 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
 #pragma unroll
         for (int j = 0; j < 2; ++j) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
     const uint32_t a_base = smem_u32(a_sm);
-    for (int s = 0; s < n_stages; ++s) {
-        cp_async_wait<kGemmStages - 2>();
-        __syncthreads();                                 // stage s landed; stage s-1 is free; (s == 0) activations visible
-        load_stage(s + kGemmStages - 1);
-        const uint32_t wb = smem_u32(w_sm + (size_t)(s % kGemmStages) * kBN * kKS * 2);
-        const int steps = min(kKS, ks - s * kKS) / 16;
-        for (int kk = 0; kk < steps; ++kk) {
+    __syncthreads();                                     // prologue stores / zero rows visible to every warp
+    bool landed = mbar_wait_bounded(mb_w, 0);
+    if (p.ln_w == nullptr) landed = mbar_wait_bounded(mb_a, 0) && landed;
+    if (landed) {
+#pragma unroll 4
+        for (int kk = 0; kk < ks / 16; ++kk) {
+            const int kcol = kk * 16;                    // k offset inside the slice
             uint32_t b00, b01, b10, b11;
             {
-                const int row = 16 * warp + (lane & 7) + ((lane >> 4) << 3);
-                const int ch = 2 * kk + ((lane >> 3) & 1);
-                ldmatrix_x4(wb + w_off(row, ch), b00, b01, b10, b11);
+                const int row = (lane & 7) + ((lane >> 4) << 3);
+                const int kbyte = (kcol + (((lane >> 3) & 1) << 3)) * 2;
+                ldmatrix_x4(my_w + row * a_stride + kbyte, b00, b01, b10, b11);
             }
-            const int kcol = s * kKS + kk * 16;          // k offset inside the slice
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 uint32_t a[4];
                 const int row = 16 * mt + (lane & 7) + (((lane >> 3) & 1) << 3);
-                const int kb = (kcol + ((lane >> 4) << 3)) * 2;
-                ldmatrix_x4(a_base + row * a_stride + kb, a[0], a[1], a[2], a[3]);
+                const int kbyte = (kcol + ((lane >> 4) << 3)) * 2;
+                ldmatrix_x4(a_base + row * a_stride + kbyte, a[0], a[1], a[2], a[3]);
                 mma_bf16_16816(acc[mt][0], a, b00, b01);
                 mma_bf16_16816(acc[mt][1], a, b10, b11);
             }
         }
     }
-    cp_async_wait<0>();
 
     // ---- partial tile to shared memory, cluster reduction -----------------------------------------------------------
     {
@@ -253,8 +291,7 @@ namespace ns {
 
 template <int MT, int EPI>
 static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
-    const size_t smem = (size_t)16 * MT * (p.k_slice * 2 + 16) + 128 + (size_t)kGemmStages * kBN * kKS * 2 +
-                        (size_t)16 * MT * kBN * 4;
+    const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + 128 + (size_t)16 * MT * kBN * 4;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -310,8 +347,9 @@ extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* l
     p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache; p.slots = slots;
     p.M = M; p.N = N; p.K = K; p.k_slice = K / split_k; p.inter = inter; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
     p.eps = eps;
-    const size_t a_bytes = (size_t)64 * (p.k_slice * 2 + 16);
-    NS_REQUIRE(a_bytes + kGemmStages * kBN * kKS * 2 + 64 * kBN * 4 + 128 <= 220 * 1024, NS_ERR_UNSUPPORTED,
+    const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const size_t a_bytes = (size_t)(mp + kBN) * (p.k_slice * 2 + 16);
+    NS_REQUIRE(a_bytes + (size_t)mp * kBN * 4 + 128 <= 220 * 1024 && p.k_slice <= 1024, NS_ERR_UNSUPPORTED,
                "skinny_gemm: K slice of %d does not fit shared memory (raise split_k)", p.k_slice);
     cudaStream_t st = (cudaStream_t)stream;
     if (epilogue == kEpiBias) return dispatch_mt<kEpiBias>(p, (N + kBN - 1) / kBN, split_k, st);

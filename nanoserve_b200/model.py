@@ -327,12 +327,16 @@ class Qwen2Model:
         sequence's last token. Fused path only."""
         if not self.fused:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
-        from nanoserve_b200.kernels.fused import rms_norm as norm, rope_cos_sin, rope_qkv, silu_mul
+        from nanoserve_b200.kernels.fused import SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin, rope_qkv, silu_mul, skinny_gemm
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
         T = meta.tokens.shape[0]
         cu = None if meta.decode_only else meta.cu_seqlens
+        # decode-sized steps: down_proj is a pure weight read (K = intermediate size): the bulk-copy skinny GEMM with
+        # an 8-way cluster split over K beats the library GEMM there; everything else stays F.linear
+        inter = self.layers[0].down_w.shape[1]
+        skinny_down = (self.dtype == torch.bfloat16 and T <= SKINNY_MAX_ROWS and inter % 128 == 0 and inter // 8 <= 1024)
         if plan:
             meta.workspace.plan(meta.seq_lens, cu, meta.n_seqs, paged.block_size, meta.table_rows)
         cos, sin = rope_cos_sin(meta.positions, self.inv_freq, hd, self.dtype)
@@ -347,7 +351,8 @@ class Qwen2Model:
                                        planned=True)
             a = self._all_reduce(F.linear(o.view(T, nh * hd), layer.o_w))
             h, x = norm(a, layer.ln2, eps, residual=x)
-            d = self._all_reduce(F.linear(silu_mul(F.linear(h, layer.gate_up_w)), layer.down_w))
+            m = silu_mul(F.linear(h, layer.gate_up_w))
+            d = self._all_reduce(skinny_gemm(m, layer.down_w, split_k=8) if skinny_down else F.linear(m, layer.down_w))
             nxt = self.layers[i + 1].ln1 if i + 1 < len(self.layers) else self.norm
             h, x = norm(d, nxt, eps, residual=x)          # x + mlp, then the next layer's (or the final) norm
         return F.linear(h.index_select(0, meta.last_rows), self.lm_head)

@@ -25,7 +25,7 @@ def close(got, want, min_same=0.98):
 
 
 @pytest.mark.parametrize("M", [1, 7, 16, 32, 33, 64])
-@pytest.mark.parametrize("N,K,split", [(896, 896, 4), (896, 4864, 8), (1152, 896, 1), (200, 256, 2)])
+@pytest.mark.parametrize("N,K,split", [(896, 896, 4), (896, 4864, 8), (1152, 896, 2), (200, 256, 2)])
 def test_plain_gemm_with_and_without_bias(M, N, K, split):
     from nanoserve_b200.kernels.fused import skinny_gemm
     g = torch.Generator().manual_seed(M * 1000 + N)
