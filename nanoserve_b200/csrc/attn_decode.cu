@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     constexpr int STAGE_PARTS = 16;                   // partials whose (m, l) are staged at once
     extern __shared__ __align__(128) uint8_t smem[];
 
+    pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
     pdl_wait();
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);

@@ -111,6 +111,9 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 // stream is still draining; pdl_wait() (griddepcontrol.wait) blocks until the predecessor's memory is visible and
 // must precede the first read of anything the predecessor wrote. It is a no-op in a normally launched kernel.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel in the stream (if it was launched with launch_pdl) start being scheduled now; it still blocks in
+// its own pdl_wait() until this grid has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const T* __restrict__
     constexpr int V = Vec16<T>::N;
     const int64_t row = blockIdx.x;
     const int chunks = hidden / V;
+    pdl_launch_dependents();
     pdl_wait();
     const T* xr = x + row * hidden;
     Vec16<T> vals[MAXC];
@@ -97,6 +98,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
     constexpr int V = Vec16<T>::N;
     const int cpr = inter / V;                       // chunks per row
     const int64_t total = rows * cpr;
+    pdl_launch_dependents();          // down_proj may start streaming its weights while this kernel runs
     pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / cpr;
@@ -153,6 +155,7 @@ __global__ void __launch_bounds__(256) rope_qkv_kernel(const T* __restrict__ qkv
     const int heads = NH + 2 * NKV;
     const int64_t total = n_tokens * heads * cph;
     const int W = heads * HD;
+    pdl_launch_dependents();          // the attention kernel that follows may get scheduled while this one runs
     pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int c = (int)(i % cph);

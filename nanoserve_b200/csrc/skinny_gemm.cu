@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
             }
         }
     }
+    pdl_wait();        // everything above touched only weights; the activations come from the preceding kernel
     if (p.ln_w == nullptr && warp == 0) {
         // plain activations: bulk copies of the valid rows, zeros for the padding rows
         if (lane == 0) mbar_expect_tx(mb_a, (uint32_t)p.M * row_bytes);
@@ -304,13 +305,15 @@ static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = (unsigned)split_k;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<MT, EPI>, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: launch failed: %s", cudaGetErrorString(e));
     return NS_OK;
@@ -334,8 +337,7 @@ extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* l
     if (M == 0) return NS_OK;
     NS_REQUIRE(x && w && out, NS_ERR_INVALID_ARG, "skinny_gemm: null pointer");
     NS_REQUIRE(M <= 64, NS_ERR_UNSUPPORTED, "skinny_gemm: %d token rows > 64 (use the library GEMM for large batches)", M);
-    NS_REQUIRE(split_k == 1 || split_k == 2 || split_k == 4 || split_k == 8, NS_ERR_INVALID_ARG,
-               "skinny_gemm: split_k must be 1, 2, 4 or 8");
+    NS_REQUIRE(split_k >= 1 && split_k <= 8, NS_ERR_INVALID_ARG, "skinny_gemm: split_k must be between 1 and 8");
     NS_REQUIRE(K % (16 * split_k) == 0, NS_ERR_UNSUPPORTED, "skinny_gemm: K=%d is not a multiple of 16*split_k", K);
     NS_REQUIRE(residual == nullptr || ln_w != nullptr, NS_ERR_INVALID_ARG, "skinny_gemm: residual needs the norm prologue");
     NS_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0, NS_ERR_INVALID_ARG,

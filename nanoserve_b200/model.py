@@ -151,6 +151,7 @@ class Qwen2Model:
     token-wise ops; attention always runs on the ragged paged kernel."""
 
     fused = False
+    skinny_gemms = True      # decode-sized steps: narrow GEMMs through the weight-streaming kernel (False = library GEMMs)
     tp_group = None          # torch.distributed process group when the model is one tensor-parallel shard
     tp_size = 1
 
@@ -327,7 +328,8 @@ class Qwen2Model:
         sequence's last token. Fused path only."""
         if not self.fused:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
-        from nanoserve_b200.kernels.fused import SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin, rope_qkv, silu_mul, skinny_gemm
+        from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin, rope_qkv,
+                                                  silu_mul, skinny_gemm)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
@@ -336,7 +338,16 @@ class Qwen2Model:
         # decode-sized steps: down_proj is a pure weight read (K = intermediate size): the bulk-copy skinny GEMM with
         # an 8-way cluster split over K beats the library GEMM there; everything else stays F.linear
         inter = self.layers[0].down_w.shape[1]
-        skinny_down = (self.dtype == torch.bfloat16 and T <= SKINNY_MAX_ROWS and inter % 128 == 0 and inter // 8 <= 1024)
+        skinny = self.dtype == torch.bfloat16 and T <= SKINNY_MAX_ROWS and self.skinny_gemms
+        skinny_down = skinny and inter % 128 == 0 and inter // 8 <= 1024
+        hidden = cfg.hidden_size
+        # QKV with the RoPE + KV-write epilogue (64-wide heads) and o_proj: narrow GEMMs whose weights can stream while
+        # the preceding norm / attention kernel still runs (programmatic dependent launch)
+        import os
+        mask = int(os.environ.get("NS_SKINNY_MASK", "3"))
+        skinny_down = skinny_down and bool(mask & 1)
+        skinny_qkv = skinny and hd == 64 and hidden % 128 == 0 and bool(mask & 2)
+        skinny_o = skinny and (nh * hd) % 128 == 0 and bool(mask & 4)
         if plan:
             meta.workspace.plan(meta.seq_lens, cu, meta.n_seqs, paged.block_size, meta.table_rows)
         cos, sin = rope_cos_sin(meta.positions, self.inv_freq, hd, self.dtype)
@@ -344,12 +355,17 @@ class Qwen2Model:
         h = norm(x, self.layers[0].ln1, eps)
         scale = hd ** -0.5
         for i, layer in enumerate(self.layers):
-            qkv = F.linear(h, layer.qkv_w, layer.qkv_b)
-            q, _, _ = rope_qkv(qkv, cos, sin, nh, nkv, hd, paged.k[i], paged.v[i], meta.slot_mapping, dense_kv=False)
+            if skinny_qkv:
+                q = skinny_gemm(h, layer.qkv_w, layer.qkv_b, split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin,
+                                k_cache=paged.k[i], v_cache=paged.v[i], slots=meta.slot_mapping, n_heads=nh, n_kv_heads=nkv)
+            else:
+                qkv = F.linear(h, layer.qkv_w, layer.qkv_b)
+                q, _, _ = rope_qkv(qkv, cos, sin, nh, nkv, hd, paged.k[i], paged.v[i], meta.slot_mapping, dense_kv=False)
             o = ragged_paged_attention(q, paged.k[i], paged.v[i], meta.block_tables, meta.seq_lens, cu, scale,
                                        n_seqs=meta.n_seqs, table_rows=meta.table_rows, workspace=meta.workspace,
                                        planned=True)
-            a = self._all_reduce(F.linear(o.view(T, nh * hd), layer.o_w))
+            o2 = o.view(T, nh * hd)
+            a = self._all_reduce(skinny_gemm(o2, layer.o_w, split_k=8) if skinny_o else F.linear(o2, layer.o_w))
             h, x = norm(a, layer.ln2, eps, residual=x)
             m = silu_mul(F.linear(h, layer.gate_up_w))
             d = self._all_reduce(skinny_gemm(m, layer.down_w, split_k=8) if skinny_down else F.linear(m, layer.down_w))
