@@ -74,10 +74,16 @@ class StepBuffers:
         self.seat_of = torch.full((self.max_seqs,), self.pad_seat, **i32)
         self.last_rows = torch.zeros(self.max_seqs, **i64)
         self.sampled = torch.zeros(self.max_seqs, **i64)
-        self.sampled_host = torch.zeros(self.max_seqs, dtype=torch.int64, pin_memory=True)
+        # two pinned landing buffers for sampled tokens and two pinned staging buffers for packed steps, used in
+        # turn: with one step in flight the host may fill step t+1's staging buffer while step t's copy is pending
+        self._sampled_host = [torch.zeros(self.max_seqs, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+        self._fetch_events = [torch.cuda.Event() for _ in range(2)]
+        self._fetch_turn = 0
         self.capacity = _HEADER_INTS + 4 * self.max_seqs + 3 * self.max_seqs * self.table_width + self.max_tokens
-        self.host_packed = torch.zeros(self.capacity, dtype=torch.int32, pin_memory=True)
-        self._np = self.host_packed.numpy()
+        self._staging = [torch.zeros(self.capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._staging_np = [t.numpy() for t in self._staging]
+        self._staging_turn = 0
+        self.host_packed = self._staging[0]          # the staging buffer of the latest upload
         self.dev_packed = torch.zeros(self.capacity, **i32)
         nh = cfg.n_heads // getattr(model, "tp_size", 1)
         self.workspace = AttnWorkspace(self.max_seqs, self.max_tokens, nh, cfg.head_dim, dev)
@@ -89,7 +95,9 @@ class StepBuffers:
         if pad_seqs > self.max_seqs or pad_tokens > self.max_tokens:
             raise ValueError(f"step of {pad_seqs} sequences / {pad_tokens} tokens exceeds the buffers "
                              f"({self.max_seqs} / {self.max_tokens})")
-        a = self._np
+        self._staging_turn ^= 1
+        self.host_packed = self._staging[self._staging_turn]
+        a = self._staging_np[self._staging_turn]
         a[:_HEADER_INTS] = (n_seqs, n_tokens, pad_seqs, pad_tokens, n_app, self.garbage_block, self.block_size,
                             self.table_width)
         o = _HEADER_INTS
@@ -137,11 +145,23 @@ class StepBuffers:
         self.sample(logits, n_seqs)
         return logits
 
+    def queue_fetch(self, n: int):
+        """Start the copy of the step's n sampled token ids to pinned host memory (stream-ordered after the step) and
+        record an event behind it. Returns a handle for wait_fetch. At most two fetches may be outstanding."""
+        turn = self._fetch_turn
+        self._fetch_turn ^= 1
+        self._sampled_host[turn][:n].copy_(self.sampled[:n], non_blocking=True)
+        self._fetch_events[turn].record()
+        return turn, n
+
+    def wait_fetch(self, handle) -> list[int]:
+        """Block until the fetch behind `handle` has landed: the step's only device->host sync."""
+        turn, n = handle
+        self._fetch_events[turn].synchronize()
+        return self._sampled_host[turn][:n].tolist()
+
     def fetch_sampled(self, n: int) -> list[int]:
-        """The step's only device->host sync: n sampled token ids."""
-        self.sampled_host[:n].copy_(self.sampled[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.sampled_host[:n].tolist()
+        return self.wait_fetch(self.queue_fetch(n))
 
 
 class _GraphRunner:

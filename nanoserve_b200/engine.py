@@ -6,6 +6,14 @@
 the forward's inputs are no longer Python lists turned into tensors: the scheduler's decision is packed into a
 small int32 record buffer, uploaded once, and expanded on the device, so pure-decode AND mixed steps replay a
 single CUDA graph that already contains the LM head and the argmax.
+
+`lookahead=True` (not in the reference) keeps one step in flight: after launching step t the host does step t's
+bookkeeping with the sampled tokens still unknown, and the next call schedules and launches step t+1 BEFORE it
+waits for step t's tokens, so scheduling and launching overlap the device. The scheduler only ever needs a token's
+VALUE for the end-of-sequence test, so this is done only for steps whose sampling sequences all have
+ignore_eos=True; any other step is waited for before the host goes on, exactly as without the option. Scheduling
+decisions, and therefore tokens, are the same as without lookahead; `step()` returns a step's outputs one call
+later and `has_unfinished()` stays true until they have been returned.
 """
 from __future__ import annotations
 
@@ -41,7 +49,7 @@ class LLMEngine:
                  batch_wait_s: float = 0.02, kv_cache: str = "paged", kv_cache_tokens: int | None = None,
                  block_size: int = 16, attn_backend: str | None = None, cuda_graphs: bool | None = None,
                  chunked_prefill: bool | None = None, piecewise_graphs: bool | None = None,
-                 fused_ops: bool | None = None, prefix_caching: bool = False):
+                 fused_ops: bool | None = None, prefix_caching: bool = False, lookahead: bool = False):
         if model.device.type != "cuda":
             raise ValueError("nanoserve_b200 engines run on a CUDA device only")
         if kv_cache != "paged":
@@ -53,6 +61,8 @@ class LLMEngine:
             raise ValueError("fused_ops=False: the engine path always runs the fused kernels "
                              "(Qwen2Model.forward_batch still offers the unfused ops for comparisons)")
         self.attn_backend = "native"
+        self.lookahead = bool(lookahead)
+        self._pending = None        # lookahead: (fetch handle, [(seq, index into output_ids, row, finished)])
         self.eos_token_ids = list(eos_token_ids)
         self._eos = set(self.eos_token_ids)
         self.max_seq_len = max_seq_len
@@ -152,7 +162,7 @@ class LLMEngine:
         return seq.seq_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._pending is not None
 
     def abort(self, seq_id: int) -> None:
         seq = self.sequences.pop(seq_id, None)
@@ -160,15 +170,20 @@ class LLMEngine:
             self.scheduler.abort(seq)
 
     # ---- one step -----------------------------------------------------------------------------------------------
+    _UNKNOWN = -1                  # stands in output_ids for a token that was sampled but not yet read back
+
     def step(self) -> list[StepOutput]:
         if self.timing is not None:
             self.timing["_step_start"] = time.perf_counter()
+        outputs: list[StepOutput] = []
         plan = self.scheduler.schedule(now=time.perf_counter())
         scheduled, chunks = plan.scheduled, plan.chunks
         if not scheduled:
             self.last_step = None
-            return []
+            return self._resolve_pending(outputs)
         self._mark("schedule")
+        if self._pending is not None and self._needs_unknown_token(scheduled, chunks):
+            self._resolve_pending(outputs)             # a re-prefill is about to read a token id from the host lists
         records, appends, token_ids = self.kv.step_records(scheduled, chunks)
         n_seqs, n_tokens = len(scheduled), sum(chunks)
         n_prefill = sum(1 for s in scheduled if s.is_prefill)
@@ -190,30 +205,62 @@ class LLMEngine:
             path = ("eager", (n_tokens, n_seqs))
         if self.step_log is not None:                                # device-resident replay (see replay_on_device)
             self.step_log.append((path, buf.host_packed[:buf.packed_ints].clone()))
+        handle = buf.queue_fetch(n_seqs)                             # greedy; one read-back for the whole batch
         self._mark("launch", gpu_end=True)
-        next_tokens = buf.fetch_sampled(n_seqs)                      # greedy; one sync for the whole batch
+        self._resolve_pending(outputs)                               # the previous step's tokens, if still out
+        run_ahead = self.lookahead and all(s.ignore_eos for s, n in zip(scheduled, chunks)
+                                           if s.num_cached + n >= s.num_tokens)
+        next_tokens = None if run_ahead else buf.wait_fetch(handle)
         self._mark("wait")
 
-        outputs = []
-        eos = self._eos
-        for seq, n, tok in zip(scheduled, chunks, next_tokens):
+        for seq, n in zip(scheduled, chunks):
             self.kv.commit(seq, n)
             seq.num_cached += n
         self._record_stats(scheduled)
-        for seq, tok in zip(scheduled, next_tokens):
+        eos = self._eos
+        entries = []
+        for row, seq in enumerate(scheduled):
             if seq.num_cached < seq.num_tokens:
                 self._stats["prefill_chunks"] += 1                   # mid-prompt chunk: nothing to sample
                 seq.token_on_device = False
                 continue
+            tok = self._UNKNOWN if run_ahead else next_tokens[row]
             seq.output_ids.append(tok)
             seq.token_on_device = True
             finished = (tok in eos and not seq.ignore_eos) or len(seq.output_ids) >= seq.max_new_tokens
             if finished:
                 self.scheduler.finish(seq)
                 del self.sequences[seq.seq_id]
-            outputs.append(StepOutput(seq.seq_id, tok, finished))
+            if run_ahead:
+                entries.append((seq, len(seq.output_ids) - 1, row, finished))
+            else:
+                outputs.append(StepOutput(seq.seq_id, tok, finished))
+        if run_ahead:
+            self._pending = (handle, entries)
         self._mark("post")
         return outputs
+
+    def _resolve_pending(self, outputs: list[StepOutput]) -> list[StepOutput]:
+        """Wait for the tokens of the step in flight (if any), put them where their stand-ins are, and append that
+        step's outputs."""
+        if self._pending is not None:
+            handle, entries = self._pending
+            self._pending = None
+            tokens = self.buffers.wait_fetch(handle)
+            for seq, at, row, finished in entries:
+                seq.output_ids[at] = tokens[row]
+                outputs.append(StepOutput(seq.seq_id, tokens[row], finished))
+        return outputs
+
+    def _needs_unknown_token(self, scheduled, chunks) -> bool:
+        """True if this step's packed record would carry the value of a token that is still on its way back: a
+        sequence whose newest output is a stand-in and which does not feed it from the device's last_tokens."""
+        unknown = self._UNKNOWN
+        for seq, n in zip(scheduled, chunks):
+            if seq.output_ids and seq.output_ids[-1] == unknown and seq.num_cached + n >= seq.num_tokens \
+                    and not (n == 1 and seq.token_on_device and seq.remaining == 1):
+                return True
+        return False
 
     # ---- device-resident replay -------------------------------------------------------------------------------------
     step_log: list | None = None      # set to [] to record (path, packed step buffer) of every step
