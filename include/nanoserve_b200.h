@@ -82,12 +82,39 @@ int ns_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cac
  *   and sum rounded to bf16), writes q to out [M, n_heads*64] and k / v into one layer's paged pool at slots[m].
  * split_k (1, 2, 4, 8) spreads K over a thread-block cluster whose partial tiles are summed through distributed
  * shared memory in a fixed order. K must be a multiple of 16*split_k.
+ * prefetch / prefetch_bytes (may be NULL / 0): a byte range, 16-byte aligned and a multiple of 16 long, that the
+ * kernels AFTER this one will read (the weights of the layer's later GEMMs); the grid issues L2 prefetches for it
+ * before it waits for its own inputs.
  * Replaces, fused: nanoserve/model.py:231 (rms_norm + merged QKV F.linear + rope_qkv), :256 (o_proj), :256-257
  * (add + rms_norm + gate/up F.linear + silu_mul) and :257 (down_proj) for steps of at most 64 token rows. */
 int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const void* w,
                    const void* bias, void* out, int32_t M, int32_t N, int32_t K, int32_t split_k, float eps,
                    int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache, void* v_cache,
-                   const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream);
+                   const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, const void* prefetch,
+                   int64_t prefetch_bytes, void* stream);
+
+/* Persistent weight-streaming GEMM for decode-sized batches (bf16 only):
+ *   out = epilogue( prologue(x) . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, N % 16 == 0,
+ *   K one of 896, 1024, 1536 (64 token rows only up to K = 1024).
+ * One CTA per SM walks 16-row units of w through a shared-memory ring fed by bulk copies; the activations stay in
+ * registers; K is split over 8 warps whose partial sums are added in a fixed order.
+ * prologue (ln_w != NULL), the GEMM input is ln_w * bf16(r * rsqrt(mean(r^2) + eps)) with
+ *   ss_in == NULL: r = residual + x rounded to bf16 (r = x when residual == NULL), stored to residual_out when given;
+ *   ss_in != NULL: r = x, and mean(r^2) comes from ss_in[M, ss_parts], the per-row partial sums of r^2 that the GEMM
+ *                  which produced x left behind (epilogue 2 below), added in order.
+ * epilogue 0: out[M, N] = bf16(acc + bias) (bias may be NULL);
+ * epilogue 1: w = [gate; up] (N = 2*inter rows), out[M, inter] = bf16(bf16(silu(bf16(gate))) * bf16(up));
+ * epilogue 2: out[M, N] = bf16(add_in + bf16(acc + bias)), the new residual stream, and ss_out[M, N/16] = the sum of
+ *             out^2 over each 16-column unit (ss_out may be NULL).
+ * Replaces, fused: nanoserve/model.py:256-257 (o_proj + residual add; rms_norm + gate/up F.linear + silu_mul) for
+ * steps of at most 64 token rows. */
+int ns_stream_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const float* ss_in,
+                   int32_t ss_parts, const void* w, const void* bias, void* out, const void* add_in, float* ss_out,
+                   int32_t M, int32_t N, int32_t K, float eps, int32_t epilogue, void* stream);
+
+/* Number of bounded waits that ran out inside ns_stream_gemm kernels since the library was loaded (0 in a healthy
+ * run; results of a launch that raised it are undefined). Synchronises the device. No reference counterpart. */
+int ns_stream_gemm_errors(uint32_t* count);
 
 /* ------------------------------------------------------------------------------------------------
  * Ragged paged attention.

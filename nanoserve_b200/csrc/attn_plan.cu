@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
                                                                  const int32_t* __restrict__ cu_seqlens,
                                                                  const int32_t* __restrict__ table_rows, int n_seqs,
                                                                  int block_size, int decode_ctas, uint8_t* ws,
-                                                                 WsLayout L, int max_items) {
+                                                                 WsLayout L, int max_items, int min_blocks) {
     constexpr int kSmemRows = 2048;            // decode rows whose prefix is mirrored in shared memory
     __shared__ int warp_sums[33];
     __shared__ int indptr_sm[kSmemRows + 1];
@@ -99,9 +99,9 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     const int* ip = n_dec <= kSmemRows ? indptr_sm : dec_indptr;
 
     int per = (dec_blocks + decode_ctas - 1) / decode_ctas;
-    if (per < kMinBlocksPerCta) per = kMinBlocksPerCta;
+    if (per < min_blocks) per = min_blocks;
     const int used = (dec_blocks + per - 1) / per;
-    const int slack = per <= 2 * kMinBlocksPerCta ? per / 2 : per / 8;   // how far a cut may move to reach a row boundary
+    const int slack = per <= 2 * kSnapBlocks ? per / 2 : per / 8;   // how far a cut may move to reach a row boundary
     int32_t* cta_start = reinterpret_cast<int32_t*>(ws + L.cta_start);
     int2* dec_span = reinterpret_cast<int2*>(ws + L.dec_span);
     __shared__ int cuts_sm[kMaxDecodeCtas + 1];
@@ -179,11 +179,14 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     }
 }
 
+static int g_min_blocks = kMinBlocksPerCta;
+void debug_set_min_blocks(int n) { g_min_blocks = n > 0 ? n : kMinBlocksPerCta; }
+
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
                      int block_size, int decode_ctas,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
     attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, decode_ctas,
-                                                 (uint8_t*)ws, L, max_items);
+                                                 (uint8_t*)ws, L, max_items, g_min_blocks);
     return check_launch("attn_plan");
 }
 

@@ -53,6 +53,10 @@ static int sm_count() {
 
 using namespace ns;
 
+namespace ns { void debug_set_min_blocks(int n); }
+// Debug hook (not part of the public header): lower bound of a decode CTA's range in KV blocks (0 = default).
+extern "C" void ns_debug_min_blocks(int n) { ns::debug_set_min_blocks(n); }
+
 extern "C" int ns_version(void) { return 100; }
 extern "C" const char* ns_last_error(void) { return g_err; }
 extern "C" int ns_sm_count(void) { return sm_count(); }

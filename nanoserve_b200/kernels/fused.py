@@ -100,6 +100,7 @@ def kv_write(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_
 
 
 EPI_BIAS, EPI_SILU_MUL, EPI_ROPE_KV = 0, 1, 2
+EPI_RESIDUAL = 2          # ns_stream_gemm's third epilogue (ns_skinny_gemm: 3)
 SKINNY_MAX_ROWS = 64
 
 
@@ -108,9 +109,10 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
                 want_residual: bool = False, epilogue: int = EPI_BIAS, cos: torch.Tensor | None = None,
                 sin: torch.Tensor | None = None, k_cache: torch.Tensor | None = None,
                 v_cache: torch.Tensor | None = None, slots: torch.Tensor | None = None, n_heads: int = 0,
-                n_kv_heads: int = 0):
+                n_kv_heads: int = 0, prefetch: tuple[int, int] | None = None):
     """Decode-sized GEMM x[M<=64, K] @ w[N, K]^T with fused prologue / epilogue (see ns_skinny_gemm in the header).
-    Returns `out`, or `(out, r)` when want_residual is set (r = residual + x, the new residual stream)."""
+    Returns `out`, or `(out, r)` when want_residual is set (r = residual + x, the new residual stream).
+    prefetch = (device address, bytes) of what the following kernels will stream (pulled into L2 by this launch)."""
     _lib.require_cuda(x, w, bias, ln_w, residual, cos, sin, k_cache, v_cache, slots)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -127,5 +129,56 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     r_out = torch.empty_like(x) if (want_residual and ln_w is not None and residual is not None) else None
     _lib.call("ns_skinny_gemm", x.data_ptr(), _lib.ptr(residual), _lib.ptr(ln_w), _lib.ptr(r_out), w.data_ptr(),
               _lib.ptr(bias), out.data_ptr(), M, N, K, split_k, float(eps), epilogue, inter, _lib.ptr(cos), _lib.ptr(sin),
-              _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slots), n_heads, n_kv_heads, _lib.stream_ptr())
+              _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slots), n_heads, n_kv_heads,
+              prefetch[0] if prefetch else None, prefetch[1] if prefetch else 0, _lib.stream_ptr())
     return (out, r_out) if want_residual else out
+
+
+STREAM_KS = (896, 1024, 1536)
+
+
+def stream_gemm_supported(M: int, N: int, K: int) -> bool:
+    """Shapes ns_stream_gemm is built for (see the header): K in STREAM_KS, N % 16 == 0, M <= 64 (M <= 32 above
+    K = 1024)."""
+    return K in STREAM_KS and N % 16 == 0 and 0 < M <= (64 if K <= 1024 else 32)
+
+
+def stream_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, ln_w: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None, eps: float = 1e-6, want_residual: bool = False,
+                epilogue: int = EPI_BIAS, ss_in: torch.Tensor | None = None, add_in: torch.Tensor | None = None,
+                want_ss: bool = False):
+    """Decode-sized GEMM x[M<=64, K] @ w[N, K]^T through the persistent weight-streaming kernel (ns_stream_gemm).
+    Prologue: RMSNorm with weight ln_w of (residual + x), or, with ss_in [M, parts] (the sum-of-squares partials a
+    producing GEMM left), of x itself. Epilogue: bias, SiLU*mul, or EPI_RESIDUAL: out = add_in + gemm, returned with
+    its own partials when want_ss is set. Returns `out`, `(out, r)` with want_residual (r = residual + x), or
+    `(out, ss)` with want_ss."""
+    _lib.require_cuda(x, w, bias, ln_w, residual, ss_in, add_in)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and epilogue in (EPI_BIAS, EPI_SILU_MUL, EPI_RESIDUAL)
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N // 2 if epilogue == EPI_SILU_MUL else N, device=x.device, dtype=x.dtype)
+    r_out = torch.empty_like(x) if (want_residual and ln_w is not None and residual is not None) else None
+    parts = 0
+    if ss_in is not None:
+        assert ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.shape[0] == M
+        parts = ss_in.shape[1]
+    ss_out = None
+    if epilogue == EPI_RESIDUAL:
+        assert add_in is not None and add_in.shape == out.shape and add_in.is_contiguous() and add_in.dtype == x.dtype
+        if want_ss:
+            ss_out = torch.empty(M, N // 16, device=x.device, dtype=torch.float32)
+    _lib.call("ns_stream_gemm", x.data_ptr(), _lib.ptr(residual), _lib.ptr(ln_w), _lib.ptr(r_out), _lib.ptr(ss_in), parts,
+              w.data_ptr(), _lib.ptr(bias), out.data_ptr(), _lib.ptr(add_in), _lib.ptr(ss_out), M, N, K, float(eps),
+              epilogue, _lib.stream_ptr())
+    if want_ss:
+        return out, ss_out
+    return (out, r_out) if want_residual else out
+
+
+def stream_gemm_errors() -> int:
+    """Bounded waits that ran out inside stream_gemm kernels since the library was loaded (synchronises)."""
+    import ctypes
+    n = ctypes.c_uint32(0)
+    _lib.call("ns_stream_gemm_errors", ctypes.addressof(n))
+    return int(n.value)

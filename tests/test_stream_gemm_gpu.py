@@ -1,0 +1,86 @@
+"""Persistent weight-streaming GEMM (ns_stream_gemm) vs the unfused oracle ops: F.linear in fp32 on the same bf16
+values rounded to bf16, then the token-wise op of the oracle. Tolerance: the GEMM sums K products in another order than
+the CPU, so the bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values
+(BASELINE's bf16 bound for fused ops), and >= 97 % of the elements bitwise equal. The residual stream is bit-exact."""
+import pytest
+import torch
+
+from oracle import ops as O
+from tests.test_skinny_gemm_gpu import close, lin
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(896, 896), (9728, 896), (48, 1024), (2368, 896)])
+def test_plain_gemm_with_and_without_bias(M, N, K):
+    from nanoserve_b200.kernels.fused import stream_gemm, stream_gemm_errors
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.03).to(torch.bfloat16)
+    b = torch.randn(N, generator=g).to(torch.bfloat16)
+    close(stream_gemm(x.cuda(), w.cuda()), lin(x, w))
+    close(stream_gemm(x.cuda(), w.cuda(), b.cuda()), lin(x, w, b))
+    assert stream_gemm_errors() == 0
+
+
+@pytest.mark.parametrize("M,H,I", [(1, 896, 4864), (5, 896, 4864), (32, 896, 4864), (64, 896, 4864), (48, 1024, 512),
+                                   (32, 1536, 8960), (9, 1536, 8960)])
+def test_norm_prologue_and_silu_epilogue(M, H, I):
+    from nanoserve_b200.kernels.fused import EPI_SILU_MUL, stream_gemm, stream_gemm_errors
+    g = torch.Generator().manual_seed(M + H)
+    a = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    ln = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    out, r = stream_gemm(a.cuda(), w.cuda(), ln_w=ln.cuda(), residual=res.cuda(), want_residual=True, epilogue=EPI_SILU_MUL)
+    h, r_ref = O.add_rms_norm(a, ln, 1e-6, res)
+    assert torch.equal(r.cpu(), r_ref)
+    close(out, O.silu_mul(lin(h, w)), min_same=0.97)
+    out2 = stream_gemm(a.cuda(), w.cuda(), ln_w=ln.cuda(), epilogue=EPI_SILU_MUL)          # norm without a residual
+    close(out2, O.silu_mul(lin(O.rms_norm(a, ln, 1e-6), w)), min_same=0.97)
+    out3 = stream_gemm(h.cuda(), w.cuda(), epilogue=EPI_SILU_MUL)                          # no prologue
+    close(out3, O.silu_mul(lin(h, w)), min_same=0.97)
+    assert stream_gemm_errors() == 0
+
+
+def test_repeated_launches_are_deterministic_and_unsupported_shapes_fail_loudly():
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.fused import EPI_SILU_MUL, stream_gemm, stream_gemm_supported
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(32, 896, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(9728, 896, generator=g) * 0.03).to(torch.bfloat16).cuda()
+    first = stream_gemm(x, w, epilogue=EPI_SILU_MUL)
+    for _ in range(20):
+        assert torch.equal(stream_gemm(x, w, epilogue=EPI_SILU_MUL), first)
+    assert not stream_gemm_supported(32, 896, 3584) and not stream_gemm_supported(64, 896, 1536)
+    with pytest.raises(_lib.NanoserveB200Error):
+        stream_gemm(torch.zeros(8, 3584, dtype=torch.bfloat16, device="cuda"),
+                    torch.zeros(64, 3584, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(_lib.NanoserveB200Error):
+        stream_gemm(torch.zeros(64, 1536, dtype=torch.bfloat16, device="cuda"),
+                    torch.zeros(64, 1536, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 32, 64])
+def test_residual_epilogue_hands_its_sum_of_squares_to_the_next_prologue(M):
+    """o_proj with the residual add in its epilogue, then gate/up whose RMSNorm takes mean(r^2) from the partial sums
+    the first GEMM left: together they equal o_proj, add + rms_norm, gate/up, silu_mul of the unfused path."""
+    from nanoserve_b200.kernels.fused import EPI_RESIDUAL, EPI_SILU_MUL, stream_gemm, stream_gemm_errors
+    g = torch.Generator().manual_seed(77 + M)
+    H, I = 896, 4864
+    o = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    wo = (torch.randn(H, H, generator=g) * 0.03).to(torch.bfloat16)
+    ln = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    wgu = (torch.randn(2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    r, ss = stream_gemm(o.cuda(), wo.cuda(), epilogue=EPI_RESIDUAL, add_in=x.cuda(), want_ss=True)
+    a_ref = lin(o, wo)
+    h_ref, r_ref = O.add_rms_norm(a_ref, ln, 1e-6, x)
+    close(r, r_ref, min_same=0.97)
+    # the partial sums are those of the r this kernel wrote
+    want_ss = r.float().view(M, H // 16, 16).pow(2).sum(-1)
+    assert ss.shape == (M, H // 16) and torch.allclose(ss, want_ss, rtol=1e-5, atol=1e-6)
+    m = stream_gemm(r, wgu.cuda(), ln_w=ln.cuda(), ss_in=ss, epilogue=EPI_SILU_MUL)
+    close(m, O.silu_mul(lin(O.rms_norm(r.cpu(), ln, 1e-6), wgu)), min_same=0.97)
+    assert stream_gemm_errors() == 0
