@@ -82,16 +82,12 @@ int ns_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cac
  *   and sum rounded to bf16), writes q to out [M, n_heads*64] and k / v into one layer's paged pool at slots[m].
  * split_k (1, 2, 4, 8) spreads K over a thread-block cluster whose partial tiles are summed through distributed
  * shared memory in a fixed order. K must be a multiple of 16*split_k.
- * prefetch / prefetch_bytes (may be NULL / 0): a byte range, 16-byte aligned and a multiple of 16 long, that the
- * kernels AFTER this one will read (the weights of the layer's later GEMMs); the grid issues L2 prefetches for it
- * before it waits for its own inputs.
  * Replaces, fused: nanoserve/model.py:231 (rms_norm + merged QKV F.linear + rope_qkv), :256 (o_proj), :256-257
  * (add + rms_norm + gate/up F.linear + silu_mul) and :257 (down_proj) for steps of at most 64 token rows. */
 int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const void* w,
                    const void* bias, void* out, int32_t M, int32_t N, int32_t K, int32_t split_k, float eps,
                    int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache, void* v_cache,
-                   const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, const void* prefetch,
-                   int64_t prefetch_bytes, void* stream);
+                   const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream);
 
 /* Persistent weight-streaming GEMM for decode-sized batches (bf16 only):
  *   out = epilogue( prologue(x) . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, N % 16 == 0,

@@ -48,8 +48,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     constexpr int STAGE_PARTS = 16;                   // partials whose (m, l) are staged at once
     extern __shared__ __align__(128) uint8_t smem[];
 
+    // This kernel may be scheduled while the kernel that produces Q and this step's K/V rows (the QKV projection with
+    // its RoPE + KV-write epilogue) is still running. Until pdl_wait() below it touches only what earlier steps and
+    // the step's plan left behind: the plan records, the block tables and the K/V rows of OLDER tokens.
     pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
-    pdl_wait();
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
@@ -116,7 +118,15 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     const int cp_row0 = lane / CPR, cp_ch = lane % CPR;
     constexpr int ROWS_PER_IT = 32 / CPR;
 
-    auto issue = [&](int t) {
+    // Tiles issued before pdl_wait(): the row of the step's new token (always the last of its block) is left out and
+    // fetched afterwards; which tile, which row and where from is remembered here.
+    int early_valid[STAGES - 1];
+    int64_t early_base[STAGES - 1];
+#pragma unroll
+    for (int t = 0; t < STAGES - 1; ++t) early_valid[t] = 0;
+    int early_q_i = -1, early_q_row = 0;
+
+    auto issue = [&](int t, bool early) {
         const int u = u0 + stripe + wph * t;
         if (u < u1) {
             bool moved = false;
@@ -136,13 +146,28 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 pf_bids = (pf_lo + jj < pf_hi) ? pf_table[jj] : 0;
             }
             if (qn_row != pf_i) {             // first tile of a row: start loading its Q now
-                qn_row = pf_i;
-                load_q(qn, pf_info.w);
+                if (early) {
+                    early_q_i = pf_i;         // Q is not there yet: loaded right after pdl_wait()
+                    early_q_row = pf_info.w;
+                } else {
+                    qn_row = pf_i;
+                    load_q(qn, pf_info.w);
+                }
             }
             const int j = u - pf_lo;
             const int blk = __shfl_sync(0xffffffffu, pf_bids, t - pf_bt);
-            const int valid = min(16, pf_info.y - 16 * j);
+            int valid = min(16, pf_info.y - 16 * j);
             const int64_t base = (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride + cp_ch * 8;
+            int skip_row = -1;
+            if (early && pf_info.y - 16 * j <= 16) {      // the row's last block: its last token is this step's
+                skip_row = valid - 1;
+#pragma unroll
+                for (int e = 0; e < STAGES - 1; ++e)
+                    if (e == t) {
+                        early_valid[e] = valid;
+                        early_base[e] = (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride;
+                    }
+            }
             const uint32_t ks = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES), vs = ks + KV_TILE;
 #pragma unroll
             for (int it = 0; it < 16 / ROWS_PER_IT; ++it) {
@@ -150,8 +175,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 const int nbytes = row < valid ? 16 : 0;
                 const int64_t goff = base + (int64_t)row * p.pos_stride;
                 const uint32_t so = tile_off<HD>(row, cp_ch);
-                cp_async16(ks + so, p.k_pool + goff, nbytes);
-                cp_async16(vs + so, p.v_pool + goff, nbytes);
+                if (row != skip_row) {
+                    cp_async16(ks + so, p.k_pool + goff, nbytes);
+                    cp_async16(vs + so, p.v_pool + goff, nbytes);
+                }
             }
         }
         cp_async_commit();
@@ -236,7 +263,35 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     // ---- pipeline ---------------------------------------------------------------------------------------------------
     const int my_tiles = (u1 - u0 - stripe + wph - 1) / wph;      // may be <= 0
 #pragma unroll
-    for (int t = 0; t < STAGES - 1; ++t) issue(t);
+    for (int t = 0; t < STAGES - 1; ++t) issue(t, true);
+    pdl_wait();                               // Q and the new token's K/V row exist from here on
+    if (early_q_i >= 0) {
+        qn_row = early_q_i;
+        load_q(qn, early_q_row);
+    }
+    {
+        bool patched = false;
+#pragma unroll
+        for (int t = 0; t < STAGES - 1; ++t) {
+            if (early_valid[t] > 0) {
+                patched = true;
+                const int row = early_valid[t] - 1;
+                if (lane < 2 * CPR) {
+                    const int ch = lane % CPR;
+                    const bool is_v = lane >= CPR;
+                    const uint32_t dst = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES) + (is_v ? KV_TILE : 0) +
+                                         tile_off<HD>(row, ch);
+                    const int64_t goff = early_base[t] + ch * 8 + (int64_t)row * p.pos_stride;
+                    cp_async16(dst, (is_v ? p.v_pool : p.k_pool) + goff, 16);
+                }
+            }
+        }
+        if (patched) {                        // rare past a row's first step range: one extra group, drained here
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+        }
+    }
 
     for (int t = 0; t < my_tiles; ++t) {
         cp_async_wait<STAGES - 2>();          // tile t has landed (one commit group per tile, empty or not)
@@ -260,7 +315,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 load_q(qa, cc_qrow);          // the prefetch cursor is already rows ahead (very short rows)
             }
         }
-        issue(t + STAGES - 1);                // refills the stage computed in iteration t-1
+        issue(t + STAGES - 1, false);         // refills the stage computed in iteration t-1
         const uint32_t ks = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES), vs = ks + KV_TILE;
         const int valid = min(16, cc_len - 16 * (u - cc_lo));
 

@@ -16,9 +16,10 @@ namespace ns {
 constexpr int kMaxDecodeCtas = 1024;      // upper bound on the persistent decode grid
 constexpr int kMaxKvHeads = 8;            // counters per decode row
 constexpr int kPrefillTileTokens = 16;    // query tokens per prefill work item
-constexpr int kMinBlocksPerCta = 8;       // a decode CTA's range is never cut below this many 16-token blocks. Measured at
-                                          // 32 rows x ~500 tokens: 13.1 us with 32 (one CTA per row, each warp walks 8
-                                          // blocks in turn), 10.7 us with 8 (127 CTAs; streaming ends at 2.3 us instead of 6)
+constexpr int kMinBlocksPerCta = 32;      // a decode CTA's range is never cut below this many 16-token blocks: splitting
+                                          // a row costs a partial write, a fence, an atomic and a cross-CTA reduce. Timed
+                                          // alone, 32 rows x ~500 tokens run faster with 8 (10.7 vs 13.1 us), but inside a
+                                          // layer, where the kernel's start overlaps the QKV GEMM, 32 wins (7.3 vs 9.5 us)
 constexpr int kSnapBlocks = 32;           // ranges up to twice this long may move a cut by half a range to reach a row
                                           // boundary (a whole row needs no partials); longer ranges by an eighth
 

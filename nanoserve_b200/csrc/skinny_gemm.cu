@@ -42,8 +42,6 @@ struct GemmParams {
     int inter;                       // kEpiSiluMul: columns of gate (= rows of W / 2)
     int n_heads, n_kv_heads;         // kEpiRopeKv
     float eps;
-    const uint8_t* prefetch;         // bytes the kernels AFTER this one will stream (their weights): pulled into L2 now
-    int64_t prefetch_bytes;          // 0 = none; a multiple of 16
 };
 
 // ---- TMA bulk copy (1-D, no tensor map) completing on an mbarrier; every wait is bounded -----------------------
@@ -94,6 +92,9 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     float* c_sm = reinterpret_cast<float*>(w_sm + (size_t)kBN * a_stride);          // [MP][64] fp32
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // QKV only: the attention kernel that follows fetches its plan, block ids and older K/V rows while this GEMM runs.
+    // (Not for the other epilogues: a successor that starts streaming ITS weights now would compete with this kernel's.)
+    if (EPI == kEpiRopeKv) pdl_launch_dependents();
 
     // weight row of the CTA's local row t
     auto w_row = [&](int t) -> int {
@@ -127,18 +128,6 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
                 for (uint32_t c = 0; c < row_bytes; c += 16)
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(my_w + lane * a_stride + c), "r"(0) : "memory");
             }
-        }
-    }
-    if (p.prefetch_bytes > 0 && tid == 32) {
-        // L2 prefetch of what the next kernels will read, spread over the grid: by the time they run (this GEMM and
-        // the attention kernel later) their weights come from L2 instead of HBM. Fire and forget: no barrier, no wait.
-        const int64_t ncta = (int64_t)gridDim.x * gridDim.y, me = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
-        const int64_t share = ((p.prefetch_bytes + ncta - 1) / ncta + 15) & ~(int64_t)15;
-        int64_t off = me * share;
-        const int64_t end = off + share < p.prefetch_bytes ? off + share : p.prefetch_bytes;
-        for (; off < end; off += 32768) {
-            const uint32_t n = (uint32_t)(end - off < 32768 ? end - off : 32768);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(n) : "memory");
         }
     }
     pdl_wait();        // everything above touched only weights; the activations come from the preceding kernel
@@ -346,8 +335,7 @@ using namespace ns;
 extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* residual_out, const void* w,
                               const void* bias, void* out, int32_t M, int32_t N, int32_t K, int32_t split_k, float eps,
                               int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache,
-                              void* v_cache, const int64_t* slots, int32_t n_heads, int32_t n_kv_heads,
-                              const void* prefetch, int64_t prefetch_bytes, void* stream) {
+                              void* v_cache, const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream) {
     NS_REQUIRE(M >= 0 && N > 0 && K > 0, NS_ERR_INVALID_ARG, "skinny_gemm: bad shape");
     if (M == 0) return NS_OK;
     NS_REQUIRE(x && w && out, NS_ERR_INVALID_ARG, "skinny_gemm: null pointer");
@@ -364,10 +352,6 @@ extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* l
     p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache; p.slots = slots;
     p.M = M; p.N = N; p.K = K; p.k_slice = K / split_k; p.inter = inter; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
     p.eps = eps;
-    NS_REQUIRE(prefetch_bytes >= 0 && prefetch_bytes % 16 == 0 && (prefetch_bytes == 0 || prefetch != nullptr) &&
-                   (reinterpret_cast<uintptr_t>(prefetch) & 15) == 0,
-               NS_ERR_INVALID_ARG, "skinny_gemm: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
-    p.prefetch = (const uint8_t*)prefetch; p.prefetch_bytes = prefetch_bytes;
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const size_t a_bytes = (size_t)(mp + kBN) * (p.k_slice * 2 + 16);
     NS_REQUIRE(a_bytes + (size_t)mp * kBN * 4 + 128 <= 220 * 1024 && p.k_slice <= 1024, NS_ERR_UNSUPPORTED,

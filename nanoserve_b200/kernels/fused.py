@@ -109,10 +109,9 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
                 want_residual: bool = False, epilogue: int = EPI_BIAS, cos: torch.Tensor | None = None,
                 sin: torch.Tensor | None = None, k_cache: torch.Tensor | None = None,
                 v_cache: torch.Tensor | None = None, slots: torch.Tensor | None = None, n_heads: int = 0,
-                n_kv_heads: int = 0, prefetch: tuple[int, int] | None = None):
+                n_kv_heads: int = 0):
     """Decode-sized GEMM x[M<=64, K] @ w[N, K]^T with fused prologue / epilogue (see ns_skinny_gemm in the header).
-    Returns `out`, or `(out, r)` when want_residual is set (r = residual + x, the new residual stream).
-    prefetch = (device address, bytes) of what the following kernels will stream (pulled into L2 by this launch)."""
+    Returns `out`, or `(out, r)` when want_residual is set (r = residual + x, the new residual stream)."""
     _lib.require_cuda(x, w, bias, ln_w, residual, cos, sin, k_cache, v_cache, slots)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -129,8 +128,7 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     r_out = torch.empty_like(x) if (want_residual and ln_w is not None and residual is not None) else None
     _lib.call("ns_skinny_gemm", x.data_ptr(), _lib.ptr(residual), _lib.ptr(ln_w), _lib.ptr(r_out), w.data_ptr(),
               _lib.ptr(bias), out.data_ptr(), M, N, K, split_k, float(eps), epilogue, inter, _lib.ptr(cos), _lib.ptr(sin),
-              _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slots), n_heads, n_kv_heads,
-              prefetch[0] if prefetch else None, prefetch[1] if prefetch else 0, _lib.stream_ptr())
+              _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slots), n_heads, n_kv_heads, _lib.stream_ptr())
     return (out, r_out) if want_residual else out
 
 

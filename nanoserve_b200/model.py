@@ -78,7 +78,6 @@ class LayerWeights:
     qkv_w: torch.Tensor | None = None       # merged [q; k; v] rows (one GEMM); the fields above become views
     qkv_b: torch.Tensor | None = None
     gate_up_w: torch.Tensor | None = None   # merged [gate; up] rows
-    after_qkv: tuple | None = None          # (device address, bytes) of the weights the layer streams after its QKV GEMM
 
     HF_NAMES = _HF_LAYER_NAMES
 
@@ -176,47 +175,9 @@ class Qwen2Model:
         """The same weights (merged in place, per-matrix names become views) behind the fused-kernel path."""
         for layer in self.layers:
             layer.merge()
-        self._pack_gemm_weights()
         m = copy.copy(self)
         m.fused = True
         return m
-
-    def _pack_gemm_weights(self) -> None:
-        """Move every layer's GEMM weights into ONE buffer in execution order (qkv, o, gate/up, down, next layer's
-        qkv, ...), each matrix 256-byte aligned, and re-point the layer fields at views of it. A decode-sized step
-        then knows the byte range the rest of a layer will stream (`layer.after_qkv`: o_proj .. the next layer's
-        qkv) and has the layer's first kernel pull it into L2 ahead of time."""
-        if getattr(self, "_packed", None) is not None or self.dtype != torch.bfloat16:
-            return
-        names = ("qkv_w", "o_w", "gate_up_w", "down_w")
-        esz = self.embed.element_size()
-        align = 256 // esz
-        total, offs = 0, []
-        for layer in self.layers:
-            for n in names:
-                offs.append(total)
-                total += -(-getattr(layer, n).numel() // align) * align
-        flat = torch.empty(total, dtype=self.dtype, device=self.device)
-        it = iter(offs)
-        for layer in self.layers:
-            for n in names:
-                w = getattr(layer, n)
-                o = next(it)
-                view = flat[o:o + w.numel()].view(w.shape)
-                view.copy_(w)
-                setattr(layer, n, view)
-            nq, nk, ng = layer.q_w.shape[0], layer.k_w.shape[0], layer.gate_w.shape[0]
-            layer.q_w, layer.k_w, layer.v_w = layer.qkv_w[:nq], layer.qkv_w[nq:nq + nk], layer.qkv_w[nq + nk:]
-            layer.gate_w, layer.up_w = layer.gate_up_w[:ng], layer.gate_up_w[ng:]
-        self._packed = flat
-        for i, layer in enumerate(self.layers):
-            start = layer.o_w.data_ptr()
-            if i + 1 < len(self.layers):
-                nxt = self.layers[i + 1].qkv_w
-                end = nxt.data_ptr() + nxt.numel() * esz
-            else:
-                end = layer.down_w.data_ptr() + layer.down_w.numel() * esz
-            layer.after_qkv = (start, (end - start) // 16 * 16)
 
     def named_weights(self) -> dict[str, torch.Tensor]:
         out = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.norm}
@@ -389,7 +350,6 @@ class Qwen2Model:
         skinny_o = skinny and (nh * hd) % 128 == 0 and bool(mask & 4)
         # gate/up (+SiLU*mul) and o_proj through the persistent weight-streaming kernel: its weights are in flight while
         # the norm / attention kernel before it still runs
-        l2_prefetch = bool(mask & 32) and getattr(self.layers[0], "after_qkv", None) is not None
         stream_gu = skinny and bool(mask & 8) and stream_gemm_supported(T, 2 * inter, hidden)
         stream_o = skinny and bool(mask & 16) and stream_gemm_supported(T, hidden, nh * hd)
         if plan:
@@ -401,8 +361,7 @@ class Qwen2Model:
         for i, layer in enumerate(self.layers):
             if skinny_qkv:
                 q = skinny_gemm(h, layer.qkv_w, layer.qkv_b, split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin,
-                                k_cache=paged.k[i], v_cache=paged.v[i], slots=meta.slot_mapping, n_heads=nh, n_kv_heads=nkv,
-                                prefetch=layer.after_qkv if l2_prefetch else None)
+                                k_cache=paged.k[i], v_cache=paged.v[i], slots=meta.slot_mapping, n_heads=nh, n_kv_heads=nkv)
             else:
                 qkv = F.linear(h, layer.qkv_w, layer.qkv_b)
                 q, _, _ = rope_qkv(qkv, cos, sin, nh, nkv, hd, paged.k[i], paged.v[i], meta.slot_mapping, dense_kv=False)
