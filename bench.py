@@ -366,6 +366,97 @@ def launch_probe() -> None:
     print(json.dumps({"probe_steps": kinds, "engine": {k: eng.stats[k] for k in ("graph_steps", "piecewise_steps", "steps")}}))
 
 
+def layer_probe(rows: int) -> None:
+    """Marginal cost of each kernel of one decode layer INSIDE the layer chain: 24 layers of the engine's kernel sequence
+    for `rows` one-token sequences (contexts U[400,600], Qwen2.5-0.5B shape, distinct weights per layer) captured in one
+    CUDA graph and timed with CUDA events; each variant removes or swaps one kernel. Prints one JSON object (us per
+    layer). Also sweeps the planner's lower bound on a decode CTA's range through a debug hook of the library."""
+    import ctypes
+    import torch.nn.functional as F
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
+                                              stream_gemm)
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
+    W = [dict(qkv=torch.randn(1152, H, device=dev, dtype=bf) * .02, b=torch.randn(1152, device=dev, dtype=bf) * .02,
+              o=torch.randn(H, H, device=dev, dtype=bf) * .02, gu=torch.randn(2 * I, H, device=dev, dtype=bf) * .02,
+              down=torch.randn(H, I, device=dev, dtype=bf) * .02, ln=torch.ones(H, device=dev, dtype=bf)) for _ in range(L)]
+    w = attention_workload(n_decode=M, decode_range=(400, 600), n_prefill=0, num_blocks=4096)
+    ws = AttnWorkspace(64, 64, 14, 64, dev)
+    ws.plan(w.seq_lens, None, M, 16)
+    inv = (1.0 / (1e6 ** (torch.arange(0, 64, 2, dtype=torch.float) / 64))).to(dev)
+    cos, sin = rope_cos_sin(torch.arange(M, device=dev), inv, 64, bf)
+    x0 = torch.randn(M, H, device=dev, dtype=bf)
+    m0 = torch.randn(M, I, device=dev, dtype=bf)
+    q0 = torch.randn(M, 14, 64, device=dev, dtype=bf)
+
+    def chain(qkv="skinny", attn=True, o="cublas", norm1=True, gu="cublas", down="skinny", norm2=True):
+        x = h = x0
+        for l in W:
+            q = q0
+            if qkv == "skinny":
+                q = skinny_gemm(h, l["qkv"], l["b"], split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=w.k_pool,
+                                v_cache=w.v_pool, slots=w.slot_mapping, n_heads=14, n_kv_heads=2)
+            if attn:
+                q = ragged_paged_attention(q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, None, 0.125, workspace=ws,
+                                           planned=True)
+            o2 = q.view(M, H)
+            a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else o2)
+            if norm1:
+                h, x = rms_norm(a, l["ln"], 1e-6, residual=x)
+            else:
+                h = a
+            if gu == "cublas":
+                m = silu_mul(F.linear(h, l["gu"]))
+            else:
+                m = stream_gemm(h, l["gu"], epilogue=EPI_SILU_MUL) if gu == "stream" else m0
+            d = skinny_gemm(m, l["down"], split_k=8) if down == "skinny" else (F.linear(m, l["down"]) if down == "cublas" else h)
+            if norm2:
+                h, x = rms_norm(d, l["ln"], 1e-6, residual=x)
+            else:
+                h = d
+        return h
+
+    def us_per_layer(**kw) -> float:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain(**kw)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            chain(**kw)
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3 / L)
+        return round(sorted(ts)[2], 2)
+
+    variants = {"engine chain": {}, "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
+                "no qkv": dict(qkv=None), "no o_proj": dict(o=None), "no norm1": dict(norm1=False),
+                "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"),
+                "o_proj and gate_up on stream_gemm": dict(o="stream", gu="stream")}
+    out = {"rows": M, "us_per_layer": {k: us_per_layer(**kw) for k, kw in variants.items()}}
+    hook = _lib.load().ns_debug_min_blocks
+    hook.argtypes, hook.restype = [ctypes.c_int], None
+    sweep = {}
+    for mb in (32, 16, 8, 4):
+        hook(mb)
+        ws.plan(w.seq_lens, None, M, 16)
+        torch.cuda.synchronize()
+        sweep[str(mb)] = round(us_per_layer() - us_per_layer(attn=False), 2)
+    hook(0)
+    out["attention_us_per_layer_by_min_blocks_per_cta"] = sweep
+    print(json.dumps(out))
+
+
 def timed_pass(eng, reqs, concurrency) -> tuple[float, int]:
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -451,6 +542,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launch-probe", action="store_true",
                     help="short run for `ncu --profile-from-start off` launch lists: 2 decode steps at c=32 + 1 mixed step")
+    ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS",
+                    help="marginal cost of each kernel of one decode layer inside the layer chain, for ROWS sequences")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the decode-attention roofline leg (the small case used for ncu captures)")
     ap.add_argument("--workload", default="serve", choices=["serve", "sweep", "prefix", "tp"],
@@ -463,6 +556,8 @@ def main() -> None:
         extra_workload(args)
     elif args.launch_probe:
         launch_probe()
+    elif args.layer_probe:
+        layer_probe(args.layer_probe)
     elif args.roofline_only:
         torch.cuda.set_device(0)
         print(json.dumps({"roofline": decode_attention_roofline(torch.device("cuda", 0))}))
