@@ -23,7 +23,7 @@ from dataclasses import dataclass
 
 import torch
 
-from nanoserve_b200.cuda_graphs import BUCKETS, DecodeGraphRunner, PiecewiseGraphRunner, StepBuffers
+from nanoserve_b200.cuda_graphs import BUCKETS, DecodeGraphRunner, PiecewiseGraphRunner, StepBuffers, step_buckets
 from nanoserve_b200.kv_manager import PagedKVManager
 from nanoserve_b200.model import Qwen2Model
 from nanoserve_b200.scheduler import Scheduler, Sequence
@@ -101,7 +101,8 @@ class LLMEngine:
         if piecewise_graphs:
             self.piecewise_runner = PiecewiseGraphRunner(self.model, self.kv.pool, self._garbage_block,
                                                          max_tokens=step_tokens, buffers=self.buffers,
-                                                         max_seqs=seq_cap, max_seq_len=max_seq_len)
+                                                         buckets=step_buckets(step_tokens), max_seqs=seq_cap,
+                                                         max_seq_len=max_seq_len)
         self.sequences: dict[int, Sequence] = {}
         self.last_step: StepStats | None = None
         self._next_id = 0

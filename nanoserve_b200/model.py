@@ -344,7 +344,10 @@ class Qwen2Model:
         # QKV with the RoPE + KV-write epilogue (64-wide heads) and o_proj: narrow GEMMs whose weights can stream while
         # the preceding norm / attention kernel still runs (programmatic dependent launch)
         import os
-        mask = int(os.environ.get("NS_SKINNY_MASK", "3"))
+        # which GEMMs leave the library GEMM (bit 0 down_proj, 1 QKV, 2 o_proj on the skinny kernel; 3 gate/up, 4 o_proj on
+        # the persistent streaming kernel). Measured inside a decode layer: the streaming kernel pays off up to 16 rows
+        # (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64).
+        mask = int(os.environ.get("NS_SKINNY_MASK", "27" if T <= 16 else "3"))
         skinny_down = skinny_down and bool(mask & 1)
         skinny_qkv = skinny and hd == 64 and hidden % 128 == 0 and bool(mask & 2)
         skinny_o = skinny and (nh * hd) % 128 == 0 and bool(mask & 4)
