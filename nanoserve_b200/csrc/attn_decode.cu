@@ -39,7 +39,10 @@ template <int HD> __device__ __forceinline__ uint32_t tile_off(int row, int chun
 }
 
 
-template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM>
+// MAX_MODE = 2: the plan may ask every CTA to act as TWO virtual CTAs of NWARPS/2 warps, each with its own range
+// (header field `mode`). Small steps (one CTA per row or less) want all 16 warps on one row; large ones want twice as
+// many, shorter ranges. Which one is decided on the device, per step, by the plan kernel: the launch never changes.
+template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM, int MAX_MODE>
 __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(const AttnParams p) {
     constexpr int CPR = HD / 8;                       // 16-byte chunks per K/V row
     constexpr int KV_TILE = 16 * HD * 2;              // bytes of one K (or V) tile
@@ -54,15 +57,37 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
-    const int32_t* __restrict__ cta_first = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_first);
-    const int cta = blockIdx.x;
     const int32_t* __restrict__ cta_start = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_start);
-    // one 32-byte record holds the CTA's range and its first row's description: a single load before the block ids
-    const int4* __restrict__ rec = reinterpret_cast<const int4*>(p.ws + p.L.cta_rec) + 2 * cta;
-    const int4 rec_a = rec[0], rec_b = rec[1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int HALF_WARPS = NWARPS / 2;
+    // one 32-byte record holds a (virtual) CTA's range and its first row's description. The record index depends on the
+    // plan's mode, so both candidates are fetched together with the mode: still a single round trip.
+    const int4* __restrict__ rec_base = reinterpret_cast<const int4*>(p.ws + p.L.cta_rec);
+    const int4* rec1 = rec_base + 2 * (int)blockIdx.x;
+    const int4* rec2 = rec_base + 2 * (2 * (int)blockIdx.x + (MAX_MODE == 2 ? warp / HALF_WARPS : 0));
+    int4 rec_a = rec1[0], rec_b = rec1[1];
+    bool split = false;
+    if (MAX_MODE == 2) {
+        const int4 a2 = rec2[0], b2 = rec2[1];
+        split = hdr->mode == 2;
+        if (split) {
+            rec_a = a2;
+            rec_b = b2;
+        }
+    }
+    const int half = split ? warp / HALF_WARPS : 0;           // which virtual CTA of this physical one
+    const int vwarps = split ? HALF_WARPS : NWARPS;           // warps of a virtual CTA
+    const int lw = warp - half * vwarps;                      // warp index inside it
+    const int cta = split ? 2 * (int)blockIdx.x + half : (int)blockIdx.x;
     const int u0 = rec_a.x, u1 = rec_a.y, i_first = rec_a.z;
+
+    __shared__ int4 pend[2 * kMaxKvHeads][2];     // rows a virtual CTA holds only in part: {row, first unit, query row, -}
+    __shared__ int2 pend_span[2 * kMaxKvHeads][2];
+    __shared__ int pend_n[2 * kMaxKvHeads];
+    __shared__ int pend_last[2 * kMaxKvHeads][2];
+    if (threadIdx.x < 2 * kMaxKvHeads) pend_n[threadIdx.x] = 0;
+    __syncthreads();                              // the only CTA-wide barrier; everything below is per head group
     if (u0 >= u1) return;
-    (void)hdr; (void)cta_first;
 
     const int4* __restrict__ dec_info = reinterpret_cast<const int4*>(p.ws + p.L.dec_info);   // {seq, len, table row, q row}
     const int2* __restrict__ dec_span = reinterpret_cast<const int2*>(p.ws + p.L.dec_span);   // {first CTA, CTAs} per row
@@ -70,11 +95,12 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     int32_t* counters = reinterpret_cast<int32_t*>(p.ws + p.L.counters);
     float* partials = reinterpret_cast<float*>(p.ws + p.L.partials);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NKV = p.n_kv_heads;
-    const int g = warp % NKV;                 // KV head of this warp
-    const int stripe = warp / NKV;            // which share of the blocks
-    const int wph = NWARPS / NKV;             // warps per head
+    const int g = lw % NKV;                   // KV head of this warp
+    const int stripe = lw / NKV;              // which share of the blocks
+    const int wph = vwarps / NKV;             // warps per head
+    const int hg = half * NKV + g;            // head group inside the physical CTA: named barrier id, staging slot
+    const int wbase = half * vwarps;          // first physical warp of this virtual CTA
     const int GROUP = p.group;
     const int gt = stripe * 32 + lane;        // thread index inside the head group
     const int gthreads = wph * 32;
@@ -84,12 +110,6 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
     constexpr int ML_STRIDE = STAGE_PARTS * 16 + 16;  // floats per head group: (m, l) x 8 rows x parts, rowM[8], rowL[8]
     float* ml_stage = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);
-    __shared__ int4 pend[kMaxKvHeads][2];     // rows this CTA holds only in part: {row, first unit, query row, -}
-    __shared__ int2 pend_span[kMaxKvHeads][2];
-    __shared__ int pend_n[kMaxKvHeads];
-    __shared__ int pend_last[kMaxKvHeads][2];
-    if (threadIdx.x < kMaxKvHeads) pend_n[threadIdx.x] = 0;
-    __syncthreads();
     __shared__ int red_stage[NWARPS];         // which idle stage of each warp holds its (m, l, O) during a combine
     int my_red = STAGES - 1;
     auto red_of = [&](int w, int stage) -> float* {
@@ -210,7 +230,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
             mine[row8 * RED_ROW + HD] = m_run;
             mine[row8 * RED_ROW + HD + 1] = lsum;
         }
-        named_barrier(1 + g, gthreads);
+        named_barrier(hg, gthreads);
 
         const int i = cc_i, lo = cc_lo, hi = cc_hi;
         const bool complete = lo >= u0 && hi <= u1;
@@ -220,10 +240,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         for (int e = gt; e < GROUP * HD; e += gthreads) {
             const int r = e / HD, c = e - r * HD;
             float M = -INFINITY;
-            for (int w = 0; w < wph; ++w) M = fmaxf(M, red_of(g + NKV * w, red_stage[g + NKV * w])[r * RED_ROW + HD]);
+            for (int w = 0; w < wph; ++w) M = fmaxf(M, red_of(wbase + g + NKV * w, red_stage[wbase + g + NKV * w])[r * RED_ROW + HD]);
             float acc = 0.f, Ls = 0.f;
             for (int w = 0; w < wph; ++w) {
-                const float* rw = red_of(g + NKV * w, red_stage[g + NKV * w]) + r * RED_ROW;
+                const float* rw = red_of(wbase + g + NKV * w, red_stage[wbase + g + NKV * w]) + r * RED_ROW;
                 const float sc = fast_exp2(rw[HD] - M);
                 acc = fmaf(sc, rw[c], acc);
                 Ls = fmaf(sc, rw[HD + 1], Ls);
@@ -239,11 +259,11 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
             }
         }
         if (!complete && gt == 0) {           // cross-CTA work for this row is deferred to the end of the CTA
-            const int k = pend_n[g]++;
-            pend[g][k] = make_int4(i, lo, (int)qrow, 0);
-            pend_span[g][k] = cc_span;
+            const int k = pend_n[hg]++;
+            pend[hg][k] = make_int4(i, lo, (int)qrow, 0);
+            pend_span[hg][k] = cc_span;
         }
-        named_barrier(1 + g, gthreads);       // every warp's scratch has been consumed
+        named_barrier(hg, gthreads);       // every warp's scratch has been consumed
         m_run = -INFINITY;
         l_run = 0.f;
 #pragma unroll
@@ -391,21 +411,21 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     // The partials were stored by every thread of the group before the barrier that ends flush(); the leader's fence
     // publishes them (fences are cumulative over what the barrier ordered before it). Whoever completes a row's
     // arrival count combines it. Nobody waits.
-    const int n_pend = pend_n[g];
+    const int n_pend = pend_n[hg];
     if (n_pend > 0) {
         if (gt == 0) {
             __threadfence();
             for (int k = 0; k < n_pend; ++k)
-                pend_last[g][k] = atomicAdd(&counters[pend[g][k].x * kMaxKvHeads + g], 1) == pend_span[g][k].y - 1;
+                pend_last[hg][k] = atomicAdd(&counters[pend[hg][k].x * kMaxKvHeads + g], 1) == pend_span[hg][k].y - 1;
             __threadfence();
         }
-        named_barrier(1 + g, gthreads);
+        named_barrier(hg, gthreads);
         for (int k = 0; k < n_pend; ++k) {
-            if (!pend_last[g][k]) continue;
-            const int i = pend[g][k].x, lo = pend[g][k].y;
-            const int64_t qrow = pend[g][k].z;
-            const int c_first = pend_span[g][k].x, n_parts = pend_span[g][k].y, c_last = c_first + n_parts - 1;
-            float* st = ml_stage + (size_t)g * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
+            if (!pend_last[hg][k]) continue;
+            const int i = pend[hg][k].x, lo = pend[hg][k].y;
+            const int64_t qrow = pend[hg][k].z;
+            const int c_first = pend_span[hg][k].x, n_parts = pend_span[hg][k].y, c_last = c_first + n_parts - 1;
+            float* st = ml_stage + (size_t)hg * ML_STRIDE;       // [STAGE_PARTS][8][2] = (m -> weight, l)
             float* rowM = st + STAGE_PARTS * 16;                // [8]
             float* rowL = rowM + 8;                             // [8]
             const int first_cut = __ldcg(&cta_start[c_first]);
@@ -426,7 +446,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                     st[idx * 2] = mv;
                     st[idx * 2 + 1] = lv;
                 }
-                named_barrier(1 + g, gthreads);
+                named_barrier(hg, gthreads);
             };
             const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
             float myM = -INFINITY;                             // threads 0..7 of the group: row maxima
@@ -435,10 +455,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 stage_ml(base, cnt);
                 if (gt < 8)
                     for (int pt = 0; pt < cnt; ++pt) myM = fmaxf(myM, st[(pt * 8 + gt) * 2]);
-                if (!single) named_barrier(1 + g, gthreads);
+                if (!single) named_barrier(hg, gthreads);
             }
             if (gt < 8) rowM[gt] = myM;
-            named_barrier(1 + g, gthreads);
+            named_barrier(hg, gthreads);
             float myL = 0.f;
             auto to_weights = [&](int cnt, bool add_l) {       // m -> exp2(m - rowM) in place
                 for (int idx = gt; idx < cnt * 8; idx += gthreads) {
@@ -446,7 +466,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                     const float mv = st[idx * 2];
                     st[idx * 2] = (r < GROUP && mv > -INFINITY) ? fast_exp2(mv - rowM[r]) : 0.f;
                 }
-                named_barrier(1 + g, gthreads);
+                named_barrier(hg, gthreads);
                 if (add_l && gt < 8)
                     for (int pt = 0; pt < cnt; ++pt) myL = fmaf(st[(pt * 8 + gt) * 2], st[(pt * 8 + gt) * 2 + 1], myL);
             };
@@ -475,11 +495,11 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                             acc.w = fmaf(wgt, v.w, acc.w);
                         }
                     }
-                    if (!single) named_barrier(1 + g, gthreads);
+                    if (!single) named_barrier(hg, gthreads);
                 }
                 if (kg == 0) {
                     if (gt < 8) rowL[gt] = myL;
-                    named_barrier(1 + g, gthreads);
+                    named_barrier(hg, gthreads);
                 }
                 if (mine) {
                     const float Ls = rowL[r];
@@ -491,25 +511,25 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 }
             }
             if (gt == 0) counters[i * kMaxKvHeads + g] = 0;
-            named_barrier(1 + g, gthreads);               // the staging area is reused by the next pending row
+            named_barrier(hg, gthreads);               // the staging area is reused by the next pending row
         }
     }
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4 + 3] = global_ns();
 }
 
-template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM>
+template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM, int MAX_MODE>
 static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
-    constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2) + kMaxKvHeads * (16 * 16 + 16) * 4;
+    constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2) + 2 * kMaxKvHeads * (16 * 16 + 16) * 4;
     static_assert(8 * (HD + 4) * 4 <= 2 * 16 * HD * 2, "the combine scratch must fit in one stage");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM>,
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "decode attention: cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
         configured = true;
     }
-    launch_pdl(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM>, dim3(sms * CTAS_PER_SM), dim3(NWARPS * 32), smem, st, p);
+    launch_pdl(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>, dim3(sms * CTAS_PER_SM), dim3(NWARPS * 32), smem, st, p);
     return check_launch("paged_decode");
 }
 
@@ -522,11 +542,14 @@ bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_
 }
 
 // Number of persistent decode CTAs for this head_dim on a device with `sms` SMs (the plan must be built for it).
-int decode_grid(int head_dim, int sms) { return head_dim == 64 ? 2 * sms : sms; }
+// Physical persistent decode CTAs for this head_dim on a device with `sms` SMs, and how many virtual CTAs each may
+// be split into (the plan must be built with the same two numbers).
+int decode_grid(int head_dim, int sms) { (void)head_dim; return sms; }
+int decode_max_mode(int head_dim) { return head_dim == 64 ? 2 : 1; }
 
 int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t st) {
-    if (head_dim == 64) return launch_decode_cfg<64, 8, 3, 2>(p, sms, st);
-    return launch_decode_cfg<128, 8, 3, 1>(p, sms, st);
+    if (head_dim == 64) return launch_decode_cfg<64, 16, 3, 1, 2>(p, sms, st);
+    return launch_decode_cfg<128, 8, 3, 1, 1>(p, sms, st);
 }
 
 }  // namespace ns

@@ -21,10 +21,12 @@
 namespace ns {
 
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
-                     int block_size, int decode_ctas, void* ws, const WsLayout& L, int max_items, cudaStream_t st);
+                     int block_size, int base_ctas, int max_mode, void* ws, const WsLayout& L, int max_items,
+                     cudaStream_t st);
 bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t st);
 int decode_grid(int head_dim, int sms);
+int decode_max_mode(int head_dim);
 
 constexpr int kStaticMaxBatch = 64;
 constexpr int kStaticMaxHeads = 32;
@@ -91,7 +93,8 @@ extern "C" int ns_paged_attn_decode_static(const void* q, const void* k_pool, co
     NS_REQUIRE(cudaGetDevice(&dev) == cudaSuccess &&
                    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0,
                NS_ERR_CUDA, "paged_attn_decode_static: cannot query the device");
-    const int ctas = decode_grid(head_dim, sms);
+    const int max_mode = decode_max_mode(head_dim);
+    const int ctas = decode_grid(head_dim, sms) * max_mode;          // virtual CTAs the scratch must hold
     NS_REQUIRE(ctas <= kStaticMaxCtas, NS_ERR_WORKSPACE, "paged_attn_decode_static: %d decode CTAs exceed the built-in scratch (%d)",
                ctas, kStaticMaxCtas);
     const WsLayout L = ws_layout(kStaticMaxBatch, kStaticMaxBatch, n_heads, head_dim, kStaticMaxCtas);
@@ -105,7 +108,7 @@ extern "C" int ns_paged_attn_decode_static(const void* q, const void* k_pool, co
     cudaError_t e = cudaMemsetAsync(ws + L.counters, 0, 4 * (size_t)kStaticMaxBatch * kMaxKvHeads, st);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "paged_attn_decode_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
     const int max_items = kStaticMaxBatch / kPrefillTileTokens + kStaticMaxBatch + 1;
-    rc = launch_attn_plan(context_lens, nullptr, nullptr, batch, block_size, ctas, ws, L, max_items, st);
+    rc = launch_attn_plan(context_lens, nullptr, nullptr, batch, block_size, ctas / max_mode, max_mode, ws, L, max_items, st);
     if (rc != NS_OK) return rc;
     AttnParams a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;

@@ -39,8 +39,9 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& 
 __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* __restrict__ seq_lens,
                                                                  const int32_t* __restrict__ cu_seqlens,
                                                                  const int32_t* __restrict__ table_rows, int n_seqs,
-                                                                 int block_size, int decode_ctas, uint8_t* ws,
-                                                                 WsLayout L, int max_items, int min_blocks) {
+                                                                 int block_size, int base_ctas, int max_mode,
+                                                                 int split_blocks, uint8_t* ws, WsLayout L, int max_items,
+                                                                 int min_blocks, int snap_blocks) {
     constexpr int kSmemRows = 2048;            // decode rows whose prefix is mirrored in shared memory
     __shared__ int warp_sums[33];
     __shared__ int indptr_sm[kSmemRows + 1];
@@ -98,10 +99,14 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     __syncthreads();
     const int* ip = n_dec <= kSmemRows ? indptr_sm : dec_indptr;
 
+    // Large steps run every decode CTA as two virtual CTAs of half the warps (twice as many, shorter ranges); small
+    // ones keep all warps of a CTA on one range. The decode kernel reads the choice from the header.
+    const int mode = (max_mode >= 2 && dec_blocks > split_blocks) ? 2 : 1;
+    const int decode_ctas = base_ctas * mode;
     int per = (dec_blocks + decode_ctas - 1) / decode_ctas;
     if (per < min_blocks) per = min_blocks;
     const int used = (dec_blocks + per - 1) / per;
-    const int slack = per <= 2 * kSnapBlocks ? per / 2 : per / 8;   // how far a cut may move to reach a row boundary
+    const int slack = per <= 2 * snap_blocks * (mode == 1 && max_mode >= 2 ? 2 : 1) ? per / 2 : per / 8;   // how far a cut may move to reach a row boundary
     int32_t* cta_start = reinterpret_cast<int32_t*>(ws + L.cta_start);
     int2* dec_span = reinterpret_cast<int2*>(ws + L.dec_span);
     __shared__ int cuts_sm[kMaxDecodeCtas + 1];
@@ -175,18 +180,22 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         hdr->n_prefill_items = n_items < max_items ? n_items : max_items;
         hdr->n_seqs = n_seqs;
         hdr->block_size = block_size;
-        hdr->reserved = 0;
+        hdr->mode = mode;
     }
 }
 
 static int g_min_blocks = kMinBlocksPerCta;
+static int g_split_blocks = kSplitBlocks;
+static int g_snap_blocks = kSnapBlocks;
+void debug_set_snap_blocks(int n) { g_snap_blocks = n > 0 ? n : kSnapBlocks; }
 void debug_set_min_blocks(int n) { g_min_blocks = n > 0 ? n : kMinBlocksPerCta; }
+void debug_set_split_blocks(int n) { g_split_blocks = n >= 0 ? n : kSplitBlocks; }
 
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
-                     int block_size, int decode_ctas,
+                     int block_size, int base_ctas, int max_mode,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
-    attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, decode_ctas,
-                                                 (uint8_t*)ws, L, max_items, g_min_blocks);
+    attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, base_ctas, max_mode,
+                                                 g_split_blocks, (uint8_t*)ws, L, max_items, g_min_blocks, g_snap_blocks);
     return check_launch("attn_plan");
 }
 

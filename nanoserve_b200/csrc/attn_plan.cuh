@@ -20,8 +20,12 @@ constexpr int kMinBlocksPerCta = 32;      // a decode CTA's range is never cut b
                                           // a row costs a partial write, a fence, an atomic and a cross-CTA reduce. Timed
                                           // alone, 32 rows x ~500 tokens run faster with 8 (10.7 vs 13.1 us), but inside a
                                           // layer, where the kernel's start overlaps the QKV GEMM, 32 wins (7.3 vs 9.5 us)
-constexpr int kSnapBlocks = 32;           // ranges up to twice this long may move a cut by half a range to reach a row
-                                          // boundary (a whole row needs no partials); longer ranges by an eighth
+constexpr int kSplitBlocks = 12800;       // steps with more decode KV blocks than this run two virtual CTAs per CTA.
+                                          // Measured (hd 64, 14q/2kv): up to ~12.4K blocks one 16-warp CTA per SM is as fast
+                                          // or faster (32 rows x 500 tokens: 7.3 vs 12.1 us; 128 rows x 1400: 18.0 vs 22.7);
+                                          // at 14.1K blocks (48 rows, U[128,8192]) two 8-warp halves win (27.6 vs 31.6 us)
+constexpr int kSnapBlocks = 32;           // ranges up to twice this long per 8 warps may move a cut by half a range to
+                                          // reach a row boundary (a whole row needs no partials); longer ranges by an eighth
 
 struct PlanHeader {
     int32_t n_dec;          // decode rows
@@ -31,7 +35,7 @@ struct PlanHeader {
     int32_t n_prefill_items;
     int32_t n_seqs;
     int32_t block_size;
-    int32_t reserved;
+    int32_t mode;           // 1: one range per decode CTA; 2: every decode CTA runs two virtual CTAs of half its warps
 };
 
 // Byte offsets inside the workspace; everything 256-byte aligned.

@@ -26,11 +26,12 @@ int check_launch(const char* what) {
 
 // attn_plan.cu / attn_decode.cu / attn_prefill_mma.cu
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
-                     int block_size, int decode_ctas,
+                     int block_size, int base_ctas, int max_mode,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st);
 bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_paged_decode(const AttnParams& p, int head_dim, int sms, cudaStream_t st);
 int decode_grid(int head_dim, int sms);
+int decode_max_mode(int head_dim);
 bool prefill_mma_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
@@ -53,7 +54,10 @@ static int sm_count() {
 
 using namespace ns;
 
-namespace ns { void debug_set_min_blocks(int n); }
+namespace ns { void debug_set_min_blocks(int n); void debug_set_split_blocks(int n); void debug_set_snap_blocks(int n); }
+extern "C" void ns_debug_snap_blocks(int n) { ns::debug_set_snap_blocks(n); }
+// Debug hook (not part of the public header): decode KV blocks above which a step runs two virtual CTAs per CTA (< 0 = default).
+extern "C" void ns_debug_split_blocks(int n) { ns::debug_set_split_blocks(n); }
 // Debug hook (not part of the public header): lower bound of a decode CTA's range in KV blocks (0 = default).
 extern "C" void ns_debug_min_blocks(int n) { ns::debug_set_min_blocks(n); }
 
@@ -80,10 +84,11 @@ static int plan_impl(const int32_t* seq_lens, const int32_t* cu_seqlens, const i
     NS_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255) == 0, NS_ERR_INVALID_ARG, "attn_plan: workspace not 256-byte aligned");
     const int sms = sm_count();
     NS_REQUIRE(sms > 0, NS_ERR_CUDA, "attn_plan: cannot query the SM count");
-    const int ctas = decode_grid(head_dim, sms);
-    NS_REQUIRE(ctas <= kMaxDecodeCtas, NS_ERR_UNSUPPORTED, "attn_plan: %d decode CTAs exceed the workspace layout", ctas);
+    const int ctas = decode_grid(head_dim, sms), max_mode = decode_max_mode(head_dim);
+    NS_REQUIRE(ctas * max_mode <= kMaxDecodeCtas, NS_ERR_UNSUPPORTED, "attn_plan: %d decode CTAs exceed the workspace layout",
+               ctas * max_mode);
     const int max_items = ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
-    return launch_attn_plan(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, ctas, ws, L, max_items, st);
+    return launch_attn_plan(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, ctas, max_mode, ws, L, max_items, st);
 }
 
 extern "C" int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows,
@@ -132,7 +137,8 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
                "ragged_paged_attn: out must be 8-byte aligned with a row stride that is a multiple of 4 elements");
     const float kLog2e = 1.4426950408889634f;
     const int sms = sm_count();
-    NS_REQUIRE(sms > 0 && decode_grid(head_dim, sms) <= kMaxDecodeCtas, NS_ERR_CUDA, "ragged_paged_attn: bad SM count");
+    NS_REQUIRE(sms > 0 && decode_grid(head_dim, sms) * decode_max_mode(head_dim) <= kMaxDecodeCtas, NS_ERR_CUDA,
+               "ragged_paged_attn: bad SM count");
 
     AttnParams a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
