@@ -227,6 +227,23 @@ def closed_loop(eng, reqs, concurrency: int) -> int:
     return tokens
 
 
+def init_nccl(device) -> None:
+    """Process group + first collective with file descriptor 1 pointed at stderr: NCCL announces its version on stdout
+    when its communicator comes up, and stdout carries exactly one JSON line."""
+    import torch.distributed as dist
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=device)
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def run_gpu_arm(args) -> None:
     import torch.distributed as dist
     from nanoserve_b200 import _lib
@@ -240,7 +257,7 @@ def run_gpu_arm(args) -> None:
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        init_nccl(device)
 
     def barrier():
         if world > 1:
@@ -485,7 +502,7 @@ def extra_workload(args) -> None:
         reqs = workload()
         for c in (1, 4, 8, 16, 32, 128, 256):
             eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=c, max_num_batched_tokens=2048,
-                            kv_cache_tokens=max(65536, c * 1280))
+                            kv_cache_tokens=max(65536, c * 1280), lookahead=not args.no_lookahead)
             eng.capture_graphs()
             timed_pass(eng, reqs, c)
             secs, n = min(timed_pass(eng, reqs, c) for _ in range(args.steps))
@@ -500,7 +517,7 @@ def extra_workload(args) -> None:
                                     seed=seed, shared_prefix=1024)
         for on in (False, True):
             eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY, max_num_batched_tokens=2048,
-                            prefix_caching=on)
+                            prefix_caching=on, lookahead=not args.no_lookahead)
             eng.capture_graphs()
             timed_pass(eng, fresh(3), CONCURRENCY)
             eng.reset_stats()
@@ -513,13 +530,13 @@ def extra_workload(args) -> None:
     else:
         from nanoserve_b200.tensor_parallel import random_tp_model
         if world > 1:
-            dist.init_process_group("nccl", device_id=device)
+            init_nccl(device)
         else:
             dist.init_process_group("gloo", rank=0, world_size=1, init_method="tcp://127.0.0.1:29533")
         model = random_tp_model("qwen2.5-7b", device=device)
         reqs = serving_requests(args.requests or 256, prompt_range=(256, 4096), output_range=(64, 512), vocab=152064, seed=4)
         eng = LLMEngine(model, eos_token_ids=[], max_seq_len=4608, max_num_seqs=64, max_num_batched_tokens=2048,
-                        kv_cache_tokens=64 * 4608)
+                        kv_cache_tokens=64 * 4608, lookahead=not args.no_lookahead)
         eng.capture_graphs()
         timed_pass(eng, reqs[:64], 64)
         secs, n = timed_pass(eng, reqs, 64)
