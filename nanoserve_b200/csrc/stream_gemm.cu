@@ -97,13 +97,15 @@ __device__ __forceinline__ uint32_t norm_pair(uint32_t v, float inv, uint32_t w)
 
 }  // namespace sg
 
-constexpr int kSgConsumerWarps = 8;
+constexpr int kSgConsumerWarps = 8;                  // mma warps: each owns K/8 columns
 constexpr int kSgConsumers = kSgConsumerWarps * 32;
-constexpr int kSgThreads = kSgConsumers + 32;        // + the producer warp
+constexpr int kSgEpiWarps = 4;                       // epilogue warps: sum the K-partials, apply the epilogue, store
+constexpr int kSgEpiThreads = kSgEpiWarps * 32;
+constexpr int kSgProducerWarp = kSgConsumerWarps + kSgEpiWarps;
+constexpr int kSgThreads = (kSgProducerWarp + 1) * 32;
+constexpr int kSgRedBufs = 3;                        // K-partial buffers in flight between mma and epilogue warps
 constexpr int kSgMaxStages = 8;
 constexpr int kSgUnitRows = 16;
-template <int MT> constexpr int kSgUnitsPerIter = 1;   // units of 16 weight rows per main-loop iteration (2 was measured
-                                                       // slower inside a decode layer: 37.5 vs 36.9 us at 32 rows)
 
 // MT: 16-row token tiles; KS: k-steps (of 16) per consumer warp, K = 128 * KS.
 template <int MT, int KS, int EPI>
@@ -115,7 +117,8 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
     constexpr int STAGE = kSgUnitRows * ROW;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kSgMaxStages], empty_bar[kSgMaxStages];
-    // [ring: stages x 16 weight rows][A staging MP rows, reused afterwards for the K-partials (2 x UPI x 8 x MP x 16 fp32)]
+    __shared__ __align__(8) uint64_t part_full[kSgRedBufs], part_empty[kSgRedBufs];
+    // [ring: stages x 16 weight rows][A staging MP rows, reused afterwards for the K-partials (kSgRedBufs x 8 x MP x 16 fp32)]
     uint8_t* ring = smem;
     uint8_t* a_sm = smem + (size_t)p.stages * STAGE;
     float* red = reinterpret_cast<float*>(a_sm);
@@ -136,6 +139,10 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
             sg::mbar_init(smem_u32(&full_bar[i]), 1);
             sg::mbar_init(smem_u32(&empty_bar[i]), kSgConsumerWarps);
         }
+        for (int i = 0; i < kSgRedBufs; ++i) {
+            sg::mbar_init(smem_u32(&part_full[i]), kSgConsumerWarps);
+            sg::mbar_init(smem_u32(&part_empty[i]), kSgEpiWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
         return unit * kSgUnitRows + r;
     };
 
-    if (warp == kSgConsumerWarps) {
+    if (warp == kSgProducerWarp) {
         // ---- producer: weights only, so it never waits for the preceding kernel ------------------------------
         auto fill = [&](int i) {
             const int slot = i % S;
@@ -172,6 +179,62 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
         return;
     }
 
+    if (warp >= kSgConsumerWarps) {
+        // ---- epilogue warps: unit j's eight K-partials sit in buffer j % kSgRedBufs once all mma warps have arrived ----
+        constexpr int MPc = 16 * MT;
+        const int et = tid - kSgConsumers;
+        for (int j = 0; j < n_my; ++j) {
+            const int b = j % kSgRedBufs;
+            if (!sg::mbar_wait_bounded(smem_u32(&part_full[b]), (uint32_t)((j / kSgRedBufs) & 1))) {
+                if (lane == 0) atomicAdd(&g_stream_gemm_errors, 1u);
+                return;
+            }
+            const int unit = (int)blockIdx.x + j * (int)gridDim.x;
+            const float* part = red + (size_t)b * kSgConsumerWarps * (MPc * 16);
+            if (EPI == kSgSiluMul) {
+                for (int e = et; e < p.M * 8; e += kSgEpiThreads) {
+                    const int m = e >> 3, c = e & 7;
+                    float g = 0.f, u = 0.f;
+#pragma unroll
+                    for (int w8 = 0; w8 < kSgConsumerWarps; ++w8) {
+                        g += part[w8 * (MPc * 16) + m * 16 + c];
+                        u += part[w8 * (MPc * 16) + m * 16 + 8 + c];
+                    }
+                    g = round_to<__nv_bfloat16>(g);
+                    u = round_to<__nv_bfloat16>(u);
+                    const float sg_ = round_to<__nv_bfloat16>(g / (1.0f + expf(-g)));
+                    p.out[(int64_t)m * p.inter + unit * 8 + c] = __float2bfloat16_rn(sg_ * u);
+                }
+            } else {
+                for (int e = et; e < MPc * 16; e += kSgEpiThreads) {     // whole half-warps share a row (shuffles below)
+                    const int m = e >> 4, c = e & 15;
+                    float v = 0.f;
+#pragma unroll
+                    for (int w8 = 0; w8 < kSgConsumerWarps; ++w8) v += part[w8 * (MPc * 16) + m * 16 + c];
+                    const int n = unit * 16 + c;
+                    if (p.bias) v += __bfloat162float(p.bias[n]);
+                    if (EPI == kSgResidual) {
+                        // r = bf16(residual + bf16(gemm)); the unit's share of sum(r^2) for the consumer's RMSNorm
+                        float r = 0.f;
+                        if (m < p.M) {
+                            r = round_to<__nv_bfloat16>(__fadd_rn(__bfloat162float(p.add_in[(int64_t)m * p.N + n]), round_to<__nv_bfloat16>(v)));
+                            p.out[(int64_t)m * p.N + n] = __float2bfloat16_rn(r);
+                        }
+                        float sq = r * r;
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        if (c == 0 && m < p.M && p.ss_out != nullptr) p.ss_out[(int64_t)m * p.units + unit] = sq;
+                    } else if (m < p.M) {
+                        p.out[(int64_t)m * p.N + n] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) sg::mbar_arrive(smem_u32(&part_empty[b]));      // this warp has read the buffer
+        }
+        return;
+    }
+
     // ---- consumers ---------------------------------------------------------------------------------------------
     // Warp w prepares token rows w, w + 8, ...; lane l owns the 16-byte chunks l, l + 32, ... of a row. Every x row
     // of the warp is fetched by 16-byte cp.async at once (one round trip); what the norm needs besides (residual
@@ -182,6 +245,26 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
     stamp();
     pdl_wait();                                         // activations come from the preceding kernel
     stamp();
+    uint32_t afrag[KS][MT][4];       // this warp's A fragments: columns [warp*KS*16, (warp+1)*KS*16) of every token row
+    if (p.ln_w == nullptr) {
+        // Plain activations: straight from global memory into the mma fragment registers (a0 = row r, cols c..c+1;
+        // a1 = row r+8; a2 = cols c+8..c+9; a3 = both), every load independent: one round trip, no staging, no barrier.
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int kcol = (warp * KS + ks) * 16 + c0;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int ra = 16 * mt + r0, rb = ra + 8;
+                const __nv_bfloat16* pa = p.x + (int64_t)ra * K + kcol;
+                const __nv_bfloat16* pb = p.x + (int64_t)rb * K + kcol;
+                afrag[ks][mt][0] = ra < p.M ? *reinterpret_cast<const uint32_t*>(pa) : 0u;
+                afrag[ks][mt][1] = rb < p.M ? *reinterpret_cast<const uint32_t*>(pb) : 0u;
+                afrag[ks][mt][2] = ra < p.M ? *reinterpret_cast<const uint32_t*>(pa + 8) : 0u;
+                afrag[ks][mt][3] = rb < p.M ? *reinterpret_cast<const uint32_t*>(pb + 8) : 0u;
+            }
+        }
+    } else {
 #pragma unroll
     for (int j = 0; j < RPW; ++j) {
         const int m = warp + kSgConsumerWarps * j;
@@ -197,9 +280,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
     }
     cp_async_commit();
     stamp();
-    if (p.ln_w == nullptr) {
-        cp_async_wait<0>();
-    } else {
+    {
         uint4 lnw[CH];
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
@@ -305,8 +386,6 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
     stamp();
     named_barrier(1, kSgConsumers);
     stamp();
-    // this warp's A fragments: columns [warp*KS*16, (warp+1)*KS*16) of every token row
-    uint32_t afrag[KS][MT][4];
     {
         const uint32_t a_base = smem_u32(a_sm);
 #pragma unroll
@@ -321,119 +400,54 @@ __global__ void __launch_bounds__(kSgThreads, 1) stream_gemm_kernel(const Stream
         }
     }
     named_barrier(1, kSgConsumers);                    // the staging area becomes the partial-sum buffers
+    }
     stamp();
 
-    // Main loop: UPI units per iteration. Unit j of this CTA sits in ring slot j % S.
-    constexpr int UPI = kSgUnitsPerIter<MT>;
+    // Main loop of the mma warps: unit j of this CTA sits in ring slot j % S; its K-partials go to buffer j % kSgRedBufs,
+    // handed to the epilogue warps through part_full / part_empty, so the mma warps never wait for an epilogue.
     bool ok = true;
-    for (int i = 0, it = 0; i < n_my; i += UPI, ++it) {
-        float acc[UPI][MT][2][4];
+    for (int j = 0; j < n_my; ++j) {
+        const int slot = j % S, b = j % kSgRedBufs;
+        float acc[MT][2][4];
 #pragma unroll
-        for (int q = 0; q < UPI; ++q)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) acc[q][mt][j][0] = acc[q][mt][j][1] = acc[q][mt][j][2] = acc[q][mt][j][3] = 0.f;
-#pragma unroll
-        for (int q = 0; q < UPI; ++q)
-            if (i + q < n_my && ok) ok = sg::mbar_wait_bounded(smem_u32(&full_bar[(i + q) % S]), (uint32_t)(((i + q) / S) & 1));
+            for (int q = 0; q < 2; ++q) acc[mt][q][0] = acc[mt][q][1] = acc[mt][q][2] = acc[mt][q][3] = 0.f;
+        if (ok) ok = sg::mbar_wait_bounded(smem_u32(&full_bar[slot]), (uint32_t)((j / S) & 1));
         stamp();
         if (ok) {
-            const int brow = (lane & 7) + ((lane >> 4) << 3);
-            uint32_t wb[UPI];
-            bool live[UPI];
-#pragma unroll
-            for (int q = 0; q < UPI; ++q) {
-                live[q] = i + q < n_my;
-                wb[q] = smem_u32(ring) + ((i + q) % S) * STAGE + brow * ROW + (warp * KS * 16 + (((lane >> 3) & 1) << 3)) * 2;
-            }
+            const uint32_t wb = smem_u32(ring) + slot * STAGE + ((lane & 7) + ((lane >> 4) << 3)) * ROW +
+                                (warp * KS * 16 + (((lane >> 3) & 1) << 3)) * 2;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
+                uint32_t b00, b01, b10, b11;
+                ldmatrix_x4(wb + ks * 32, b00, b01, b10, b11);
 #pragma unroll
-                for (int q = 0; q < UPI; ++q) {
-                    if (live[q]) {
-                        uint32_t b00, b01, b10, b11;
-                        ldmatrix_x4(wb[q] + ks * 32, b00, b01, b10, b11);
-#pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            mma_bf16_16816(acc[q][mt][0], afrag[ks][mt], b00, b01);
-                            mma_bf16_16816(acc[q][mt][1], afrag[ks][mt], b10, b11);
-                        }
-                    }
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16_16816(acc[mt][0], afrag[ks][mt], b00, b01);
+                    mma_bf16_16816(acc[mt][1], afrag[ks][mt], b10, b11);
                 }
             }
         } else if (lane == 0) {
             atomicAdd(&g_stream_gemm_errors, 1u);
         }
         __syncwarp();
-#pragma unroll
-        for (int q = 0; q < UPI; ++q)
-            if (i + q < n_my && lane == 0) sg::mbar_arrive(smem_u32(&empty_bar[(i + q) % S]));   // this warp is done with the stage
-        // K-partials: red[it & 1][q][warp][MP][16]
-        float* buf = red + (size_t)(it & 1) * UPI * kSgConsumerWarps * (MP * 16);
+        if (lane == 0) sg::mbar_arrive(smem_u32(&empty_bar[slot]));        // this warp is done with the stage
+        if (ok && j >= kSgRedBufs) ok = sg::mbar_wait_bounded(smem_u32(&part_empty[b]), (uint32_t)((j / kSgRedBufs - 1) & 1));
+        float* mine = red + ((size_t)b * kSgConsumerWarps + warp) * (MP * 16);
         {
             const int r0 = lane >> 2, cp = (lane & 3) * 2;
 #pragma unroll
-            for (int q = 0; q < UPI; ++q) {
-                float* mine = buf + ((size_t)q * kSgConsumerWarps + warp) * (MP * 16);
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        *reinterpret_cast<float2*>(mine + (16 * mt + r0) * 16 + 8 * j + cp) = make_float2(acc[q][mt][j][0], acc[q][mt][j][1]);
-                        *reinterpret_cast<float2*>(mine + (16 * mt + r0 + 8) * 16 + 8 * j + cp) = make_float2(acc[q][mt][j][2], acc[q][mt][j][3]);
-                    }
-            }
-        }
-        stamp();
-        named_barrier(1, kSgConsumers);
-        stamp();
-        // A buffer is written again two iterations later; every thread passes the next iteration's barrier in between,
-        // after its reads below, so one barrier per iteration is enough.
-#pragma unroll
-        for (int q = 0; q < UPI; ++q) {
-            if (i + q >= n_my) break;
-            const int unit = (int)blockIdx.x + (i + q) * (int)gridDim.x;
-            const float* part = buf + (size_t)q * kSgConsumerWarps * (MP * 16);
-            if (EPI == kSgSiluMul) {
-                for (int e = tid; e < p.M * 8; e += kSgConsumers) {
-                    const int m = e >> 3, c = e & 7;
-                    float g = 0.f, u = 0.f;
-#pragma unroll
-                    for (int w8 = 0; w8 < kSgConsumerWarps; ++w8) {
-                        g += part[w8 * (MP * 16) + m * 16 + c];
-                        u += part[w8 * (MP * 16) + m * 16 + 8 + c];
-                    }
-                    g = round_to<__nv_bfloat16>(g);
-                    u = round_to<__nv_bfloat16>(u);
-                    const float sg_ = round_to<__nv_bfloat16>(g / (1.0f + expf(-g)));
-                    p.out[(int64_t)m * p.inter + unit * 8 + c] = __float2bfloat16_rn(sg_ * u);
+                for (int q = 0; q < 2; ++q) {
+                    *reinterpret_cast<float2*>(mine + (16 * mt + r0) * 16 + 8 * q + cp) = make_float2(acc[mt][q][0], acc[mt][q][1]);
+                    *reinterpret_cast<float2*>(mine + (16 * mt + r0 + 8) * 16 + 8 * q + cp) = make_float2(acc[mt][q][2], acc[mt][q][3]);
                 }
-            } else {
-                for (int e = tid; e < MP * 16; e += kSgConsumers) {     // whole half-warps share a row (shuffles below)
-                    const int m = e >> 4, c = e & 15;
-                    float v = 0.f;
-#pragma unroll
-                    for (int w8 = 0; w8 < kSgConsumerWarps; ++w8) v += part[w8 * (MP * 16) + m * 16 + c];
-                    const int n = unit * 16 + c;
-                    if (p.bias) v += __bfloat162float(p.bias[n]);
-                    if (EPI == kSgResidual) {
-                        // r = bf16(residual + bf16(gemm)); the unit's share of sum(r^2) for the consumer's RMSNorm
-                        float r = 0.f;
-                        if (m < p.M) {
-                            r = round_to<__nv_bfloat16>(__fadd_rn(__bfloat162float(p.add_in[(int64_t)m * p.N + n]), round_to<__nv_bfloat16>(v)));
-                            p.out[(int64_t)m * p.N + n] = __float2bfloat16_rn(r);
-                        }
-                        float sq = r * r;
-#pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                        if (c == 0 && m < p.M && p.ss_out != nullptr) p.ss_out[(int64_t)m * p.units + unit] = sq;
-                    } else if (m < p.M) {
-                        p.out[(int64_t)m * p.N + n] = __float2bfloat16_rn(v);
-                    }
-                }
-            }
         }
+        __syncwarp();
+        if (lane == 0) sg::mbar_arrive(smem_u32(&part_full[b]));           // release: the stores above are visible to waiters
+        stamp();
     }
 }
 
@@ -441,7 +455,7 @@ template <int MT, int KS, int EPI>
 static int launch_stream(const StreamGemmParams& p0, cudaStream_t st) {
     StreamGemmParams p = p0;
     constexpr int MP = 16 * MT, K = 128 * KS, ROW = K * 2 + 16, STAGE = kSgUnitRows * ROW;
-    const size_t staging = (size_t)MP * ROW, red = (size_t)2 * kSgUnitsPerIter<MT> * kSgConsumerWarps * MP * 16 * 4;
+    const size_t staging = (size_t)MP * ROW, red = (size_t)kSgRedBufs * kSgConsumerWarps * MP * 16 * 4;
     const size_t fixed = staging > red ? staging : red;
     const size_t budget = 224 * 1024;
     int stages = (int)((budget - fixed) / STAGE);
