@@ -144,3 +144,35 @@ def test_strided_layer_pool_and_table_rows():
                                  table_rows=rows.cuda()).float().cpu()
     ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, 0.125)
     assert (out - ref).abs().max().item() <= 1e-2
+
+
+def test_decode_one_range_per_cta_and_two_virtual_ctas_agree():
+    """The plan kernel picks, per step, whether every 16-warp decode CTA works on one range or runs as two virtual
+    8-warp CTAs with a range each (steps above 12,800 KV blocks). Both paths are forced here through the library's
+    debug hook on a small ragged case (checked against the CPU oracle) and on BASELINE config 1's decode rows at full
+    size (checked against the scalar fp32-accumulating kernel of the same library): tolerance 1e-2 as above."""
+    import ctypes
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, paged_attention_decode, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    hook = _lib.load().ns_debug_split_blocks
+    hook.argtypes, hook.restype = [ctypes.c_int], None
+    lens_list = [8192, 3, 4097, 16, 1, 777, 2048, 33, 5000, 64, 129, 6001]
+    q, k, v, tables, lens, _ = make_case(14, 2, 64, lens_list, torch.bfloat16, seed=3)
+    ref = O.paged_attention_decode(q.float(), k.float(), v.float(), tables, lens, 0.125)
+    w = attention_workload(n_decode=48, n_prefill=0, num_blocks=16384, seed=5)
+    S = w.seq_lens.shape[0]
+    want = ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale, simple=True).float()
+    try:
+        for split_above in (1 << 30, 0):                 # one range per CTA; two virtual CTAs per CTA
+            hook(split_above)
+            ws = AttnWorkspace(64, 64, 14, 64)
+            for _ in range(2):                           # twice: the arrival counters must be back at zero
+                out = paged_attention_decode(*dev(q, k, v, tables, lens), 0.125, workspace=ws).float().cpu()
+                assert (out - ref).abs().max().item() <= 1e-2
+            ws2 = AttnWorkspace(64, 4096, 14, 64)
+            got = ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale,
+                                         n_seqs=S, workspace=ws2).float()
+            assert (got - want).abs().max().item() <= 1e-2
+    finally:
+        hook(-1)
