@@ -392,7 +392,7 @@ def layer_probe(rows: int) -> None:
     import torch.nn.functional as F
     from nanoserve_b200 import _lib
     from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
-                                              stream_gemm)
+                                              stream_gemm, swiglu_gemm)
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
     from nanoserve_b200.synthetic import attention_workload
     M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
@@ -426,6 +426,8 @@ def layer_probe(rows: int) -> None:
                 h = a
             if gu == "cublas":
                 m = silu_mul(F.linear(h, l["gu"]))
+            elif gu == "umma":
+                m = swiglu_gemm(h, l["gu"])
             else:
                 m = stream_gemm(h, l["gu"], epilogue=EPI_SILU_MUL) if gu == "stream" else m0
             d = skinny_gemm(m, l["down"], split_k=8) if down == "skinny" else (F.linear(m, l["down"]) if down == "cublas" else h)
@@ -458,7 +460,8 @@ def layer_probe(rows: int) -> None:
 
     variants = {"engine chain": {}, "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
                 "no qkv": dict(qkv=None), "no o_proj": dict(o=None), "no norm1": dict(norm1=False),
-                "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"),
+                "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": dict(gu="umma"),
+                "o_proj on stream_gemm, gate_up on swiglu_gemm": dict(o="stream", gu="umma"),
                 "o_proj and gate_up on stream_gemm": dict(o="stream", gu="stream")}
     out = {"rows": M, "us_per_layer": {k: us_per_layer(**kw) for k, kw in variants.items()}}
     hook = _lib.load().ns_debug_min_blocks

@@ -108,6 +108,18 @@ int ns_stream_gemm(const void* x, const void* residual, const void* ln_w, void* 
                    int32_t ss_parts, const void* w, const void* bias, void* out, const void* add_in, float* ss_out,
                    int32_t M, int32_t N, int32_t K, float eps, int32_t epilogue, void* stream);
 
+/* Decode-sized gate/up projection with SiLU(gate)*up on tcgen05 tensor cores, weights streamed by tiled TMA loads (bf16):
+ *   out[M <= 64, inter] = bf16( bf16(silu(bf16(x . Wg^T))) * bf16(x . Wu^T) ),  w_gate_up = [Wg; Wu]: [2*inter, K] row-major.
+ * K must be a multiple of 64; x: [M, K] contiguous. One CTA per SM owns a contiguous share of the gate rows and the
+ * matching up rows as (part of) the 128-row M operand of the UMMA tile (the token rows are the N operand) and
+ * accumulates in tensor memory.
+ * Replaces, fused: nanoserve/model.py:257 (gate/up F.linear + silu_mul) for steps of at most 64 token rows. */
+int ns_swiglu_gemm(const void* x, const void* w_gate_up, void* out, int32_t M, int32_t inter, int32_t K, void* stream);
+
+/* Number of bounded waits that ran out inside ns_swiglu_gemm kernels since the library was loaded (0 in a healthy run).
+ * Synchronises the device. No reference counterpart. */
+int ns_umma_gemm_errors(uint32_t* count);
+
 /* Number of bounded waits that ran out inside ns_stream_gemm kernels since the library was loaded (0 in a healthy
  * run; results of a launch that raised it are undefined). Synchronises the device. No reference counterpart. */
 int ns_stream_gemm_errors(uint32_t* count);

@@ -28,6 +28,8 @@ SIGNATURES: dict[str, tuple] = {
                                _I32, _P]),
     "ns_stream_gemm": (c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32, _I32, _I32, _F, _I32, _P]),
     "ns_stream_gemm_errors": (c_int, [_P]),
+    "ns_swiglu_gemm": (c_int, [_P, _P, _P, _I32, _I32, _I32, _P]),
+    "ns_umma_gemm_errors": (c_int, [_P]),
     "ns_attn_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "ns_attn_plan": (c_int, [_P, _P, _P, _I32, _I32, _I32, _I32, _P, _I64, _I32, _I32, _P]),
     "ns_ragged_paged_attn": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _I32, _I64, _I64,

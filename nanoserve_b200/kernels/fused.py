@@ -180,3 +180,38 @@ def stream_gemm_errors() -> int:
     n = ctypes.c_uint32(0)
     _lib.call("ns_stream_gemm_errors", ctypes.addressof(n))
     return int(n.value)
+
+
+def swiglu_gemm_supported(M: int, inter: int, K: int, sms: int = 148) -> bool:
+    """Shapes ns_swiglu_gemm takes: at most 64 token rows, K a multiple of 64, a per-SM share of the gate rows of at most
+    64, and the activations + two weight stages + the exchange buffer within shared memory."""
+    if not (0 < M <= 64 and K % 64 == 0 and inter >= 1):
+        return False
+    nt = 32 if M <= 32 else 64
+    g = min(sms, inter)
+    while -(-inter // g) > 64:
+        g += 1
+    region = (inter // g + (1 if inter % g else 0) + 7) // 8 * 8
+    stage = 2 * region * 128
+    return (K // 64) * nt * 128 + nt * 128 * 4 + 2 * stage + 16384 <= 223 * 1024
+
+
+def swiglu_gemm(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ Wg^T) * (x @ Wu^T) for x[M<=64, K] and the merged [gate; up] weight [2*inter, K] on the tcgen05 tensor
+    cores (ns_swiglu_gemm). Returns [M, inter]."""
+    _lib.require_cuda(x, w_gate_up)
+    assert x.dim() == 2 and w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1]
+    assert x.is_contiguous() and w_gate_up.is_contiguous() and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+    M, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    out = torch.empty(M, inter, device=x.device, dtype=x.dtype)
+    _lib.call("ns_swiglu_gemm", x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), M, inter, K, _lib.stream_ptr())
+    return out
+
+
+def umma_gemm_errors() -> int:
+    """Bounded waits that ran out inside swiglu_gemm kernels since the library was loaded (synchronises)."""
+    import ctypes
+    n = ctypes.c_uint32(0)
+    _lib.call("ns_umma_gemm_errors", ctypes.addressof(n))
+    return int(n.value)

@@ -329,7 +329,8 @@ class Qwen2Model:
         if not self.fused:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
         from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
-                                                  rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported)
+                                                  rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
+                                                  swiglu_gemm_supported)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
@@ -345,7 +346,7 @@ class Qwen2Model:
         # the preceding norm / attention kernel still runs (programmatic dependent launch)
         import os
         # which GEMMs leave the library GEMM (bit 0 down_proj, 1 QKV, 2 o_proj on the skinny kernel; 3 gate/up, 4 o_proj on
-        # the persistent streaming kernel). Measured inside a decode layer: the streaming kernel pays off up to 16 rows
+        # the persistent streaming kernel; 5 gate/up on the tcgen05 + TMA kernel). Measured inside a decode layer: the streaming kernel pays off up to 16 rows
         # (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64).
         mask = int(os.environ.get("NS_SKINNY_MASK", "27" if T <= 16 else "3"))
         skinny_down = skinny_down and bool(mask & 1)
@@ -355,6 +356,7 @@ class Qwen2Model:
         # the norm / attention kernel before it still runs
         stream_gu = skinny and bool(mask & 8) and stream_gemm_supported(T, 2 * inter, hidden)
         stream_o = skinny and bool(mask & 16) and stream_gemm_supported(T, hidden, nh * hd)
+        umma_gu = skinny and bool(mask & 32) and swiglu_gemm_supported(T, inter, hidden)     # tcgen05 + TMA (off: slower)
         if plan:
             meta.workspace.plan(meta.seq_lens, cu, meta.n_seqs, paged.block_size, meta.table_rows)
         cos, sin = rope_cos_sin(meta.positions, self.inv_freq, hd, self.dtype)
@@ -378,7 +380,9 @@ class Qwen2Model:
                 a = skinny_gemm(o2, layer.o_w, split_k=8) if skinny_o else F.linear(o2, layer.o_w)
             a = self._all_reduce(a)
             h, x = norm(a, layer.ln2, eps, residual=x)
-            if stream_gu:
+            if umma_gu:
+                m = swiglu_gemm(h, layer.gate_up_w)
+            elif stream_gu:
                 m = stream_gemm(h, layer.gate_up_w, epilogue=EPI_SILU_MUL)
             else:
                 m = silu_mul(F.linear(h, layer.gate_up_w))

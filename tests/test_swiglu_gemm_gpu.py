@@ -1,0 +1,45 @@
+"""tcgen05 gate/up + SiLU*mul GEMM (ns_swiglu_gemm) vs the unfused oracle ops: F.linear in fp32 on the same bf16 values
+rounded to bf16, then the oracle's silu_mul. Tolerance: the tensor core sums K products in another order than the CPU, so
+a bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values (BASELINE's bf16
+bound for fused ops) and >= 97 % of the elements bitwise equal."""
+import pytest
+import torch
+
+from oracle import ops as O
+from tests.test_skinny_gemm_gpu import lin
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 31, 32, 33, 48, 64])
+@pytest.mark.parametrize("H,I", [(896, 4864), (1536, 8960), (128, 192), (3584, 1024), (64, 40), (896, 9472)])
+def test_swiglu_gemm_matches_the_unfused_ops(M, H, I):
+    from nanoserve_b200.kernels.fused import swiglu_gemm, swiglu_gemm_supported, umma_gemm_errors
+    if not swiglu_gemm_supported(M, I, H):
+        pytest.skip("shape outside the kernel's shared-memory budget")
+    g = torch.Generator().manual_seed(M * 7 + H)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    out = swiglu_gemm(x.cuda(), w.cuda())
+    want = O.silu_mul(lin(x, w))
+    # silu(gate) and up may each land one bf16 ulp away (another summation order at a rounding boundary), so their
+    # product may be two ulps off: for values where that exceeds the absolute bound, compare relatively (2 * 2^-7)
+    got = out.float().cpu()
+    rel_ok = (got - want.float()).abs() <= torch.maximum(torch.tensor(2e-2), want.float().abs() * 2 ** -6)
+    assert bool(rel_ok.all()) and (out.cpu() == want).float().mean().item() >= 0.97
+    assert umma_gemm_errors() == 0
+
+
+def test_swiglu_gemm_is_deterministic_and_refuses_what_it_cannot_do():
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.fused import swiglu_gemm
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(32, 896, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(9728, 896, generator=g) * 0.03).to(torch.bfloat16).cuda()
+    first = swiglu_gemm(x, w)
+    for _ in range(20):
+        assert torch.equal(swiglu_gemm(x, w), first)
+    with pytest.raises(_lib.NanoserveB200Error):
+        swiglu_gemm(torch.zeros(65, 896, dtype=torch.bfloat16, device="cuda"), w)
+    with pytest.raises(_lib.NanoserveB200Error):
+        swiglu_gemm(torch.zeros(8, 96, dtype=torch.bfloat16, device="cuda"), torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda"))
