@@ -23,6 +23,7 @@ constexpr int kRows = 128;          // UMMA M
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
 constexpr int kHD = 64;             // head_dim handled here
 constexpr int kTmemCols = 128;      // S: columns 0..63, PV: columns 64..127
+constexpr int kStages = 4;          // K/V tiles in shared memory: copies run kStages-1 tiles ahead of the tile in use
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -100,7 +101,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 
 }  // namespace tc
 
-__global__ void __launch_bounds__(tc::kRows, 3) prefill_tc_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnParams p) {
     using namespace tc;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t mbar;
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(tc::kRows, 3) prefill_tc_kernel(const AttnPara
 
     // shared memory: 1024-byte aligned tiles (the swizzle pattern repeats every 8 rows x 128 bytes)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sK = sQ + kRows * 128, sV = sK + 2 * kKeys * 128, sP = sV + 2 * kKeys * 128;
+    const uint32_t sQ = base, sK = sQ + kRows * 128, sV = sK + kStages * kKeys * 128, sP = sV + kStages * kKeys * 128;
     const uint32_t mbar_s = smem_u32(&mbar);
 
     if (tid == 0) {
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(tc::kRows, 3) prefill_tc_kernel(const AttnPara
     };
     auto load_kv = [&](int kt) {                    // uses blk_next (the ids of tile kt), then fetches those of tile kt + 1
         if (kt < n_tiles) {
-            const uint32_t ks = sK + (kt & 1) * kKeys * 128, vs = sV + (kt & 1) * kKeys * 128;
+            const uint32_t ks = sK + (kt % kStages) * kKeys * 128, vs = sV + (kt % kStages) * kKeys * 128;
 #pragma unroll
             for (int it = 0; it < (kKeys * 8) / kRows; ++it) {
                 const int qd = it * kRows + tid;
@@ -185,6 +186,8 @@ __global__ void __launch_bounds__(tc::kRows, 3) prefill_tc_kernel(const AttnPara
     static_assert((kKeys * 8) / kRows == kKeys / 16, "one pool block per copy iteration");
     fetch_ids(0);
     load_kv(0);                       // group 0 = Q + tile 0
+#pragma unroll
+    for (int t = 1; t < kStages - 1; ++t) load_kv(t);
 
     constexpr uint32_t idesc_s = instr_desc(false), idesc_pv = instr_desc(true);
     float o[kHD];
@@ -196,12 +199,12 @@ __global__ void __launch_bounds__(tc::kRows, 3) prefill_tc_kernel(const AttnPara
     bool ok = true;
 
     for (int kt = 0; kt < n_tiles && ok; ++kt) {
-        load_kv(kt + 1);
-        cp_async_wait<1>();                                            // tile kt (and Q) landed for this thread
+        load_kv(kt + kStages - 1);                                     // into the buffer tile kt-1 has left
+        cp_async_wait<kStages - 1>();                                  // tile kt (and Q) landed for this thread
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        const uint32_t ks = sK + (kt & 1) * kKeys * 128, vs = sV + (kt & 1) * kKeys * 128;
+        const uint32_t ks = sK + (kt % kStages) * kKeys * 128, vs = sV + (kt % kStages) * kKeys * 128;
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -309,7 +312,7 @@ bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_s
 
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st) {
     if (max_items <= 0) return NS_OK;
-    constexpr int smem = (tc::kRows + 4 * tc::kKeys + tc::kRows) * 128 + 1024;
+    constexpr int smem = (tc::kRows + 2 * tc::kStages * tc::kKeys + tc::kRows) * 128 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
