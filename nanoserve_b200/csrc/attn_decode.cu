@@ -237,25 +237,32 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         const int64_t qrow = cc_qrow;
         const int slot = (i == i_first) ? 0 : 1;
         float* part = partials + ((size_t)(cta * 2 + slot) * p.n_heads + (size_t)g * GROUP) * RED_ROW;
-        for (int e = gt; e < GROUP * HD; e += gthreads) {
-            const int r = e / HD, c = e - r * HD;
+        // four output columns per thread: 16-byte reads of the warps' scratch, 16-byte (partial) or 8-byte (final) stores
+        for (int e = gt; e < GROUP * (HD / 4); e += gthreads) {
+            const int r = e / (HD / 4), c = (e - r * (HD / 4)) * 4;
             float M = -INFINITY;
             for (int w = 0; w < wph; ++w) M = fmaxf(M, red_of(wbase + g + NKV * w, red_stage[wbase + g + NKV * w])[r * RED_ROW + HD]);
-            float acc = 0.f, Ls = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float Ls = 0.f;
             for (int w = 0; w < wph; ++w) {
                 const float* rw = red_of(wbase + g + NKV * w, red_stage[wbase + g + NKV * w]) + r * RED_ROW;
                 const float sc = fast_exp2(rw[HD] - M);
-                acc = fmaf(sc, rw[c], acc);
+                const float4 v = *reinterpret_cast<const float4*>(rw + c);
+                acc.x = fmaf(sc, v.x, acc.x);
+                acc.y = fmaf(sc, v.y, acc.y);
+                acc.z = fmaf(sc, v.z, acc.z);
+                acc.w = fmaf(sc, v.w, acc.w);
                 Ls = fmaf(sc, rw[HD + 1], Ls);
             }
             if (complete) {
-                p.out[qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c] = __float2bfloat16_rn(Ls > 0.f ? acc / Ls : 0.f);
+                const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+                uint2 packed;
+                packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+                packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c) = packed;
             } else {
-                part[r * RED_ROW + c] = acc;
-                if (c == 0) {
-                    part[r * RED_ROW + HD] = M;
-                    part[r * RED_ROW + HD + 1] = Ls;
-                }
+                *reinterpret_cast<float4*>(part + r * RED_ROW + c) = acc;
+                if (c == 0) *reinterpret_cast<float2*>(part + r * RED_ROW + HD) = make_float2(M, Ls);
             }
         }
         if (!complete && gt == 0) {           // cross-CTA work for this row is deferred to the end of the CTA

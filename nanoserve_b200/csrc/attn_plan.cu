@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
                                                                  const int32_t* __restrict__ table_rows, int n_seqs,
                                                                  int block_size, int base_ctas, int max_mode,
                                                                  int split_blocks, uint8_t* ws, WsLayout L, int max_items,
-                                                                 int min_blocks, int snap_blocks) {
+                                                                 int min_blocks, int snap_blocks, int balance) {
     constexpr int kSmemRows = 2048;            // decode rows whose prefix is mirrored in shared memory
     __shared__ int warp_sums[33];
     __shared__ int indptr_sm[kSmemRows + 1];
@@ -119,6 +119,59 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         }
         return lo;
     };
+    // Large steps (mode 2) with the row prefix in shared memory: ROW-ALIGNED BALANCED cuts. Rows are packed whole into a
+    // CTA up to T blocks; a row longer than T starts a CTA of its own and is cut into ceil(L / T) equal pieces. T is the
+    // smallest of 64 candidates in [per, 3 per) for which that needs no more CTAs than there are: every range is at most
+    // T blocks and no CTA holds part of two rows. (Equal cuts snapped to row boundaries, below, leave ranges between 0.5
+    // and 2 times the average: measured on 48 rows x U[128,8192] tokens the slowest CTA streamed 20.8 us, the median 14.9.)
+    const bool balanced = mode == 2 && n_dec <= kSmemRows && balance != 0;
+    __shared__ int cand_ok[64];
+    if (balanced) {
+        if (threadIdx.x < 64) {
+            const int T = per + (per * (int)threadIdx.x) / 32;
+            int ctas = 0, cur = 0;
+            for (int i = 0; i < n_dec; ++i) {
+                const int len = ip[i + 1] - ip[i];
+                if (len > T) {
+                    ctas += (cur > 0) + (len + T - 1) / T;
+                    cur = 0;
+                } else if (cur + len > T) {
+                    ++ctas;
+                    cur = len;
+                } else {
+                    cur += len;
+                }
+            }
+            cand_ok[threadIdx.x] = ctas + (cur > 0) <= decode_ctas;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int best = 63;
+            for (int l = 62; l >= 0; --l)
+                if (cand_ok[l]) best = l;
+            const int T = cand_ok[best] ? per + (per * best) / 32 : dec_blocks;       // nothing fits: one open-ended pass
+            int c = 0, cur = 0;
+            cuts_sm[0] = 0;
+            for (int i = 0; i < n_dec && c < decode_ctas; ++i) {
+                const int start = ip[i], len = ip[i + 1] - start;
+                if (len > T) {
+                    if (cur > 0) cuts_sm[++c] = start;
+                    cur = 0;
+                    const int k = (len + T - 1) / T;
+                    for (int j = 1; j <= k && c < decode_ctas; ++j) cuts_sm[++c] = start + (int)(((long long)j * len) / k);
+                } else if (cur + len > T) {
+                    cuts_sm[++c] = start;
+                    cur = len;
+                } else {
+                    cur += len;
+                }
+            }
+            if (cur > 0 && c < decode_ctas) ++c;
+            for (; c <= decode_ctas; ++c) cuts_sm[c] = dec_blocks;      // closes the last range; the rest are empty
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) cta_start[c] = cuts_sm[c];
+    } else {
     for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) {
         long long u = (long long)c * per;
         int cut = u >= dec_blocks ? dec_blocks : (int)u;
@@ -133,6 +186,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         }
         cuts_sm[c] = cut;
         cta_start[c] = cut;
+    }
     }
     __syncthreads();
     int4* cta_rec = reinterpret_cast<int4*>(ws + L.cta_rec);
@@ -187,6 +241,8 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
 static int g_min_blocks = kMinBlocksPerCta;
 static int g_split_blocks = kSplitBlocks;
 static int g_snap_blocks = kSnapBlocks;
+static int g_balance = 1;
+void debug_set_balance(int on) { g_balance = on; }
 void debug_set_snap_blocks(int n) { g_snap_blocks = n > 0 ? n : kSnapBlocks; }
 void debug_set_min_blocks(int n) { g_min_blocks = n > 0 ? n : kMinBlocksPerCta; }
 void debug_set_split_blocks(int n) { g_split_blocks = n >= 0 ? n : kSplitBlocks; }
@@ -195,7 +251,7 @@ int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const i
                      int block_size, int base_ctas, int max_mode,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
     attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, base_ctas, max_mode,
-                                                 g_split_blocks, (uint8_t*)ws, L, max_items, g_min_blocks, g_snap_blocks);
+                                                 g_split_blocks, (uint8_t*)ws, L, max_items, g_min_blocks, g_snap_blocks, g_balance);
     return check_launch("attn_plan");
 }
 

@@ -56,6 +56,9 @@ using namespace ns;
 
 namespace ns { void debug_set_min_blocks(int n); void debug_set_split_blocks(int n); void debug_set_snap_blocks(int n); }
 extern "C" void ns_debug_snap_blocks(int n) { ns::debug_set_snap_blocks(n); }
+namespace ns { void debug_set_balance(int on); }
+// Debug hook (not part of the public header): 0 = equal cuts snapped to row boundaries also for large steps.
+extern "C" void ns_debug_balance(int on) { ns::debug_set_balance(on); }
 // Debug hook (not part of the public header): decode KV blocks above which a step runs two virtual CTAs per CTA (< 0 = default).
 extern "C" void ns_debug_split_blocks(int n) { ns::debug_set_split_blocks(n); }
 // Debug hook (not part of the public header): lower bound of a decode CTA's range in KV blocks (0 = default).
