@@ -455,7 +455,57 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 }
                 named_barrier(hg, gthreads);
             };
-            const bool single = n_parts <= STAGE_PARTS;        // then one staging serves both passes
+            if (n_parts <= STAGE_PARTS) {
+                // Few parts (the usual case): every thread fetches, for ITS row and four output columns, (m, l) of all
+                // parts and the first eight partial vectors at once - one round trip, no staging, no barrier.
+                constexpr int V4 = HD / 4;
+                for (int e = gt; e < GROUP * V4; e += gthreads) {
+                    const int r = e / V4, c4 = e - r * V4;
+                    float2 ml[STAGE_PARTS];
+                    float4 v[8];
+#pragma unroll
+                    for (int pt = 0; pt < STAGE_PARTS; ++pt)
+                        ml[pt] = pt < n_parts ? __ldcg(reinterpret_cast<const float2*>(part_row(c_first + pt, r) + HD))
+                                              : make_float2(-INFINITY, 0.f);
+#pragma unroll
+                    for (int pt = 0; pt < 8; ++pt)
+                        v[pt] = pt < n_parts ? __ldcg(reinterpret_cast<const float4*>(part_row(c_first + pt, r)) + c4)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                    float M = -INFINITY;
+#pragma unroll
+                    for (int pt = 0; pt < STAGE_PARTS; ++pt) M = fmaxf(M, ml[pt].x);
+                    float Ls = 0.f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int pt = 0; pt < STAGE_PARTS; ++pt) {
+                        const float wgt = ml[pt].x > -INFINITY ? fast_exp2(ml[pt].x - M) : 0.f;
+                        ml[pt].x = wgt;
+                        Ls = fmaf(wgt, ml[pt].y, Ls);
+                    }
+#pragma unroll
+                    for (int pt = 0; pt < 8; ++pt) {
+                        acc.x = fmaf(ml[pt].x, v[pt].x, acc.x);
+                        acc.y = fmaf(ml[pt].x, v[pt].y, acc.y);
+                        acc.z = fmaf(ml[pt].x, v[pt].z, acc.z);
+                        acc.w = fmaf(ml[pt].x, v[pt].w, acc.w);
+                    }
+                    for (int pt = 8; pt < n_parts; ++pt) {             // parts nine and up: a second round trip
+                        const float4 w4 = __ldcg(reinterpret_cast<const float4*>(part_row(c_first + pt, r)) + c4);
+                        acc.x = fmaf(ml[pt].x, w4.x, acc.x);
+                        acc.y = fmaf(ml[pt].x, w4.y, acc.y);
+                        acc.z = fmaf(ml[pt].x, w4.z, acc.z);
+                        acc.w = fmaf(ml[pt].x, w4.w, acc.w);
+                    }
+                    const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+                    uint2 packed;
+                    packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+                    packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+                    *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + 4 * c4) = packed;
+                }
+                if (gt == 0) counters[i * kMaxKvHeads + g] = 0;
+                continue;
+            }
+            const bool single = false;                         // more parts than one staging holds: staged in batches
             float myM = -INFINITY;                             // threads 0..7 of the group: row maxima
             for (int base = c_first; base <= c_last; base += STAGE_PARTS) {
                 const int cnt = min(STAGE_PARTS, c_last - base + 1);
