@@ -421,10 +421,16 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     const int n_pend = pend_n[hg];
     if (n_pend > 0) {
         if (gt == 0) {
-            __threadfence();
-            for (int k = 0; k < n_pend; ++k)
-                pend_last[hg][k] = atomicAdd(&counters[pend[hg][k].x * kMaxKvHeads + g], 1) == pend_span[hg][k].y - 1;
-            __threadfence();
+            // one acquire-release atomic per row instead of fence, atomic, fence: it releases the partials the barrier in
+            // flush() ordered before it and acquires those of the CTAs that arrived earlier
+            for (int k = 0; k < n_pend; ++k) {
+                int prev;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                             : "=r"(prev)
+                             : "l"(&counters[pend[hg][k].x * kMaxKvHeads + g])
+                             : "memory");
+                pend_last[hg][k] = prev == pend_span[hg][k].y - 1;
+            }
         }
         named_barrier(hg, gthreads);
         for (int k = 0; k < n_pend; ++k) {
