@@ -119,12 +119,17 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         }
         return lo;
     };
-    // Large steps (mode 2) with the row prefix in shared memory: ROW-ALIGNED BALANCED cuts. Rows are packed whole into a
+    // Steps with the row prefix in shared memory, large ones (mode 2) always: ROW-ALIGNED BALANCED cuts. Rows are packed whole into a
     // CTA up to T blocks; a row longer than T starts a CTA of its own and is cut into ceil(L / T) equal pieces. T is the
     // smallest of 64 candidates in [per, 3 per) for which that needs no more CTAs than there are: every range is at most
     // T blocks and no CTA holds part of two rows. (Equal cuts snapped to row boundaries, below, leave ranges between 0.5
     // and 2 times the average: measured on 48 rows x U[128,8192] tokens the slowest CTA streamed 20.8 us, the median 14.9.)
-    const bool balanced = mode == 2 && n_dec <= kSmemRows && balance != 0;
+    // ... and for small steps whose rows are, on average, at least three quarters of a range long (many short rows per
+    // range pack better with the equal cuts below: 256 rows x U[64,1024] tokens 19.4 vs 20.9 us)
+    const bool balanced = balance != 0 && n_dec <= kSmemRows &&
+                          (mode == 2 || (balance >= 2 && 4LL * dec_blocks >= 3LL * n_dec * per));
+    // small steps: a row of up to 2 * min_blocks blocks is never split (a cross-CTA combine costs more than it saves)
+    const int no_split = mode == 2 ? 0 : 2 * min_blocks;
     __shared__ int cand_ok[64];
     if (balanced) {
         if (threadIdx.x < 64) {
@@ -133,7 +138,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
             for (int i = 0; i < n_dec; ++i) {
                 const int len = ip[i + 1] - ip[i];
                 if (len > T) {
-                    ctas += (cur > 0) + (len + T - 1) / T;
+                    ctas += (cur > 0) + (len > no_split ? (len + T - 1) / T : 1);
                     cur = 0;
                 } else if (cur + len > T) {
                     ++ctas;
@@ -157,7 +162,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
                 if (len > T) {
                     if (cur > 0) cuts_sm[++c] = start;
                     cur = 0;
-                    const int k = (len + T - 1) / T;
+                    const int k = len > no_split ? (len + T - 1) / T : 1;
                     for (int j = 1; j <= k && c < decode_ctas; ++j) cuts_sm[++c] = start + (int)(((long long)j * len) / k);
                 } else if (cur + len > T) {
                     cuts_sm[++c] = start;
@@ -241,7 +246,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
 static int g_min_blocks = kMinBlocksPerCta;
 static int g_split_blocks = kSplitBlocks;
 static int g_snap_blocks = kSnapBlocks;
-static int g_balance = 1;
+static int g_balance = 2;
 void debug_set_balance(int on) { g_balance = on; }
 void debug_set_snap_blocks(int n) { g_snap_blocks = n > 0 ? n : kSnapBlocks; }
 void debug_set_min_blocks(int n) { g_min_blocks = n > 0 ? n : kMinBlocksPerCta; }
