@@ -20,10 +20,11 @@ constexpr int kMinBlocksPerCta = 32;      // a decode CTA's range is never cut b
                                           // a row costs a partial write, a fence, an atomic and a cross-CTA reduce. Timed
                                           // alone, 32 rows x ~500 tokens run faster with 8 (10.7 vs 13.1 us), but inside a
                                           // layer, where the kernel's start overlaps the QKV GEMM, 32 wins (7.3 vs 9.5 us)
-constexpr int kSplitBlocks = 12800;       // steps with more decode KV blocks than this run two virtual CTAs per CTA.
-                                          // Measured (hd 64, 14q/2kv): up to ~12.4K blocks one 16-warp CTA per SM is as fast
-                                          // or faster (32 rows x 500 tokens: 7.3 vs 12.1 us; 128 rows x 1400: 18.0 vs 22.7);
-                                          // at 14.1K blocks (48 rows, U[128,8192]) two 8-warp halves win (27.6 vs 31.6 us)
+constexpr int kSplitBlocks = 15360;       // steps with more decode KV blocks than this run two virtual CTAs per CTA.
+                                          // Measured (hd 64, 14q/2kv, balanced ranges): up to ~14K blocks one 16-warp CTA per
+                                          // SM is as fast or faster (32 rows x 500 tokens: 6.8 vs 12.1 us; 128 rows x 1400:
+                                          // 17.3 vs 20.5; 48 rows x U[128,8192], 14.1K blocks: 24.2 vs 24.4); from ~16K blocks
+                                          // two 8-warp halves win (256 rows x 1000: 23.6 vs 25.7; 27.5K blocks: 42.6 vs 44.4)
 constexpr int kSnapBlocks = 32;           // ranges up to twice this long per 8 warps may move a cut by half a range to
                                           // reach a row boundary (a whole row needs no partials); longer ranges by an eighth
 

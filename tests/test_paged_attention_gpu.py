@@ -148,7 +148,7 @@ def test_strided_layer_pool_and_table_rows():
 
 def test_decode_one_range_per_cta_and_two_virtual_ctas_agree():
     """The plan kernel picks, per step, whether every 16-warp decode CTA works on one range or runs as two virtual
-    8-warp CTAs with a range each (steps above 12,800 KV blocks). Both paths are forced here through the library's
+    8-warp CTAs with a range each (steps above 15,360 KV blocks). Both paths are forced here through the library's
     debug hook on a small ragged case (checked against the CPU oracle) and on BASELINE config 1's decode rows at full
     size (checked against the scalar fp32-accumulating kernel of the same library): tolerance 1e-2 as above."""
     import ctypes
