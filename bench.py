@@ -43,7 +43,7 @@ CPU_SAMPLE_REQUESTS, CPU_SAMPLE_MAX_NEW = 6, 16
 HBM_FALLBACK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch on the config-1 batch, from the ncu
 # capture summarised in profiles/paged_decode_kernel_config1.md
-DECODE_DRAM_TRAFFIC_BYTES = 118_160_000
+DECODE_DRAM_TRAFFIC_BYTES = 117_000_000
 
 
 def workload():
