@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE config 2): Qwen2.5-0.5B architecture, bf16, random-init weights; 64 requests with uniform random
+Workload (benchmark configuration 2): Qwen2.5-0.5B architecture, bf16, random-init weights; 64 requests with uniform random
 prompt ids, prompt lengths uniform in 64-1024, seeded output lengths uniform in 16-256; closed loop at concurrency
 32, chunked prefill 2048 tokens/step, CUDA graphs. One "step" of this benchmark = one pass over the 64 requests.
 
@@ -11,7 +11,7 @@ Reported on one JSON line:
             between steps (CUDA events, max over ranks);
   e2e       the same metric through the public API (LLMEngine.add_request / step): host token lists in, per-step
             upload of the packed step records from pinned memory, per-step device->host read of the sampled tokens;
-  roofline  decode paged attention on BASELINE config 1 (48 decode rows, contexts 128-8192, 14/2 heads, hd 64):
+  roofline  decode paged attention on benchmark configuration 1 (48 decode rows, contexts 128-8192, 14/2 heads, hd 64):
             algorithmic bytes / CUDA-event time per launch, against the measured HBM copy bandwidth;
   cpu_baseline  the CPU oracle (a port of the reference's torch path, fp32) on a bounded sample of the same request
             stream, timed on this box's host cores (rank 0, N=1 only).
@@ -153,7 +153,7 @@ def run_reference_arm(args) -> None:
 
 # ------------------------------------------------------------------------------------------------ roofline leg
 def decode_attention_roofline(device) -> dict:
-    """Decode paged attention on BASELINE config 1, timed alone: R launches rotating over 4 KV pools (inputs larger
+    """Decode paged attention on benchmark configuration 1, timed alone: R launches rotating over 4 KV pools (inputs larger
     than the 126 MB L2) inside one CUDA graph, CUDA events around the replay on the launching stream."""
     from nanoserve_b200.kernels.fused import kv_write
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
@@ -486,7 +486,7 @@ def timed_pass(eng, reqs, concurrency) -> tuple[float, int]:
 
 
 def extra_workload(args) -> None:
-    """The other BASELINE configurations, end to end through the public API (wall clock between synchronisations):
+    """The other benchmark configurations, end to end through the public API (wall clock between synchronisations):
     sweep  = config 2 at concurrency 1/4/8/16/32/128/256;
     prefix = config 3, Qwen2.5-1.5B shape, shared 1024-token prefix, c=32, prefix caching on vs off;
     tp     = config 4, Qwen2.5-7B shape, tensor parallel over all ranks of the torchrun job (c=64)."""

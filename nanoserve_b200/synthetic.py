@@ -63,7 +63,7 @@ def attention_workload(n_decode: int = 48, decode_range=(128, 8192), n_prefill: 
                        prefill_ctx_range=(0, 2048), n_heads: int = 14, n_kv_heads: int = 2, head_dim: int = 64,
                        num_blocks: int = 65536, block_size: int = 16, dtype=torch.bfloat16, device="cuda",
                        seed: int = 0) -> AttentionWorkload:
-    """BASELINE config 1: decode rows with context lengths uniform in decode_range (the new token included) plus
+    """benchmark configuration 1: decode rows with context lengths uniform in decode_range (the new token included) plus
     prefill chunks of `chunk` new tokens on top of a cached context uniform in prefill_ctx_range. Block tables
     are consecutive slices of a seeded random permutation of the pool; Q/K/V are N(0,1); scale 1/sqrt(hd)."""
     rng = random.Random(seed)

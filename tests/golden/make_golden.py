@@ -7,7 +7,7 @@ Outputs (committed):
   planner_traces.json   step-by-step integer decisions of the reference Scheduler + PagedKVManager
   ops.pt                outputs of the reference's torch ops / attention paths on seeded inputs
   tiny_engine.json      tokens of the reference LLMEngine (CPU, fp32) on a tiny random Qwen2-shaped model
-  config0_tokens.json   tokens + top-2 logit gaps of the reference LLMEngine on the 0.5B shape (BASELINE config 0)
+  config0_tokens.json   tokens + top-2 logit gaps of the reference LLMEngine on the 0.5B shape (benchmark configuration 0)
 The tests regenerate the same inputs from the same seeds (helpers below are imported by the tests).
 """
 from __future__ import annotations
@@ -93,7 +93,7 @@ TINY_ENGINE_KW = dict(max_seq_len=128, max_num_seqs=4, max_num_batched_tokens=32
 
 
 def config0_requests():
-    """BASELINE config 0: 8 requests, prompt lengths uniform in 32-256, uniform token ids, 64 greedy tokens."""
+    """benchmark configuration 0: 8 requests, prompt lengths uniform in 32-256, uniform token ids, 64 greedy tokens."""
     rng = random.Random(0)
     reqs = []
     for _ in range(8):
@@ -255,7 +255,7 @@ def main(ref_root: str) -> None:
                                                            prefill_chunks=eng.stats["prefill_chunks"])))
     print("tiny engine:", eng.stats["steps"], "steps")
 
-    # ---- 4. BASELINE config 0 on the full 0.5B shape (random init), CPU fp32
+    # ---- 4. benchmark configuration 0 on the full 0.5B shape (random init), CPU fp32
     from nanoserve_b200.synthetic import random_state_dict
     sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
     model = Qwen2Model(ModelConfig(**cfg), sd)
@@ -280,4 +280,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
+    main(sys.argv[1])

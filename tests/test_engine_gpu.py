@@ -188,7 +188,7 @@ def test_padding_touches_only_the_garbage_block():
 
 
 def test_config0_fp32_greedy_tokens_match_the_reference():
-    """BASELINE config 0 on the GPU in fp32: the first 32 generated tokens of all 8 requests equal the reference's
+    """benchmark configuration 0 on the GPU in fp32: the first 32 generated tokens of all 8 requests equal the reference's
     CPU run (golden file); a divergence is accepted only at a step whose reference top-2 gap is below 1e-3."""
     from nanoserve_b200.synthetic import random_state_dict
     gold = json.loads((GOLD / "config0_tokens.json").read_text())

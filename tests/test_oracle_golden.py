@@ -122,7 +122,7 @@ def test_oracle_engine_tiny_model_tokens():
 
 
 def test_oracle_engine_config0_tokens():
-    """BASELINE config 0 (0.5B shape, fp32, 8 requests x 64 tokens) against the reference's own run."""
+    """benchmark configuration 0 (0.5B shape, fp32, 8 requests x 64 tokens) against the reference's own run."""
     from nanoserve_b200.synthetic import random_state_dict
     gold = json.loads((GOLD / "config0_tokens.json").read_text())
     sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)

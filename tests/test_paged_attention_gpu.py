@@ -1,7 +1,7 @@
 """Ragged paged attention (through the C ABI) vs the CPU oracle.
 
 Tolerances, stated up front (reference tests/test_paged_attention_kernel.py:3-8): fp32 inputs max|diff| <= 1e-5;
-bf16 inputs compared with the oracle run in fp32 on the SAME bf16 values, max|diff| <= 1e-2 (BASELINE allows
+bf16 inputs compared with the oracle run in fp32 on the SAME bf16 values, max|diff| <= 1e-2 (the benchmark specification allows
 2e-2). Cases: the reference's head layouts (14/2/64, 12/2/128, 16/2/128) and context lengths
 [1, 15, 16, 17, 100, 333, 700], fragmented block tables, the ctx == 1 known answer, long contexts that split
 over many CTAs, mixed prefill + decode batches with chunk-on-context, and strided pools."""
@@ -149,7 +149,7 @@ def test_strided_layer_pool_and_table_rows():
 def test_decode_one_range_per_cta_and_two_virtual_ctas_agree():
     """The plan kernel picks, per step, whether every 16-warp decode CTA works on one range or runs as two virtual
     8-warp CTAs with a range each (steps above 15,360 KV blocks). Both paths are forced here through the library's
-    debug hook on a small ragged case (checked against the CPU oracle) and on BASELINE config 1's decode rows at full
+    debug hook on a small ragged case (checked against the CPU oracle) and on benchmark configuration 1's decode rows at full
     size (checked against the scalar fp32-accumulating kernel of the same library): tolerance 1e-2 as above."""
     import ctypes
     from nanoserve_b200 import _lib

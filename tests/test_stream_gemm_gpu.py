@@ -1,7 +1,7 @@
 """Persistent weight-streaming GEMM (ns_stream_gemm) vs the unfused oracle ops: F.linear in fp32 on the same bf16
 values rounded to bf16, then the token-wise op of the oracle. Tolerance: the GEMM sums K products in another order than
 the CPU, so the bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values
-(BASELINE's bf16 bound for fused ops), and >= 97 % of the elements bitwise equal. The residual stream is bit-exact."""
+(the benchmark specification's bf16 bound for fused ops), and >= 97 % of the elements bitwise equal. The residual stream is bit-exact."""
 import pytest
 import torch
 

@@ -1,6 +1,6 @@
 """tcgen05 gate/up + SiLU*mul GEMM (ns_swiglu_gemm) vs the unfused oracle ops: F.linear in fp32 on the same bf16 values
 rounded to bf16, then the oracle's silu_mul. Tolerance: the tensor core sums K products in another order than the CPU, so
-a bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values (BASELINE's bf16
+a bf16 result may differ by one ulp at a rounding boundary; stated bound 2e-2 max-abs on O(1) values (the benchmark specification's bf16
 bound for fused ops) and >= 97 % of the elements bitwise equal."""
 import pytest
 import torch
