@@ -262,3 +262,22 @@ def test_prefix_cache_lookup_eviction_and_duplicates():
     dup.free([blk])
     with pytest.raises(ValueError):
         dup.free([blk])
+
+
+def test_step_buckets_extend_the_reference_grid_to_the_step_budget():
+    from nanoserve_b200.cuda_graphs import PIECEWISE_CAP, piecewise_buckets, step_buckets
+    assert step_buckets(100) == piecewise_buckets(100) and step_buckets(512) == piecewise_buckets(512)
+    b = step_buckets(2080)
+    assert b[:len(piecewise_buckets(2080))] == piecewise_buckets(2080)          # the reference's grid up to its cap ...
+    assert b[-1] == 2080 and b == sorted(set(b))                                # ... then up to the budget itself
+    above = [x for x in b if x > PIECEWISE_CAP]
+    assert all(y - x <= 128 for x, y in zip([PIECEWISE_CAP] + above, above))    # padding waste of at most 128 rows
+
+
+def test_gemm_shape_predicates():
+    from nanoserve_b200.kernels.fused import stream_gemm_supported, swiglu_gemm_supported
+    assert stream_gemm_supported(32, 9728, 896) and stream_gemm_supported(64, 896, 1024)
+    assert not stream_gemm_supported(64, 9728, 1536) and not stream_gemm_supported(8, 9728, 3584)
+    assert not stream_gemm_supported(65, 9728, 896) and not stream_gemm_supported(8, 100, 896)
+    assert swiglu_gemm_supported(32, 4864, 896) and swiglu_gemm_supported(64, 4864, 896)
+    assert not swiglu_gemm_supported(65, 4864, 896) and not swiglu_gemm_supported(8, 4864, 900)
