@@ -153,6 +153,7 @@ class Qwen2Model:
     fused = False
     skinny_gemms = True      # decode-sized steps: narrow GEMMs through the weight-streaming kernel (False = library GEMMs)
     tp_group = None          # torch.distributed process group when the model is one tensor-parallel shard
+    _plan_streams: dict = {}  # one side stream per device for the attention plan (shared by every model)
     tp_size = 1
 
     def __init__(self, cfg: ModelConfig, state_dict: dict[str, torch.Tensor]):
@@ -357,8 +358,18 @@ class Qwen2Model:
         stream_gu = skinny and bool(mask & 8) and stream_gemm_supported(T, 2 * inter, hidden)
         stream_o = skinny and bool(mask & 16) and stream_gemm_supported(T, hidden, nh * hd)
         umma_gu = skinny and bool(mask & 32) and swiglu_gemm_supported(T, inter, hidden)     # tcgen05 + TMA (off: slower)
+        # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's
+        # attention: it runs on a second stream next to the RoPE tables, the embedding, the first norm and the first QKV
+        # GEMM (inside a capture this becomes a fork and a join in the graph).
+        plan_stream = None
         if plan:
-            meta.workspace.plan(meta.seq_lens, cu, meta.n_seqs, paged.block_size, meta.table_rows)
+            main = torch.cuda.current_stream()
+            plan_stream = Qwen2Model._plan_streams.get(self.device)
+            if plan_stream is None:
+                plan_stream = Qwen2Model._plan_streams[self.device] = torch.cuda.Stream(device=self.device)
+            plan_stream.wait_stream(main)
+            with torch.cuda.stream(plan_stream):
+                meta.workspace.plan(meta.seq_lens, cu, meta.n_seqs, paged.block_size, meta.table_rows)
         cos, sin = rope_cos_sin(meta.positions, self.inv_freq, hd, self.dtype)
         x = F.embedding(meta.tokens, self.embed)
         h = norm(x, self.layers[0].ln1, eps)
@@ -370,6 +381,9 @@ class Qwen2Model:
             else:
                 qkv = F.linear(h, layer.qkv_w, layer.qkv_b)
                 q, _, _ = rope_qkv(qkv, cos, sin, nh, nkv, hd, paged.k[i], paged.v[i], meta.slot_mapping, dense_kv=False)
+            if plan_stream is not None:
+                torch.cuda.current_stream().wait_stream(plan_stream)          # join: the plan is complete from here on
+                plan_stream = None
             o = ragged_paged_attention(q, paged.k[i], paged.v[i], meta.block_tables, meta.seq_lens, cu, scale,
                                        n_seqs=meta.n_seqs, table_rows=meta.table_rows, workspace=meta.workspace,
                                        planned=True)
