@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const T* __restrict__
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
     const int row_id = blockIdx.x / csize;
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "this CTA runs", waited for before the DSMEM stores
     constexpr int V = Vec16<T>::N;
     const T* row = logits + (int64_t)row_id * row_stride;
     float best = -INFINITY;
@@ -156,6 +157,7 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const T* __restrict__
     // every CTA's candidate goes to slot `rank` of the first CTA's shared memory; the first CTA picks among them
     __shared__ float cv[8];
     __shared__ int ci[8];
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // the first CTA is running: its shared memory exists
     if (threadIdx.x == 0) {
         *cluster.map_shared_rank(&cv[rank], 0) = best;
         *cluster.map_shared_rank(&ci[rank], 0) = best_i;

@@ -8,7 +8,8 @@
 //     by 16 bytes in shared memory so ldmatrix is conflict-free without a swizzle;
 //   * 4 warps x (16 weight rows x all token rows) of mma.sync m16n8k16 bf16 -> fp32;
 //   * narrow-N GEMMs (o_proj, down_proj, QKV) are split over K across a thread-block cluster; the partial tiles are
-//     summed through distributed shared memory in rank order (deterministic, no atomics, no second kernel);
+//     pushed into the shared memory of the rank that finishes the row and summed there in rank order (deterministic,
+//     no atomics, no second kernel, one cluster barrier between the last mma and the epilogue);
 //   * prologue (optional): r = residual + a rounded to bf16, X = ln_w * bf16(r * rsqrt(mean(r^2) + eps)) computed on
 //     the fly (replaces a separate add+RMSNorm kernel; r is stored once for the residual stream);
 //   * epilogue: bias; or SiLU(gate)*up (the CTA's 64 weight rows are 32 gate rows + the matching 32 up rows); or
@@ -73,6 +74,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
     return false;
 }
 
+// Split cluster barrier: arrive early, wait where the guarantee is needed.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 constexpr int kBN = 64;              // weight rows per CTA
 constexpr int kGemmThreads = 128;
 
@@ -89,7 +94,7 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     uint8_t* a_sm = smem;
     uint8_t* w_sm = smem + (size_t)MP * a_stride;       // 4 warps x [16 weight rows][k-slice], rows padded like a_sm
     w_sm += (128 - (reinterpret_cast<uintptr_t>(w_sm) & 127)) & 127;
-    float* c_sm = reinterpret_cast<float*>(w_sm + (size_t)kBN * a_stride);          // [MP][64] fp32
+    float* c_sm = reinterpret_cast<float*>(w_sm + (size_t)kBN * a_stride);          // [csize][rows per rank][64] fp32
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // QKV only: the attention kernel that follows fetches its plan, block ids and older K/V rows while this GEMM runs.
@@ -111,6 +116,7 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    cluster_arrive();                                   // "this CTA runs": peers wait for it before they store into c_sm
     const uint32_t row_bytes = (uint32_t)ks * 2;
     const uint32_t my_w = smem_u32(w_sm) + (uint32_t)(16 * warp) * a_stride;
     {
@@ -221,29 +227,39 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
         }
     }
 
-    // ---- partial tile to shared memory, cluster reduction -----------------------------------------------------------
+    // ---- cluster reduction: every CTA pushes its partial rows into the shared memory of the rank that finishes them ----
+    // Rank q finishes token rows q, q + csize, ...; its receive buffer is [csize senders][rows per rank][64] fp32. Stores
+    // into a peer's shared memory are one-way, so the only cluster barrier on the critical path is the one between the
+    // stores and the sums; the first barrier (every CTA of the cluster is running) was arrived at before the loads.
+    const int rpr = (MP + csize - 1) / csize;           // receive rows per rank
+    cluster_wait();
     {
         const int r0 = lane >> 2, cp = (lane & 3) * 2;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int col = 16 * warp + 8 * j + cp;
-                *reinterpret_cast<float2*>(c_sm + (16 * mt + r0) * kBN + col) = make_float2(acc[mt][j][0], acc[mt][j][1]);
-                *reinterpret_cast<float2*>(c_sm + (16 * mt + r0 + 8) * kBN + col) = make_float2(acc[mt][j][2], acc[mt][j][3]);
+            for (int half = 0; half < 2; ++half) {
+                const int m = 16 * mt + r0 + 8 * half;
+                if (m >= p.M) continue;
+                const int owner = m % csize, slot = m / csize;
+                float* dst = cluster.map_shared_rank(c_sm, owner) + ((size_t)rank * rpr + slot) * kBN + 16 * warp + cp;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(acc[mt][j][2 * half], acc[mt][j][2 * half + 1]);
             }
     }
-    cluster.sync();
-    // rank r finishes token rows r, r + csize, ...: sum the partial tiles in rank order, then the epilogue
+    cluster_arrive();
+    cluster_wait();
+    // sum the partial rows in rank order (deterministic), then the epilogue
     for (int m = rank; m < p.M; m += csize) {
-        // every thread gets one pair (n, n + 32) of the row, or with 128 threads: threads 0..31 -> pairs, 4 rows at a time
-        // simpler: each warp takes one row of this rank's share at a time
-        if (((m - rank) / csize) % (kGemmThreads / 32) != warp) continue;
+        const int slot = (m - rank) / csize;
+        if (slot % (kGemmThreads / 32) != warp) continue;          // each warp takes one row of this rank's share at a time
         float lo = 0.f, hi = 0.f;                       // columns lane and lane + 32 of the tile
+#pragma unroll 8
         for (int r = 0; r < csize; ++r) {
-            const float* peer = cluster.map_shared_rank(c_sm, r);
-            lo += peer[m * kBN + lane];
-            hi += peer[m * kBN + lane + 32];
+            const float* part = c_sm + ((size_t)r * rpr + slot) * kBN;
+            lo += part[lane];
+            hi += part[lane + 32];
         }
         if (EPI == kEpiBias) {
             const int n_lo = tile * kBN + lane, n_hi = n_lo + 32;
@@ -286,7 +302,6 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
             dst[lane + 32] = __float2bfloat16_rn(xh);
         }
     }
-    cluster.sync();                                      // peers may still be reading this CTA's tile
 }
 
 }  // namespace ns
@@ -295,7 +310,7 @@ namespace ns {
 
 template <int MT, int EPI>
 static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
-    const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + 128 + (size_t)16 * MT * kBN * 4;
+    const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + 128 + (size_t)(16 * MT + 8) * kBN * 4;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -354,7 +369,7 @@ extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* l
     p.eps = eps;
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const size_t a_bytes = (size_t)(mp + kBN) * (p.k_slice * 2 + 16);
-    NS_REQUIRE(a_bytes + (size_t)mp * kBN * 4 + 128 <= 220 * 1024 && p.k_slice <= 1024, NS_ERR_UNSUPPORTED,
+    NS_REQUIRE(a_bytes + (size_t)(mp + 8) * kBN * 4 + 128 <= 220 * 1024 && p.k_slice <= 1024, NS_ERR_UNSUPPORTED,
                "skinny_gemm: K slice of %d does not fit shared memory (raise split_k)", p.k_slice);
     cudaStream_t st = (cudaStream_t)stream;
     if (epilogue == kEpiBias) return dispatch_mt<kEpiBias>(p, (N + kBN - 1) / kBN, split_k, st);
