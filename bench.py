@@ -392,7 +392,7 @@ def layer_probe(rows: int) -> None:
     import torch.nn.functional as F
     from nanoserve_b200 import _lib
     from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
-                                              stream_gemm, swiglu_gemm)
+                                              stream_gemm, swiglu_gemm, thin_gemm)
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
     from nanoserve_b200.synthetic import attention_workload
     M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
@@ -415,11 +415,14 @@ def layer_probe(rows: int) -> None:
             if qkv == "skinny":
                 q = skinny_gemm(h, l["qkv"], l["b"], split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=w.k_pool,
                                 v_cache=w.v_pool, slots=w.slot_mapping, n_heads=14, n_kv_heads=2)
+            elif qkv == "thin":
+                q = thin_gemm(h, l["qkv"], l["b"], epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=w.k_pool, v_cache=w.v_pool,
+                              slots=w.slot_mapping, n_heads=14, n_kv_heads=2)
             if attn:
                 q = ragged_paged_attention(q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, None, 0.125, workspace=ws,
                                            planned=True)
             o2 = q.view(M, H)
-            a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else o2)
+            a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else (thin_gemm(o2, l["o"]) if o == "thin" else o2))
             if norm1:
                 h, x = rms_norm(a, l["ln"], 1e-6, residual=x)
             else:
@@ -458,7 +461,11 @@ def layer_probe(rows: int) -> None:
             ts.append(a.elapsed_time(b) * 1e3 / L)
         return round(sorted(ts)[2], 2)
 
-    variants = {"engine chain": {}, "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
+    variants = {"engine chain": dict(qkv="thin", o="thin") if M > 16 else dict(qkv="thin", o="thin", gu="stream"),
+                "qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}, "qkv on thin_gemm": dict(qkv="thin"), "o_proj on thin_gemm": dict(o="thin"),
+                "qkv and o_proj on thin_gemm": dict(qkv="thin", o="thin"),
+                "qkv and o_proj on thin_gemm, gate_up on stream_gemm": dict(qkv="thin", o="thin", gu="stream"),
+                "qkv on thin_gemm, o_proj and gate_up on stream_gemm": dict(qkv="thin", o="stream", gu="stream"), "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
                 "no qkv": dict(qkv=None), "no o_proj": dict(o=None), "no norm1": dict(norm1=False),
                 "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": dict(gu="umma"),
                 "o_proj on stream_gemm, gate_up on swiglu_gemm": dict(o="stream", gu="umma"),

@@ -89,6 +89,22 @@ int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* 
                    int32_t epilogue, int32_t inter, const void* cos, const void* sin, void* k_cache, void* v_cache,
                    const int64_t* slots, int32_t n_heads, int32_t n_kv_heads, void* stream);
 
+/* Narrow GEMM for decode-sized batches without a split over K across CTAs (bf16 only):
+ *   out = epilogue( x . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, K % 128 == 0, N % 8 == 0,
+ *   (8 + M rounded up to 16, 32 or 64) rows of K must fit shared memory (K <= 1536 at 64 rows, <= 2688 at 32).
+ * One CTA per eight weight rows over all of K: a GEMM with N around 1000 is one CTA per SM; the weight rows are
+ * requested before the kernel waits for its predecessor in the stream, every CTA then fetches all of x (16-byte
+ * cp.async copies, each warp its own quarter of K), and the four warps' partial tiles are summed through shared
+ * memory in a fixed order. No cluster, no barrier a thread could wait on beyond __syncthreads.
+ * epilogue 0: out[M, N] = bf16(acc + bias) (bias may be NULL);
+ * epilogue 2: as ns_skinny_gemm's epilogue 2 (merged QKV of 64-wide heads: bias, RoPE, q to out, k / v into one
+ *   layer's paged pool at slots[m]).
+ * Replaces, fused: nanoserve/model.py:231 (merged QKV F.linear + rope_qkv with the KV write) and :256 (o_proj) for
+ * steps of at most 64 token rows. */
+int ns_thin_gemm(const void* x, const void* w, const void* bias, void* out, int32_t M, int32_t N, int32_t K,
+                 int32_t epilogue, const void* cos, const void* sin, void* k_cache, void* v_cache, const int64_t* slots,
+                 int32_t n_heads, int32_t n_kv_heads, void* stream);
+
 /* Persistent weight-streaming GEMM for decode-sized batches (bf16 only):
  *   out = epilogue( prologue(x) . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, N % 16 == 0,
  *   K one of 896, 1024, 1536 (64 token rows only up to K = 1024).

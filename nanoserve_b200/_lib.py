@@ -26,6 +26,7 @@ SIGNATURES: dict[str, tuple] = {
     "ns_kv_write": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, c_int, _P]),
     "ns_skinny_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _F, _I32, _I32, _P, _P, _P, _P, _P, _I32,
                                _I32, _P]),
+    "ns_thin_gemm": (c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I32, _I32, _P]),
     "ns_stream_gemm": (c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32, _I32, _I32, _F, _I32, _P]),
     "ns_stream_gemm_errors": (c_int, [_P]),
     "ns_swiglu_gemm": (c_int, [_P, _P, _P, _I32, _I32, _I32, _P]),

@@ -331,7 +331,7 @@ class Qwen2Model:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
         from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
                                                   rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
-                                                  swiglu_gemm_supported)
+                                                  swiglu_gemm_supported, thin_gemm, thin_gemm_supported)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
@@ -347,9 +347,11 @@ class Qwen2Model:
         # the preceding norm / attention kernel still runs (programmatic dependent launch)
         import os
         # which GEMMs leave the library GEMM (bit 0 down_proj, 1 QKV, 2 o_proj on the skinny kernel; 3 gate/up, 4 o_proj on
-        # the persistent streaming kernel; 5 gate/up on the tcgen05 + TMA kernel). Measured inside a decode layer: the streaming kernel pays off up to 16 rows
-        # (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64).
-        mask = int(os.environ.get("NS_SKINNY_MASK", "27" if T <= 16 else "3"))
+        # the persistent streaming kernel; 5 gate/up on the tcgen05 + TMA kernel; 6 QKV, 7 o_proj on the 8-row-tile kernel
+        # without split-K, which wins over bits 1, 2 and 4). Measured inside a decode layer: the streaming kernel pays off
+        # for gate/up up to 16 rows (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64); QKV and o_proj
+        # together on the 8-row-tile kernel take 2.9 us off a layer at 32 rows.
+        mask = int(os.environ.get("NS_SKINNY_MASK", "219" if T <= 16 else "195"))
         skinny_down = skinny_down and bool(mask & 1)
         skinny_qkv = skinny and hd == 64 and hidden % 128 == 0 and bool(mask & 2)
         skinny_o = skinny and (nh * hd) % 128 == 0 and bool(mask & 4)
@@ -358,6 +360,10 @@ class Qwen2Model:
         stream_gu = skinny and bool(mask & 8) and stream_gemm_supported(T, 2 * inter, hidden)
         stream_o = skinny and bool(mask & 16) and stream_gemm_supported(T, hidden, nh * hd)
         umma_gu = skinny and bool(mask & 32) and swiglu_gemm_supported(T, inter, hidden)     # tcgen05 + TMA (off: slower)
+        # (only where its N / 8 CTAs are one wave of the SMs: the shapes it was measured on)
+        thin_qkv = (skinny and hd == 64 and bool(mask & 64) and (nh + 2 * nkv) * hd // 8 <= 148 and
+                    thin_gemm_supported(T, (nh + 2 * nkv) * hd, hidden))
+        thin_o = skinny and bool(mask & 128) and hidden // 8 <= 148 and thin_gemm_supported(T, hidden, nh * hd)
         # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's
         # attention: it runs on a second stream next to the RoPE tables, the embedding, the first norm and the first QKV
         # GEMM (inside a capture this becomes a fork and a join in the graph).
@@ -375,7 +381,10 @@ class Qwen2Model:
         h = norm(x, self.layers[0].ln1, eps)
         scale = hd ** -0.5
         for i, layer in enumerate(self.layers):
-            if skinny_qkv:
+            if thin_qkv:
+                q = thin_gemm(h, layer.qkv_w, layer.qkv_b, epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=paged.k[i],
+                              v_cache=paged.v[i], slots=meta.slot_mapping, n_heads=nh, n_kv_heads=nkv)
+            elif skinny_qkv:
                 q = skinny_gemm(h, layer.qkv_w, layer.qkv_b, split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin,
                                 k_cache=paged.k[i], v_cache=paged.v[i], slots=meta.slot_mapping, n_heads=nh, n_kv_heads=nkv)
             else:
@@ -388,7 +397,9 @@ class Qwen2Model:
                                        n_seqs=meta.n_seqs, table_rows=meta.table_rows, workspace=meta.workspace,
                                        planned=True)
             o2 = o.view(T, nh * hd)
-            if stream_o:
+            if thin_o:
+                a = thin_gemm(o2, layer.o_w)
+            elif stream_o:
                 a = stream_gemm(o2, layer.o_w)
             else:
                 a = skinny_gemm(o2, layer.o_w, split_k=8) if skinny_o else F.linear(o2, layer.o_w)

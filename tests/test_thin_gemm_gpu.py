@@ -1,0 +1,83 @@
+"""Narrow decode GEMM (ns_thin_gemm: eight weight rows per CTA, no split over K across CTAs) vs the unfused oracle ops:
+F.linear in fp32 on the same bf16 values rounded to bf16, then the token-wise op of the oracle. Tolerance as for the
+other decode GEMMs: K products are summed in another order than on the CPU, so a bf16 result may differ by one ulp at a
+rounding boundary; stated bound 2e-2 max-abs on O(1) values and >= 98 % of the elements bitwise equal."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+
+def lin(x, w, b=None):
+    y = F.linear(x.float(), w.float(), None if b is None else b.float())
+    return y.to(torch.bfloat16)
+
+
+def close(got, want, min_same=0.98):
+    got, want = got.cpu(), want.cpu()
+    assert got.shape == want.shape
+    same = (got == want).float().mean().item()
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 and same >= min_same, (err, same)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(896, 896), (1152, 896), (200, 256), (1536, 1536), (8, 128)])
+def test_plain_gemm_with_and_without_bias(M, N, K):
+    from nanoserve_b200.kernels.fused import thin_gemm, thin_gemm_supported
+    if not thin_gemm_supported(M, N, K):
+        pytest.skip("shape outside the kernel's shared-memory budget")
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.03).to(torch.bfloat16)
+    b = torch.randn(N, generator=g).to(torch.bfloat16)
+    close(thin_gemm(x.cuda(), w.cuda()), lin(x, w))
+    close(thin_gemm(x.cuda(), w.cuda(), b.cuda()), lin(x, w, b))
+
+
+@pytest.mark.parametrize("M", [3, 16, 32, 48, 64])
+def test_qkv_rope_kv_write_epilogue(M):
+    from nanoserve_b200.kernels.fused import EPI_ROPE_KV, thin_gemm
+    g = torch.Generator().manual_seed(100 + M)
+    H, NH, NKV, HD = 896, 14, 2, 64
+    h = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn((NH + 2 * NKV) * HD, H, generator=g) * 0.03).to(torch.bfloat16)
+    b = torch.randn((NH + 2 * NKV) * HD, generator=g).to(torch.bfloat16)
+    cos, sin = O.rope_cos_sin(torch.randint(0, 4000, (M,), generator=g), HD, 1_000_000.0, torch.bfloat16)
+    slots = torch.randperm(16 * 16, generator=g)[:M]
+    kc = torch.zeros(16, 16, NKV, HD, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q = thin_gemm(h.cuda(), w.cuda(), b.cuda(), epilogue=EPI_ROPE_KV, cos=cos.cuda(), sin=sin.cuda(), k_cache=kc, v_cache=vc,
+                  slots=slots.cuda(), n_heads=NH, n_kv_heads=NKV)
+    rq, rk, rv = O.rope_qkv(lin(h, w, b), cos, sin, NH, NKV, HD)
+    close(q, rq, min_same=0.97)
+    fk, fv = kc.view(-1, NKV, HD).cpu(), vc.view(-1, NKV, HD).cpu()
+    close(fk[slots], rk, min_same=0.97)
+    close(fv[slots], rv, min_same=0.97)
+    untouched = torch.ones(16 * 16, dtype=torch.bool)
+    untouched[slots] = False
+    assert not fk[untouched].any() and not fv[untouched].any()        # nothing written outside the step's slots
+
+
+def test_same_result_as_the_split_k_kernel_up_to_summation_order():
+    from nanoserve_b200.kernels.fused import skinny_gemm, thin_gemm
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(32, 896, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(896, 896, generator=g) * 0.03).to(torch.bfloat16).cuda()
+    close(thin_gemm(x, w), skinny_gemm(x, w, split_k=8), min_same=0.97)
+
+
+def test_rejects_what_it_cannot_run():
+    from nanoserve_b200._lib import NanoserveB200Error
+    from nanoserve_b200.kernels.fused import thin_gemm
+    x = torch.zeros(65, 896, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(896, 896, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NanoserveB200Error):
+        thin_gemm(x, w)                                   # more than 64 rows
+    with pytest.raises(NanoserveB200Error):
+        thin_gemm(x[:4, :64].contiguous(), w[:, :64].contiguous())      # K not a multiple of 128
+    with pytest.raises(NanoserveB200Error):
+        thin_gemm(torch.zeros(64, 3584, dtype=torch.bfloat16, device="cuda"), torch.zeros(8, 3584, dtype=torch.bfloat16, device="cuda"))
