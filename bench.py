@@ -392,7 +392,7 @@ def layer_probe(rows: int) -> None:
     import torch.nn.functional as F
     from nanoserve_b200 import _lib
     from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
-                                              stream_gemm, swiglu_gemm, thin_gemm)
+                                              stream_gemm, swiglu_gemm, thin_gemm, thin_swiglu_gemm)
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
     from nanoserve_b200.synthetic import attention_workload
     M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
@@ -431,6 +431,8 @@ def layer_probe(rows: int) -> None:
                 m = silu_mul(F.linear(h, l["gu"]))
             elif gu == "umma":
                 m = swiglu_gemm(h, l["gu"])
+            elif gu == "thin":
+                m = thin_swiglu_gemm(h, l["gu"])
             else:
                 m = stream_gemm(h, l["gu"], epilogue=EPI_SILU_MUL) if gu == "stream" else m0
             d = skinny_gemm(m, l["down"], split_k=8) if down == "skinny" else (F.linear(m, l["down"]) if down == "cublas" else h)
@@ -464,6 +466,8 @@ def layer_probe(rows: int) -> None:
     variants = {"engine chain": dict(qkv="thin", o="thin") if M > 16 else dict(qkv="thin", o="thin", gu="stream"),
                 "qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}, "qkv on thin_gemm": dict(qkv="thin"), "o_proj on thin_gemm": dict(o="thin"),
                 "qkv and o_proj on thin_gemm": dict(qkv="thin", o="thin"),
+                "qkv, o_proj and gate_up on thin_gemm": dict(qkv="thin", o="thin", gu="thin"),
+                "gate_up on thin_gemm": dict(gu="thin"),
                 "qkv and o_proj on thin_gemm, gate_up on stream_gemm": dict(qkv="thin", o="thin", gu="stream"),
                 "qkv on thin_gemm, o_proj and gate_up on stream_gemm": dict(qkv="thin", o="stream", gu="stream"), "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
                 "no qkv": dict(qkv=None), "no o_proj": dict(o=None), "no norm1": dict(norm1=False),

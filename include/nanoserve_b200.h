@@ -105,6 +105,15 @@ int ns_thin_gemm(const void* x, const void* w, const void* bias, void* out, int3
                  int32_t epilogue, const void* cos, const void* sin, void* k_cache, void* v_cache, const int64_t* slots,
                  int32_t n_heads, int32_t n_kv_heads, void* stream);
 
+/* gate/up projection + SiLU*mul for at most 32 token rows (bf16 only), same construction as ns_thin_gemm:
+ *   w = [gate; up] (2*inter rows of K), out[M, inter] = bf16(bf16(silu(bf16(x.gate^T))) * bf16(x.up^T)).
+ * A CTA keeps nine tiles of four gate rows + the matching four up rows and all of x in shared memory (K % 128 == 0,
+ * (72 + M rounded up to 16 or 32) rows of K within 227 KB: K <= 1024); inter % 4 == 0; ceil(inter / 36) CTAs.
+ * x arrives by bulk copies whose bounded wait is counted in ns_thin_gemm_errors when it runs out (0 unless a fault).
+ * Replaces, fused: nanoserve/model.py:256-257 (gate/up F.linear + silu_mul) for steps of at most 32 token rows. */
+int ns_thin_swiglu_gemm(const void* x, const void* w, void* out, int32_t M, int32_t inter, int32_t K, void* stream);
+int ns_thin_gemm_errors(int32_t* count);
+
 /* Persistent weight-streaming GEMM for decode-sized batches (bf16 only):
  *   out = epilogue( prologue(x) . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, N % 16 == 0,
  *   K one of 896, 1024, 1536 (64 token rows only up to K = 1024).

@@ -27,6 +27,8 @@ SIGNATURES: dict[str, tuple] = {
     "ns_skinny_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _F, _I32, _I32, _P, _P, _P, _P, _P, _I32,
                                _I32, _P]),
     "ns_thin_gemm": (c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I32, _I32, _P]),
+    "ns_thin_swiglu_gemm": (c_int, [_P, _P, _P, _I32, _I32, _I32, _P]),
+    "ns_thin_gemm_errors": (c_int, [_P]),
     "ns_stream_gemm": (c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32, _I32, _I32, _F, _I32, _P]),
     "ns_stream_gemm_errors": (c_int, [_P]),
     "ns_swiglu_gemm": (c_int, [_P, _P, _P, _I32, _I32, _I32, _P]),

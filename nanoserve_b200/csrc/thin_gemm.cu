@@ -37,6 +37,36 @@ struct ThinParams {
     int n_heads, n_kv_heads;
 };
 
+__device__ unsigned int g_thin_errors = 0;   // bulk copies that did not land within the bounded wait (never expected)
+
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(mbar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 constexpr int kThinThreads = 128;
 constexpr int kThinRows = 8;          // weight rows per CTA
 
@@ -211,6 +241,179 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
     }
 }
 
+// ---- gate/up + SiLU*mul: nine 8-row tiles per CTA, twelve warps ----------------------------------------------------
+// W = [gate; up] with 2 * inter rows. A tile is FOUR gate rows and the matching four up rows (one mma n-tile), a CTA owns
+// nine consecutive tiles (inter = 4864 -> 1216 tiles -> 136 CTAs: one wave) and keeps their weight rows (130 KB) and all
+// of X in shared memory. Warp w works on K quarter w % 4 - so the four SM sub-partitions carry the same number of mma -
+// for the three tiles 3 * (w / 4) + {0, 1, 2} at once: one set of activation fragments feeds three weight tiles, which
+// keeps shared-memory reads (the bound after the tensor pipe at this shape) at 3.5 KB per 12 mma. The four K quarters of
+// a tile meet in shared memory (the activation rows' space, free by then) and one thread finishes (tile, token row):
+// bf16(gate), bf16(up), SiLU in fp32 rounded to bf16, product rounded to bf16, one 8-byte store.
+constexpr int kSwTiles = 9;
+constexpr int kSwThreads = 384;
+
+template <int MT>
+__global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ out, int M, int K, int inter) {
+    constexpr int MP = 16 * MT;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, grp = warp >> 2;             // K quarter; which three of the CTA's nine tiles
+    const uint32_t pitch = (uint32_t)K * 2 + 16;
+    const uint32_t x_sm = smem_u32(smem);                // [MP][pitch]; later the partial tiles [9][4][MP][8] fp32
+    const uint32_t w_sm = x_sm + MP * pitch;             // [9 * 8][pitch]
+    float* c_sm = reinterpret_cast<float*>(smem);
+    const int n_tiles = inter / 4;
+    const int tile0 = blockIdx.x * kSwTiles + grp * 3;   // this warp's first tile
+    // X arrives by bulk copies (one per token row, issued after the dependency wait) on this barrier: they do not queue
+    // behind the weights' cp.async traffic in the load/store pipe the way ordinary loads of X would
+    __shared__ __align__(8) uint64_t x_bar;
+    const uint32_t mb_x = smem_u32(&x_bar);
+    if (tid == 0) {
+        mbar_init(mb_x, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(mb_x, (uint32_t)M * (uint32_t)K * 2);
+    }
+    __syncthreads();
+    const int qchunks = K / 32;                           // 16-byte chunks in a quarter of a row
+    const uint32_t kbase = (uint32_t)q * (uint32_t)(K / 4) * 2;
+    // This warp's quarter of its three tiles' weight rows, before the dependency wait (they stream while the norm runs),
+    // in the order the k-loop uses them: one commit group per iteration (32 columns = 64 bytes of each of the 24 rows;
+    // lane = (row, 16-byte chunk)), so the loop can start on the first group while the rest is still on its way.
+    const int iters = K / 128;
+    {
+        const int r = lane >> 2, c = lane & 3;
+        const uint8_t* src[3];
+        uint32_t dst[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int gt = min(tile0 + i, n_tiles - 1);   // a tile past the end re-reads the last one; it is never stored
+            const int row = (r < 4 ? 0 : inter) + 4 * gt + (r & 3);
+            src[i] = reinterpret_cast<const uint8_t*>(w + (int64_t)row * K) + kbase + c * 16;
+            dst[i] = w_sm + ((grp * 3 + i) * 8 + r) * pitch + kbase + c * 16;
+        }
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int i = 0; i < 3; ++i) cp_async16(dst[i] + it * 64, src[i] + it * 64, 16);
+            cp_async_commit();
+        }
+    }
+    pdl_wait();
+    if (lane < 3) {                                       // token rows over the twelve warps, up to three copies each
+        const int m = warp + 12 * lane;
+        if (m < M) bulk_g2s(x_sm + m * pitch, x + (int64_t)m * K, (uint32_t)K * 2, mb_x);
+    }
+
+    float acc[3][MT][4];
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) acc[i][mt][0] = acc[i][mt][1] = acc[i][mt][2] = acc[i][mt][3] = 0.f;
+    const uint32_t b_addr = w_sm + (grp * 24 + (lane & 7)) * pitch + kbase + (lane >> 3) * 16;
+    const uint32_t a_addr = x_sm + ((lane & 7) + (((lane >> 3) & 1) << 3)) * pitch + kbase + (lane >> 4) * 16;
+    struct Frag { uint32_t b[3][4]; uint32_t a[2][MT][4]; };
+    auto load_frag = [&](Frag& f, int it) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) ldmatrix_x4(b_addr + i * 8 * pitch + it * 64, f.b[i][0], f.b[i][1], f.b[i][2], f.b[i][3]);
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                ldmatrix_x4(a_addr + 16 * mt * pitch + it * 64 + s * 32, f.a[s][mt][0], f.a[s][mt][1], f.a[s][mt][2], f.a[s][mt][3]);
+    };
+    auto compute = [&](const Frag& f) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(acc[i][mt], f.a[s][mt], f.b[i][2 * s], f.b[i][2 * s + 1]);
+    };
+    // group `it` holds iteration it's weights: at most iters - 1 - it younger groups may still be pending
+    auto wait_for = [&](int it) {
+        switch (iters - 1 - it) {
+            case 0: cp_async_wait<0>(); break;
+            case 1: cp_async_wait<1>(); break;
+            case 2: cp_async_wait<2>(); break;
+            case 3: cp_async_wait<3>(); break;
+            case 4: cp_async_wait<4>(); break;
+            case 5: cp_async_wait<5>(); break;
+            case 6: cp_async_wait<6>(); break;
+            case 7: cp_async_wait<7>(); break;
+            default: break;                               // more than 7 younger groups: this one is waited for later
+        }
+        __syncwarp();
+    };
+    {
+        Frag f0, f1;
+        if (iters > 8) cp_async_wait<7>();                // groups 0 .. iters - 9: the switch above covers the last eight
+        if (!mbar_wait_bounded(mb_x, 0) && lane == 0) atomicAdd(&g_thin_errors, 1u);
+        wait_for(0);
+        load_frag(f0, 0);
+        for (int it = 0; it < iters; it += 2) {
+            if (it + 1 < iters) { wait_for(it + 1); load_frag(f1, it + 1); }
+            compute(f0);
+            if (it + 2 < iters) { wait_for(it + 2); load_frag(f0, it + 2); }
+            if (it + 1 < iters) compute(f1);
+        }
+    }
+    __syncthreads();                                      // every warp is done reading X: its space takes the partial tiles
+    {
+        const int r0 = lane >> 2, cp = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            float* mine = c_sm + ((size_t)((grp * 3 + i) * 4 + q) * MP) * 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                *reinterpret_cast<float2*>(mine + (16 * mt + r0) * 8 + cp) = make_float2(acc[i][mt][0], acc[i][mt][1]);
+                *reinterpret_cast<float2*>(mine + (16 * mt + r0 + 8) * 8 + cp) = make_float2(acc[i][mt][2], acc[i][mt][3]);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < kSwTiles * MP) {
+        const int lt = tid / MP, row = tid % MP;
+        const int gt = blockIdx.x * kSwTiles + lt;
+        if (row < M && gt < n_tiles) {
+            float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) {              // K quarters in order
+                const float4 a = *reinterpret_cast<const float4*>(c_sm + ((size_t)(lt * 4 + qq) * MP + row) * 8);
+                const float4 b = *reinterpret_cast<const float4*>(c_sm + ((size_t)(lt * 4 + qq) * MP + row) * 8 + 4);
+                g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
+            }
+            float r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float gg = round_to<__nv_bfloat16>(g[j]), uu = round_to<__nv_bfloat16>(u[j]);
+                const float sg = round_to<__nv_bfloat16>(gg / (1.0f + expf(-gg)));
+                r[j] = sg * uu;
+            }
+            uint2 packed;
+            packed.x = pack_bf16x2(r[0], r[1]);
+            packed.y = pack_bf16x2(r[2], r[3]);
+            *reinterpret_cast<uint2*>(out + (int64_t)row * inter + 4 * gt) = packed;
+        }
+    }
+}
+
+template <int MT>
+int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out, int M, int K, int inter, cudaStream_t st) {
+    const size_t smem = (size_t)(16 * MT + kSwTiles * 8) * ((size_t)K * 2 + 16);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(thin_swiglu_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_swiglu_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
+                                          cudaGetErrorString(e));
+        configured = smem;
+    }
+    const int grid = (inter / 4 + kSwTiles - 1) / kSwTiles;
+    cudaError_t e = launch_pdl(thin_swiglu_kernel<MT>, dim3((unsigned)grid), dim3(kSwThreads), smem, st, x, w, out, M, K, inter);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_swiglu_gemm: launch failed: %s", cudaGetErrorString(e));
+    return NS_OK;
+}
+
 template <int MT, int EPI>
 int launch_thin(const ThinParams& p, int tiles, cudaStream_t st) {
     const size_t smem = (size_t)(kThinRows + 16 * MT) * ((size_t)p.K * 2 + 16) + (size_t)4 * 16 * MT * 8 * 4;
@@ -265,4 +468,30 @@ extern "C" int ns_thin_gemm(const void* x, const void* w, const void* bias, void
         return dispatch_thin<kThinRopeKv>(p, N / kThinRows, st);
     }
     return fail(NS_ERR_INVALID_ARG, "thin_gemm: unknown epilogue %d (0 = bias, 2 = RoPE + KV write)", epilogue);
+}
+
+extern "C" int ns_thin_swiglu_gemm(const void* x, const void* w, void* out, int32_t M, int32_t inter, int32_t K, void* stream) {
+    NS_REQUIRE(M >= 0 && inter > 0 && K > 0, NS_ERR_INVALID_ARG, "thin_swiglu_gemm: bad shape");
+    if (M == 0) return NS_OK;
+    NS_REQUIRE(x && w && out, NS_ERR_INVALID_ARG, "thin_swiglu_gemm: null pointer");
+    NS_REQUIRE(M <= 32, NS_ERR_UNSUPPORTED, "thin_swiglu_gemm: %d token rows > 32", M);
+    NS_REQUIRE(K % 128 == 0 && inter % 4 == 0, NS_ERR_UNSUPPORTED, "thin_swiglu_gemm: K=%d must be a multiple of 128 and inter=%d of 4", K, inter);
+    NS_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0,
+               NS_ERR_INVALID_ARG, "thin_swiglu_gemm: x / w must be 16-byte aligned, out 8-byte aligned");
+    const int mp = M <= 16 ? 16 : 32;
+    const size_t smem = (size_t)(mp + kSwTiles * 8) * ((size_t)K * 2 + 16);
+    NS_REQUIRE(smem <= 227 * 1024 && (size_t)kSwTiles * 4 * mp * 8 * 4 <= (size_t)mp * ((size_t)K * 2 + 16), NS_ERR_UNSUPPORTED,
+               "thin_swiglu_gemm: K=%d does not fit shared memory (72 weight rows + %d token rows)", K, mp);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M <= 16) return launch_thin_swiglu<1>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
+    return launch_thin_swiglu<2>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
+}
+
+extern "C" int ns_thin_gemm_errors(int32_t* count) {
+    NS_REQUIRE(count != nullptr, NS_ERR_INVALID_ARG, "thin_gemm_errors: null pointer");
+    unsigned int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_thin_errors, sizeof(v));
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_gemm_errors: %s", cudaGetErrorString(e));
+    *count = (int32_t)v;
+    return NS_OK;
 }

@@ -162,6 +162,38 @@ def thin_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
     return out
 
 
+def thin_swiglu_gemm_supported(M: int, inter: int, K: int) -> bool:
+    """Shapes ns_thin_swiglu_gemm takes: at most 32 rows, K % 128 == 0, inter % 4 == 0, 72 weight rows plus the padded
+    token rows of K columns within 227 KB of shared memory, and at most one wave of CTAs (148)."""
+    if not (0 < M <= 32 and K % 128 == 0 and inter % 4 == 0):
+        return False
+    mp = 16 if M <= 16 else 32
+    pitch = 2 * K + 16
+    return (mp + 72) * pitch <= 227 * 1024 and 9 * 4 * mp * 32 <= mp * pitch and -(-(inter // 4) // 9) <= 148
+
+
+def thin_swiglu_gemm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """SiLU(x @ gate^T) * (x @ up^T) for x[M<=32, K] and w = [gate; up] ([2*inter, K]) in one kernel
+    (ns_thin_swiglu_gemm in the header); returns [M, inter]."""
+    _lib.require_cuda(x, w)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] % 2 == 0
+    M, K = x.shape
+    inter = w.shape[0] // 2
+    out = torch.empty(M, inter, device=x.device, dtype=x.dtype)
+    _lib.call("ns_thin_swiglu_gemm", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, inter, K, _lib.stream_ptr())
+    return out
+
+
+def thin_gemm_errors() -> int:
+    """Bulk copies of ns_thin_swiglu_gemm that did not land within the kernel's bounded wait since the library was
+    loaded (synchronises; 0 unless the device faulted)."""
+    import ctypes
+    n = ctypes.c_int32(0)
+    _lib.call("ns_thin_gemm_errors", ctypes.addressof(n))
+    return int(n.value)
+
+
 STREAM_KS = (896, 1024, 1536)
 
 

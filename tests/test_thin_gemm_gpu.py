@@ -81,3 +81,28 @@ def test_rejects_what_it_cannot_run():
         thin_gemm(x[:4, :64].contiguous(), w[:, :64].contiguous())      # K not a multiple of 128
     with pytest.raises(NanoserveB200Error):
         thin_gemm(torch.zeros(64, 3584, dtype=torch.bfloat16, device="cuda"), torch.zeros(8, 3584, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 17, 24, 32])
+@pytest.mark.parametrize("inter,K", [(4864, 896), (100, 128), (36 * 5 + 8, 256), (4864, 1024)])
+def test_gate_up_silu_mul(M, inter, K):
+    from nanoserve_b200.kernels.fused import thin_swiglu_gemm, thin_swiglu_gemm_supported
+    if not thin_swiglu_gemm_supported(M, inter, K):
+        pytest.skip("shape outside the kernel's shared-memory budget")
+    g = torch.Generator().manual_seed(M * 7 + inter)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, generator=g) * 0.02).to(torch.bfloat16)
+    close(thin_swiglu_gemm(x.cuda(), w.cuda()), O.silu_mul(lin(x, w)), min_same=0.97)
+    from nanoserve_b200.kernels.fused import thin_gemm_errors
+    assert thin_gemm_errors() == 0
+
+
+def test_gate_up_rejects_what_it_cannot_run():
+    from nanoserve_b200._lib import NanoserveB200Error
+    from nanoserve_b200.kernels.fused import thin_swiglu_gemm
+    w = torch.zeros(2 * 4864, 896, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NanoserveB200Error):
+        thin_swiglu_gemm(torch.zeros(33, 896, dtype=torch.bfloat16, device="cuda"), w)          # more than 32 rows
+    with pytest.raises(NanoserveB200Error):
+        thin_swiglu_gemm(torch.zeros(8, 1536, dtype=torch.bfloat16, device="cuda"),
+                         torch.zeros(2 * 64, 1536, dtype=torch.bfloat16, device="cuda"))             # K too wide for shared memory
