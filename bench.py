@@ -474,7 +474,13 @@ def layer_probe(rows: int) -> None:
                 "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": dict(gu="umma"),
                 "o_proj on stream_gemm, gate_up on swiglu_gemm": dict(o="stream", gu="umma"),
                 "o_proj and gate_up on stream_gemm": dict(o="stream", gu="stream")}
-    out = {"rows": M, "us_per_layer": {k: us_per_layer(**kw) for k, kw in variants.items()}}
+    def try_variant(kw):
+        try:
+            return us_per_layer(**kw)
+        except Exception as e:       # a kernel that does not take this row count
+            torch.cuda.synchronize()
+            return f"n/a ({type(e).__name__})"
+    out = {"rows": M, "us_per_layer": {k: try_variant(kw) for k, kw in variants.items()}}
     hook = _lib.load().ns_debug_min_blocks
     hook.argtypes, hook.restype = [ctypes.c_int], None
     sweep = {}

@@ -110,22 +110,24 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     // barrier for the activations, one per warp for its own 16 weight rows. ~100 copy instructions per CTA.
     __shared__ __align__(8) uint64_t mbars[5];
     const uint32_t mb_a = smem_u32(&mbars[4]), mb_w = smem_u32(&mbars[warp]);
+    const uint32_t row_bytes = (uint32_t)ks * 2;
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < 5; ++i) mbar_init(smem_u32(&mbars[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the byte counts are known now; every copy that completes on these barriers is issued after the barrier below
+        for (int i = 0; i < 4; ++i) {
+            int valid = 0;
+            for (int r = 0; r < 16; ++r) valid += w_row(16 * i + r) < p.N;
+            mbar_expect_tx(smem_u32(&mbars[i]), valid * row_bytes);
+        }
+        if (p.ln_w == nullptr) mbar_expect_tx(mb_a, (uint32_t)p.M * row_bytes);
     }
     __syncthreads();
     cluster_arrive();                                   // "this CTA runs": peers wait for it before they store into c_sm
-    const uint32_t row_bytes = (uint32_t)ks * 2;
     const uint32_t my_w = smem_u32(w_sm) + (uint32_t)(16 * warp) * a_stride;
     {
         // this warp's weight rows
-        int valid = 0;
-#pragma unroll
-        for (int r = 0; r < 16; ++r) valid += w_row(16 * warp + r) < p.N;
-        if (lane == 0) mbar_expect_tx(mb_w, valid * row_bytes);
-        __syncwarp();
         if (lane < 16) {
             const int wr = w_row(16 * warp + lane);
             if (wr < p.N) {
@@ -137,19 +139,12 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
         }
     }
     pdl_wait();        // everything above touched only weights; the activations come from the preceding kernel
-    if (p.ln_w == nullptr && warp == 0) {
-        // plain activations: bulk copies of the valid rows, zeros for the padding rows
-        if (lane == 0) mbar_expect_tx(mb_a, (uint32_t)p.M * row_bytes);
-        __syncwarp();
+    if (p.ln_w == nullptr && lane < 8) {
+        // plain activations: bulk copies of the valid rows, spread over the four warps (a bulk copy costs its issuing
+        // lane ~100 cycles, one lane after the other: 32 copies from one warp were 1 us on the critical path). Padding
+        // rows stay unwritten: they only feed rows of the result that are never stored.
         const uint32_t ab = smem_u32(a_sm);
-        for (int m = lane; m < MP; m += 32) {
-            if (m < p.M) {
-                bulk_g2s(ab + m * a_stride, p.x + (int64_t)m * p.K + k0, row_bytes, mb_a);
-            } else {
-                for (uint32_t c = 0; c < row_bytes; c += 16)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(ab + m * a_stride + c), "r"(0) : "memory");
-            }
-        }
+        for (int m = warp + 4 * lane; m < p.M; m += 32) bulk_g2s(ab + m * a_stride, p.x + (int64_t)m * p.K + k0, row_bytes, mb_a);
     }
 
     // ---- activations of this K-slice into shared memory --------------------------------------------------------
@@ -206,24 +201,30 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     bool landed = mbar_wait_bounded(mb_w, 0);
     if (p.ln_w == nullptr) landed = mbar_wait_bounded(mb_a, 0) && landed;
     if (landed) {
-#pragma unroll 4
-        for (int kk = 0; kk < ks / 16; ++kk) {
-            const int kcol = kk * 16;                    // k offset inside the slice
-            uint32_t b00, b01, b10, b11;
-            {
-                const int row = (lane & 7) + ((lane >> 4) << 3);
-                const int kbyte = (kcol + (((lane >> 3) & 1) << 3)) * 2;
-                ldmatrix_x4(my_w + row * a_stride + kbyte, b00, b01, b10, b11);
-            }
+        // fragments one k-step ahead of the mma that use them (ldmatrix -> mma back to back was ~100 cycles per k-step)
+        struct Frag { uint32_t b[4]; uint32_t a[MT][4]; };
+        const uint32_t b_addr = my_w + ((lane & 7) + ((lane >> 4) << 3)) * a_stride + (((lane >> 3) & 1) << 3) * 2;
+        const uint32_t a_addr = a_base + ((lane & 7) + (((lane >> 3) & 1) << 3)) * a_stride + ((lane >> 4) << 3) * 2;
+        auto load_frag = [&](Frag& f, int kk) {
+            ldmatrix_x4(b_addr + kk * 32, f.b[0], f.b[1], f.b[2], f.b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a_addr + 16 * mt * a_stride + kk * 32, f.a[mt][0], f.a[mt][1], f.a[mt][2], f.a[mt][3]);
+        };
+        auto compute = [&](const Frag& f) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                uint32_t a[4];
-                const int row = 16 * mt + (lane & 7) + (((lane >> 3) & 1) << 3);
-                const int kbyte = (kcol + ((lane >> 4) << 3)) * 2;
-                ldmatrix_x4(a_base + row * a_stride + kbyte, a[0], a[1], a[2], a[3]);
-                mma_bf16_16816(acc[mt][0], a, b00, b01);
-                mma_bf16_16816(acc[mt][1], a, b10, b11);
+                mma_bf16_16816(acc[mt][0], f.a[mt], f.b[0], f.b[1]);
+                mma_bf16_16816(acc[mt][1], f.a[mt], f.b[2], f.b[3]);
             }
+        };
+        const int ksteps = ks / 16;
+        Frag f0, f1;
+        load_frag(f0, 0);
+        for (int kk = 0; kk < ksteps; kk += 2) {
+            if (kk + 1 < ksteps) load_frag(f1, kk + 1);
+            compute(f0);
+            if (kk + 2 < ksteps) load_frag(f0, kk + 2);
+            if (kk + 1 < ksteps) compute(f1);
         }
     }
 
@@ -232,6 +233,8 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     // into a peer's shared memory are one-way, so the only cluster barrier on the critical path is the one between the
     // stores and the sums; the first barrier (every CTA of the cluster is running) was arrived at before the loads.
     const int rpr = (MP + csize - 1) / csize;           // receive rows per rank
+    const bool pow2 = (csize & (csize - 1)) == 0;       // 1, 2, 4, 8: shifts instead of divisions
+    const int cshift = __ffs(csize) - 1;
     cluster_wait();
     {
         const int r0 = lane >> 2, cp = (lane & 3) * 2;
@@ -241,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
             for (int half = 0; half < 2; ++half) {
                 const int m = 16 * mt + r0 + 8 * half;
                 if (m >= p.M) continue;
-                const int owner = m % csize, slot = m / csize;
+                const int owner = pow2 ? (m & (csize - 1)) : m % csize, slot = pow2 ? (m >> cshift) : m / csize;
                 float* dst = cluster.map_shared_rank(c_sm, owner) + ((size_t)rank * rpr + slot) * kBN + 16 * warp + cp;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
@@ -251,9 +254,8 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     cluster_arrive();
     cluster_wait();
     // sum the partial rows in rank order (deterministic), then the epilogue
-    for (int m = rank; m < p.M; m += csize) {
-        const int slot = (m - rank) / csize;
-        if (slot % (kGemmThreads / 32) != warp) continue;          // each warp takes one row of this rank's share at a time
+    for (int slot = warp; rank + slot * csize < p.M; slot += kGemmThreads / 32) {          // each warp one row at a time
+        const int m = rank + slot * csize;
         float lo = 0.f, hi = 0.f;                       // columns lane and lane + 32 of the tile
 #pragma unroll 8
         for (int r = 0; r < csize; ++r) {

@@ -331,7 +331,8 @@ class Qwen2Model:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
         from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
                                                   rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
-                                                  swiglu_gemm_supported, thin_gemm, thin_gemm_supported)
+                                                  swiglu_gemm_supported, thin_gemm, thin_gemm_supported, thin_swiglu_gemm,
+                                                  thin_swiglu_gemm_supported)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
@@ -364,6 +365,7 @@ class Qwen2Model:
         thin_qkv = (skinny and hd == 64 and bool(mask & 64) and (nh + 2 * nkv) * hd // 8 <= 148 and
                     thin_gemm_supported(T, (nh + 2 * nkv) * hd, hidden))
         thin_o = skinny and bool(mask & 128) and hidden // 8 <= 148 and thin_gemm_supported(T, hidden, nh * hd)
+        thin_gu = skinny and bool(mask & 256) and thin_swiglu_gemm_supported(T, inter, hidden)      # bit 8: gate/up + SiLU*mul
         # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's
         # attention: it runs on a second stream next to the RoPE tables, the embedding, the first norm and the first QKV
         # GEMM (inside a capture this becomes a fork and a join in the graph).
@@ -405,7 +407,9 @@ class Qwen2Model:
                 a = skinny_gemm(o2, layer.o_w, split_k=8) if skinny_o else F.linear(o2, layer.o_w)
             a = self._all_reduce(a)
             h, x = norm(a, layer.ln2, eps, residual=x)
-            if umma_gu:
+            if thin_gu:
+                m = thin_swiglu_gemm(h, layer.gate_up_w)
+            elif umma_gu:
                 m = swiglu_gemm(h, layer.gate_up_w)
             elif stream_gu:
                 m = stream_gemm(h, layer.gate_up_w, epilogue=EPI_SILU_MUL)
