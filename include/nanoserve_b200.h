@@ -91,14 +91,15 @@ int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* 
 
 /* Narrow GEMM for decode-sized batches without a split over K across CTAs (bf16 only):
  *   out = epilogue( x . w^T ),  x: [M <= 64, K], w: [N, K] row-major, fp32 accumulation, K % 128 == 0, N % 8 == 0,
- *   (8 + M rounded up to 16, 32 or 64) rows of K must fit shared memory (K <= 1536 at 64 rows, <= 2688 at 32).
- * One CTA per eight weight rows over all of K: a GEMM with N around 1000 is one CTA per SM; the weight rows are
+ *   (8 or 16 + M rounded up to 16, 32 or 64) rows of K must fit 220 KB of shared memory.
+ * One CTA per eight weight rows over all of K (sixteen where N / 8 > 148 and N % 16 == 0, so that the grid stays one
+ * wave of a 148-SM part): a GEMM with N around 1000 is one CTA per SM; the weight rows are
  * requested before the kernel waits for its predecessor in the stream, every CTA then fetches all of x (16-byte
  * cp.async copies, each warp its own quarter of K), and the four warps' partial tiles are summed through shared
  * memory in a fixed order. No cluster, no barrier a thread could wait on beyond __syncthreads.
  * epilogue 0: out[M, N] = bf16(acc + bias) (bias may be NULL);
- * epilogue 2: as ns_skinny_gemm's epilogue 2 (merged QKV of 64-wide heads: bias, RoPE, q to out, k / v into one
- *   layer's paged pool at slots[m]).
+ * epilogue 2: as ns_skinny_gemm's epilogue 2 (merged QKV: bias, RoPE, q to out, k / v into one layer's paged pool
+ *   at slots[m]) for heads of 64 or 128 (head_dim = N / (n_heads + 2 * n_kv_heads); cos / sin are [M, head_dim]).
  * Replaces, fused: nanoserve/model.py:231 (merged QKV F.linear + rope_qkv with the KV write) and :256 (o_proj) for
  * steps of at most 64 token rows. */
 int ns_thin_gemm(const void* x, const void* w, const void* bias, void* out, int32_t M, int32_t N, int32_t K,

@@ -34,7 +34,7 @@ struct ThinParams {
     __nv_bfloat16* v_cache;
     const int64_t* slots;            // kThinRopeKv: [M]
     int M, N, K;
-    int n_heads, n_kv_heads;
+    int n_heads, n_kv_heads, head_dim;
 };
 
 __device__ unsigned int g_thin_errors = 0;   // bulk copies that did not land within the bounded wait (never expected)
@@ -70,33 +70,38 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
 constexpr int kThinThreads = 128;
 constexpr int kThinRows = 8;          // weight rows per CTA
 
-template <int MT, int EPI>
+template <int MT, int NT, int EPI>
 __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParams p) {
     constexpr int MP = 16 * MT;                          // padded token rows
-    constexpr int PASSES = MT >= 2 ? MT / 2 : 1;         // epilogue: MP * 4 (row, column pair) items over 128 threads
+    constexpr int R = kThinRows * NT;                    // weight rows per CTA: NT mma n-tiles
+    constexpr int ITEMS = MP * 4 * NT;                   // epilogue items (n-tile, token row, column pair)
+    constexpr int PASSES = (ITEMS + kThinThreads - 1) / kThinThreads;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x;
     const uint32_t pitch = (uint32_t)p.K * 2 + 16;       // bytes per row in shared memory (+16: ldmatrix without conflicts)
-    const uint32_t w_sm = smem_u32(smem);                // [8][pitch]
-    const uint32_t x_sm = w_sm + kThinRows * pitch;      // [MP][pitch] (rows >= M stay unwritten: they only feed rows
+    const uint32_t w_sm = smem_u32(smem);                // [R][pitch]
+    const uint32_t x_sm = w_sm + R * pitch;              // [MP][pitch] (rows >= M stay unwritten: they only feed rows
                                                          // of the result that are never stored)
-    float* c_sm = reinterpret_cast<float*>(smem + (size_t)(kThinRows + MP) * pitch);      // [4 warps][MP][8] fp32
+    float* c_sm = reinterpret_cast<float*>(smem + (size_t)(R + MP) * pitch);      // [4 warps][NT][MP][8] fp32
 
     pdl_launch_dependents();
-    // weight row of the CTA's local row t
-    int head = 0, sub = 0;
-    if (EPI == kThinRopeKv) { head = tile >> 3; sub = tile & 7; }
-    auto w_row = [&](int t) -> int {
-        if (EPI == kThinRopeKv) return head * 64 + (t < 4 ? 0 : 32) + sub * 4 + (t & 3);
-        return tile * kThinRows + t;
+    // RoPE epilogue: n-tile g = tile * NT + nt is rows [4 sub, 4 sub + 4) of a head's first half + the matching four of
+    // its second half; a head has head_dim / 8 such tiles
+    const int half = p.head_dim >> 1, per_head = p.head_dim >> 3;
+    auto w_row = [&](int t) -> int {                     // weight row of the CTA's local row t
+        if (EPI == kThinRopeKv) {
+            const int g = tile * NT + (t >> 3), head = g / per_head, sub = g - head * per_head;
+            return head * p.head_dim + ((t & 4) ? half : 0) + sub * 4 + (t & 3);
+        }
+        return tile * R + t;
     };
     const int qchunks = p.K / 32;                         // 16-byte chunks in a warp's quarter of a row
     const uint32_t kbase = (uint32_t)warp * (uint32_t)(p.K / 4) * 2;      // byte offset of this warp's K range in a row
-    // this warp's quarter of the eight weight rows: lane = chunk column, one copy per row
+    // this warp's quarter of the weight rows: lane = chunk column, one copy per row
     for (int cc = lane; cc < qchunks; cc += 32) {
 #pragma unroll
-        for (int t = 0; t < kThinRows; ++t)
+        for (int t = 0; t < R; ++t)
             cp_async16(w_sm + t * pitch + kbase + cc * 16, reinterpret_cast<const uint8_t*>(p.w + (int64_t)w_row(t) * p.K) + kbase + cc * 16, 16);
     }
     cp_async_commit();
@@ -115,48 +120,51 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
     int64_t e_slot[PASSES];
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
-        const int idx = tid + ps * kThinThreads, row = idx >> 2, j = idx & 3;
+        const int idx = tid + ps * kThinThreads, j = idx & 3, row = (idx >> 2) & (MP - 1), nt = idx / (4 * MP);
         e_bias[ps][0] = e_bias[ps][1] = __float2bfloat16_rn(0.f);
         e_cos[ps][0] = e_cos[ps][1] = __float2bfloat16_rn(1.f);
         e_sin[ps][0] = e_sin[ps][1] = __float2bfloat16_rn(0.f);
         e_slot[ps] = 0;
-        if (row >= p.M || idx >= MP * 4) continue;
+        if (row >= p.M || idx >= ITEMS) continue;
         if (EPI == kThinBias) {
             if (p.bias) {
-                e_bias[ps][0] = p.bias[tile * kThinRows + 2 * j];
-                e_bias[ps][1] = p.bias[tile * kThinRows + 2 * j + 1];
+                e_bias[ps][0] = p.bias[tile * R + nt * 8 + 2 * j];
+                e_bias[ps][1] = p.bias[tile * R + nt * 8 + 2 * j + 1];
             }
         } else {
-            const int d = sub * 4 + j;                    // rotation pair (d, d + 32) of the head
+            const int g = tile * NT + nt, head = g / per_head, d = (g - head * per_head) * 4 + j;   // rotation pair (d, d + half)
             if (p.bias) {
-                e_bias[ps][0] = p.bias[head * 64 + d];
-                e_bias[ps][1] = p.bias[head * 64 + 32 + d];
+                e_bias[ps][0] = p.bias[head * p.head_dim + d];
+                e_bias[ps][1] = p.bias[head * p.head_dim + half + d];
             }
             if (head < p.n_heads + p.n_kv_heads) {
-                e_cos[ps][0] = p.cos[row * 64 + d];
-                e_cos[ps][1] = p.cos[row * 64 + 32 + d];
-                e_sin[ps][0] = p.sin[row * 64 + d];
-                e_sin[ps][1] = p.sin[row * 64 + 32 + d];
+                e_cos[ps][0] = p.cos[row * p.head_dim + d];
+                e_cos[ps][1] = p.cos[row * p.head_dim + half + d];
+                e_sin[ps][0] = p.sin[row * p.head_dim + d];
+                e_sin[ps][1] = p.sin[row * p.head_dim + half + d];
             }
             if (head >= p.n_heads) e_slot[ps] = p.slots[row];
         }
     }
 
     // ---- main loop: warp w owns K / 4 of every row; two k-steps (32 columns) per iteration, fragments one iteration
-    // ahead; the two k-steps of an iteration accumulate into separate sets so four mma chains run side by side
-    float acc[2][MT][4];
+    // ahead; the two k-steps of an iteration accumulate into separate sets so the mma chains run side by side
+    float acc[2][MT][NT][4];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) acc[s][mt][0] = acc[s][mt][1] = acc[s][mt][2] = acc[s][mt][3] = 0.f;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) acc[s][mt][nt][0] = acc[s][mt][nt][1] = acc[s][mt][nt][2] = acc[s][mt][nt][3] = 0.f;
     const int iters = p.K / 128;                          // per warp
-    // B: one ldmatrix.x4 = rows 0..7 x columns [0,8) [8,16) [16,24) [24,32) of the iteration
+    // B: per n-tile one ldmatrix.x4 = rows 0..7 x columns [0,8) [8,16) [16,24) [24,32) of the iteration
     const uint32_t b_addr = w_sm + (lane & 7) * pitch + kbase + (lane >> 3) * 16;
     // A: per m-tile and k-step one ldmatrix.x4 (rows 0..7 / 8..15 x columns [0,8) / [8,16))
     const uint32_t a_addr = x_sm + ((lane & 7) + (((lane >> 3) & 1) << 3)) * pitch + kbase + (lane >> 4) * 16;
-    struct Frag { uint32_t b[4]; uint32_t a[2][MT][4]; };
+    struct Frag { uint32_t b[NT][4]; uint32_t a[2][MT][4]; };
     auto load_frag = [&](Frag& f, int it) {
-        ldmatrix_x4(b_addr + it * 64, f.b[0], f.b[1], f.b[2], f.b[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) ldmatrix_x4(b_addr + nt * 8 * pitch + it * 64, f.b[nt][0], f.b[nt][1], f.b[nt][2], f.b[nt][3]);
 #pragma unroll
         for (int s = 0; s < 2; ++s)
 #pragma unroll
@@ -167,7 +175,9 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
 #pragma unroll
         for (int s = 0; s < 2; ++s)
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(acc[s][mt], f.a[s][mt], f.b[2 * s], f.b[2 * s + 1]);
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(acc[s][mt][nt], f.a[s][mt], f.b[nt][2 * s], f.b[nt][2 * s + 1]);
     };
     cp_async_wait<0>();                                   // this warp's own copies: nobody else reads them
     __syncwarp();
@@ -185,58 +195,61 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
     // ---- the four warps' partial tiles meet in shared memory -----------------------------------------------------
     {
         const int r0 = lane >> 2, cp = (lane & 3) * 2;
-        float* mine = c_sm + (size_t)warp * MP * 8;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            *reinterpret_cast<float2*>(mine + (16 * mt + r0) * 8 + cp) =
-                make_float2(acc[0][mt][0] + acc[1][mt][0], acc[0][mt][1] + acc[1][mt][1]);
-            *reinterpret_cast<float2*>(mine + (16 * mt + r0 + 8) * 8 + cp) =
-                make_float2(acc[0][mt][2] + acc[1][mt][2], acc[0][mt][3] + acc[1][mt][3]);
+        for (int nt = 0; nt < NT; ++nt) {
+            float* mine = c_sm + (size_t)(warp * NT + nt) * MP * 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                *reinterpret_cast<float2*>(mine + (16 * mt + r0) * 8 + cp) =
+                    make_float2(acc[0][mt][nt][0] + acc[1][mt][nt][0], acc[0][mt][nt][1] + acc[1][mt][nt][1]);
+                *reinterpret_cast<float2*>(mine + (16 * mt + r0 + 8) * 8 + cp) =
+                    make_float2(acc[0][mt][nt][2] + acc[1][mt][nt][2], acc[0][mt][nt][3] + acc[1][mt][nt][3]);
+            }
         }
     }
     __syncthreads();
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
-        const int idx = tid + ps * kThinThreads, row = idx >> 2, j = idx & 3;
-        if (row >= p.M || idx >= MP * 4) continue;
+        const int idx = tid + ps * kThinThreads, j = idx & 3, row = (idx >> 2) & (MP - 1), nt = idx / (4 * MP);
+        if (row >= p.M || idx >= ITEMS) continue;
         if (EPI == kThinBias) {
-            float lo = 0.f, hi = 0.f;                     // columns 2j, 2j + 1 of the tile, summed in warp order
+            float lo = 0.f, hi = 0.f;                     // columns 2j, 2j + 1 of the n-tile, summed in warp order
 #pragma unroll
             for (int wv = 0; wv < 4; ++wv) {
-                const float2 v = *reinterpret_cast<const float2*>(c_sm + ((size_t)wv * MP + row) * 8 + 2 * j);
+                const float2 v = *reinterpret_cast<const float2*>(c_sm + ((size_t)(wv * NT + nt) * MP + row) * 8 + 2 * j);
                 lo += v.x;
                 hi += v.y;
             }
             const uint32_t packed = pack_bf16x2(lo + __bfloat162float(e_bias[ps][0]), hi + __bfloat162float(e_bias[ps][1]));
-            *reinterpret_cast<uint32_t*>(p.out + (int64_t)row * p.N + tile * kThinRows + 2 * j) = packed;
+            *reinterpret_cast<uint32_t*>(p.out + (int64_t)row * p.N + tile * R + nt * 8 + 2 * j) = packed;
         } else {
-            float xl = 0.f, xh = 0.f;                     // columns j (first half) and j + 4 (second half) of the tile
+            float xl = 0.f, xh = 0.f;                     // columns j (first half) and j + 4 (second half) of the n-tile
 #pragma unroll
             for (int wv = 0; wv < 4; ++wv) {
-                xl += c_sm[((size_t)wv * MP + row) * 8 + j];
-                xh += c_sm[((size_t)wv * MP + row) * 8 + 4 + j];
+                xl += c_sm[((size_t)(wv * NT + nt) * MP + row) * 8 + j];
+                xh += c_sm[((size_t)(wv * NT + nt) * MP + row) * 8 + 4 + j];
             }
+            const int g = tile * NT + nt, head = g / per_head, d = (g - head * per_head) * 4 + j;
             xl = round_to<__nv_bfloat16>(xl + __bfloat162float(e_bias[ps][0]));
             xh = round_to<__nv_bfloat16>(xh + __bfloat162float(e_bias[ps][1]));
             if (head < p.n_heads + p.n_kv_heads) {
                 const float cl = __bfloat162float(e_cos[ps][0]), ch = __bfloat162float(e_cos[ps][1]);
                 const float sl = __bfloat162float(e_sin[ps][0]), sh = __bfloat162float(e_sin[ps][1]);
                 const float a = round_to<__nv_bfloat16>(__fmul_rn(xl, cl)), b = round_to<__nv_bfloat16>(__fmul_rn(xh, sl));
-                const float d = round_to<__nv_bfloat16>(__fmul_rn(xh, ch)), e = round_to<__nv_bfloat16>(__fmul_rn(xl, sh));
+                const float dd = round_to<__nv_bfloat16>(__fmul_rn(xh, ch)), e = round_to<__nv_bfloat16>(__fmul_rn(xl, sh));
                 xl = round_to<__nv_bfloat16>(__fadd_rn(a, -b));
-                xh = round_to<__nv_bfloat16>(__fadd_rn(d, e));
+                xh = round_to<__nv_bfloat16>(__fadd_rn(dd, e));
             }
             __nv_bfloat16* dst;
             if (head < p.n_heads) {
-                dst = p.out + ((int64_t)row * p.n_heads + head) * 64;
+                dst = p.out + ((int64_t)row * p.n_heads + head) * p.head_dim;
             } else if (head < p.n_heads + p.n_kv_heads) {
-                dst = p.k_cache + (e_slot[ps] * p.n_kv_heads + (head - p.n_heads)) * 64;
+                dst = p.k_cache + (e_slot[ps] * p.n_kv_heads + (head - p.n_heads)) * p.head_dim;
             } else {
-                dst = p.v_cache + (e_slot[ps] * p.n_kv_heads + (head - p.n_heads - p.n_kv_heads)) * 64;
+                dst = p.v_cache + (e_slot[ps] * p.n_kv_heads + (head - p.n_heads - p.n_kv_heads)) * p.head_dim;
             }
-            const int d = sub * 4 + j;
             dst[d] = __float2bfloat16_rn(xl);
-            dst[d + 32] = __float2bfloat16_rn(xh);
+            dst[d + half] = __float2bfloat16_rn(xh);
         }
     }
 }
@@ -414,25 +427,37 @@ int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bflo
     return NS_OK;
 }
 
-template <int MT, int EPI>
-int launch_thin(const ThinParams& p, int tiles, cudaStream_t st) {
-    const size_t smem = (size_t)(kThinRows + 16 * MT) * ((size_t)p.K * 2 + 16) + (size_t)4 * 16 * MT * 8 * 4;
+// n-tiles per CTA: one while N / 8 CTAs are a single wave of a 148-SM part, else two if that makes them one
+inline int thin_ntiles(int N) { return (N / kThinRows <= 148 || N % (2 * kThinRows) != 0) ? 1 : 2; }
+inline size_t thin_smem(int mp, int nt, int K) {
+    return (size_t)(kThinRows * nt + mp) * ((size_t)K * 2 + 16) + (size_t)4 * nt * mp * 8 * 4;
+}
+
+template <int MT, int NT, int EPI>
+int launch_thin(const ThinParams& p, cudaStream_t st) {
+    const size_t smem = thin_smem(16 * MT, NT, p.K);
     static size_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(thin_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(thin_gemm_kernel<MT, NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
         configured = smem;
     }
-    cudaError_t e = launch_pdl(thin_gemm_kernel<MT, EPI>, dim3((unsigned)tiles), dim3(kThinThreads), smem, st, p);
+    const int tiles = p.N / (kThinRows * NT);
+    cudaError_t e = launch_pdl(thin_gemm_kernel<MT, NT, EPI>, dim3((unsigned)tiles), dim3(kThinThreads), smem, st, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_gemm: launch failed: %s", cudaGetErrorString(e));
     return NS_OK;
 }
 
-template <int EPI> int dispatch_thin(const ThinParams& p, int tiles, cudaStream_t st) {
-    if (p.M <= 16) return launch_thin<1, EPI>(p, tiles, st);
-    if (p.M <= 32) return launch_thin<2, EPI>(p, tiles, st);
-    return launch_thin<4, EPI>(p, tiles, st);
+template <int EPI> int dispatch_thin(const ThinParams& p, cudaStream_t st) {
+    if (thin_ntiles(p.N) == 1) {
+        if (p.M <= 16) return launch_thin<1, 1, EPI>(p, st);
+        if (p.M <= 32) return launch_thin<2, 1, EPI>(p, st);
+        return launch_thin<4, 1, EPI>(p, st);
+    }
+    if (p.M <= 16) return launch_thin<1, 2, EPI>(p, st);
+    if (p.M <= 32) return launch_thin<2, 2, EPI>(p, st);
+    return launch_thin<4, 2, EPI>(p, st);
 }
 
 }  // namespace
@@ -452,20 +477,23 @@ extern "C" int ns_thin_gemm(const void* x, const void* w, const void* bias, void
                    (reinterpret_cast<uintptr_t>(out) & 3) == 0,
                NS_ERR_INVALID_ARG, "thin_gemm: x / w must be 16-byte aligned, out 4-byte aligned");
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    NS_REQUIRE((size_t)(kThinRows + mp) * ((size_t)K * 2 + 16) + (size_t)4 * mp * 8 * 4 <= 220 * 1024, NS_ERR_UNSUPPORTED,
-               "thin_gemm: %d rows of K=%d do not fit shared memory", mp, K);
+    NS_REQUIRE(thin_smem(mp, thin_ntiles(N), K) <= 220 * 1024, NS_ERR_UNSUPPORTED,
+               "thin_gemm: %d token rows + %d weight rows of K=%d do not fit shared memory", mp, kThinRows * thin_ntiles(N), K);
     ThinParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = (const __nv_bfloat16*)bias;
     p.out = (__nv_bfloat16*)out; p.cos = (const __nv_bfloat16*)cos; p.sin = (const __nv_bfloat16*)sin;
     p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache; p.slots = slots;
-    p.M = M; p.N = N; p.K = K; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
+    p.M = M; p.N = N; p.K = K; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (epilogue == kThinBias) return dispatch_thin<kThinBias>(p, N / kThinRows, st);
+    if (epilogue == kThinBias) return dispatch_thin<kThinBias>(p, st);
     if (epilogue == kThinRopeKv) {
-        NS_REQUIRE(n_heads > 0 && n_kv_heads > 0 && N == (n_heads + 2 * n_kv_heads) * 64, NS_ERR_UNSUPPORTED,
-                   "thin_gemm: the RoPE + KV-write epilogue handles head_dim 64 only");
+        NS_REQUIRE(n_heads > 0 && n_kv_heads > 0 && N % (n_heads + 2 * n_kv_heads) == 0, NS_ERR_INVALID_ARG,
+                   "thin_gemm: N is not (n_heads + 2 * n_kv_heads) * head_dim");
+        p.head_dim = N / (n_heads + 2 * n_kv_heads);
+        NS_REQUIRE(p.head_dim == 64 || p.head_dim == 128, NS_ERR_UNSUPPORTED,
+                   "thin_gemm: the RoPE + KV-write epilogue handles head_dim 64 and 128, not %d", p.head_dim);
         NS_REQUIRE(cos && sin && k_cache && v_cache && slots, NS_ERR_INVALID_ARG, "thin_gemm: RoPE epilogue needs cos, sin, caches, slots");
-        return dispatch_thin<kThinRopeKv>(p, N / kThinRows, st);
+        return dispatch_thin<kThinRopeKv>(p, st);
     }
     return fail(NS_ERR_INVALID_ARG, "thin_gemm: unknown epilogue %d (0 = bias, 2 = RoPE + KV write)", epilogue);
 }

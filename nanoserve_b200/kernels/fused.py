@@ -132,13 +132,20 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     return (out, r_out) if want_residual else out
 
 
+def thin_gemm_ctas(N: int) -> int:
+    """CTAs ns_thin_gemm launches for N weight rows: one per 8 rows, or per 16 when that turns more than one wave of a
+    148-SM part into one."""
+    return N // 8 if (N // 8 <= 148 or N % 16) else N // 16
+
+
 def thin_gemm_supported(M: int, N: int, K: int) -> bool:
-    """Shapes ns_thin_gemm takes: at most 64 rows, K % 128 == 0, N % 8 == 0, and 8 weight rows plus the padded token
-    rows of K columns within 220 KB of shared memory."""
+    """Shapes ns_thin_gemm takes: at most 64 rows, K % 128 == 0, N % 8 == 0, and a CTA's weight rows (8 or 16) plus the
+    padded token rows of K columns within 220 KB of shared memory."""
     if not (0 < M <= 64 and K % 128 == 0 and N % 8 == 0):
         return False
     mp = 16 if M <= 16 else (32 if M <= 32 else 64)
-    return (8 + mp) * (2 * K + 16) + 4 * mp * 8 * 4 <= 220 * 1024
+    rows = N // thin_gemm_ctas(N)
+    return (rows + mp) * (2 * K + 16) + 4 * (rows // 8) * mp * 8 * 4 <= 220 * 1024
 
 
 def thin_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, epilogue: int = EPI_BIAS,
@@ -146,15 +153,15 @@ def thin_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
               v_cache: torch.Tensor | None = None, slots: torch.Tensor | None = None, n_heads: int = 0,
               n_kv_heads: int = 0) -> torch.Tensor:
     """Decode-sized narrow GEMM x[M<=64, K] @ w[N, K]^T with eight weight rows per CTA and no split over K across CTAs
-    (ns_thin_gemm in the header). Epilogue EPI_BIAS (bias optional) or EPI_ROPE_KV (merged QKV of 64-wide heads: returns
-    q [M, n_heads, 64]; k and v go to the pool rows slots[m])."""
+    (ns_thin_gemm in the header). Epilogue EPI_BIAS (bias optional) or EPI_ROPE_KV (merged QKV of 64- or 128-wide heads:
+    returns q [M, n_heads, head_dim]; k and v go to the pool rows slots[m])."""
     _lib.require_cuda(x, w, bias, cos, sin, k_cache, v_cache, slots)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     M, K = x.shape
     N = w.shape[0]
     if epilogue == EPI_ROPE_KV:
-        out = torch.empty(M, n_heads, 64, device=x.device, dtype=x.dtype)
+        out = torch.empty(M, n_heads, N // (n_heads + 2 * n_kv_heads), device=x.device, dtype=x.dtype)
     else:
         out = torch.empty(M, N, device=x.device, dtype=x.dtype)
     _lib.call("ns_thin_gemm", x.data_ptr(), w.data_ptr(), _lib.ptr(bias), out.data_ptr(), M, N, K, epilogue, _lib.ptr(cos),
