@@ -98,7 +98,8 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // QKV only: the attention kernel that follows fetches its plan, block ids and older K/V rows while this GEMM runs.
-    // (Not for the other epilogues: a successor that starts streaming ITS weights now would compete with this kernel's.)
+    // (Not for the other epilogues: a successor that starts streaming ITS weights now would compete with this kernel's;
+    // for down_proj, whose successor is the norm kernel, an early trigger measured the same at engine level.)
     if (EPI == kEpiRopeKv) pdl_launch_dependents();
 
     // weight row of the CTA's local row t

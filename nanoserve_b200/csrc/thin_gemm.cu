@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
     float* c_sm = reinterpret_cast<float*>(smem);
     const int n_tiles = inter / 4;
     const int tile0 = blockIdx.x * kSwTiles + grp * 3;   // this warp's first tile
+    pdl_launch_dependents();                              // the next kernel's launch latency passes while this one runs
     // X arrives by bulk copies (one per token row, issued after the dependency wait) on this barrier: they do not queue
     // behind the weights' cp.async traffic in the load/store pipe the way ordinary loads of X would
     __shared__ __align__(8) uint64_t x_bar;

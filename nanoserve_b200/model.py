@@ -351,11 +351,12 @@ class Qwen2Model:
         # the persistent streaming kernel; 5 gate/up on the tcgen05 + TMA kernel; 6 QKV, 7 o_proj on the 8-row-tile kernel
         # without split-K, which wins over bits 1, 2 and 4). Measured inside a decode layer: the streaming kernel pays off
         # for gate/up up to 16 rows (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64); QKV and o_proj
-        # together on the 8-row-tile kernel take 2.9 us off a layer at 32 rows.
+        # together on the 8-row-tile kernel take 2.9 us off a layer at 32 rows; bit 8: gate/up + SiLU*mul on the 8-row-tile
+        # kernel (17..32 rows: +5-7 % tok/s at c=32 over the library GEMM + SiLU kernel).
         if T <= 16:
             mask = int(os.environ.get("NS_SKINNY_MASK_SMALL", os.environ.get("NS_SKINNY_MASK", "219")))
         else:
-            mask = int(os.environ.get("NS_SKINNY_MASK", "195"))
+            mask = int(os.environ.get("NS_SKINNY_MASK", "451"))
         skinny_down = skinny_down and bool(mask & 1)
         skinny_qkv = skinny and hd == 64 and hidden % 128 == 0 and bool(mask & 2)
         skinny_o = skinny and (nh * hd) % 128 == 0 and bool(mask & 4)
