@@ -463,17 +463,17 @@ def layer_probe(rows: int) -> None:
             ts.append(a.elapsed_time(b) * 1e3 / L)
         return round(sorted(ts)[2], 2)
 
-    variants = {"engine chain": dict(qkv="thin", o="thin") if M > 16 else dict(qkv="thin", o="thin", gu="stream"),
-                "qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}, "qkv on thin_gemm": dict(qkv="thin"), "o_proj on thin_gemm": dict(o="thin"),
-                "qkv and o_proj on thin_gemm": dict(qkv="thin", o="thin"),
-                "qkv, o_proj and gate_up on thin_gemm": dict(qkv="thin", o="thin", gu="thin"),
-                "gate_up on thin_gemm": dict(gu="thin"),
-                "qkv and o_proj on thin_gemm, gate_up on stream_gemm": dict(qkv="thin", o="thin", gu="stream"),
-                "qkv on thin_gemm, o_proj and gate_up on stream_gemm": dict(qkv="thin", o="stream", gu="stream"), "no gate_up": dict(gu=None), "no attention": dict(attn=False), "no down": dict(down=None),
-                "no qkv": dict(qkv=None), "no o_proj": dict(o=None), "no norm1": dict(norm1=False),
-                "no norm2": dict(norm2=False), "down on cublas": dict(down="cublas"), "gate_up on stream_gemm": dict(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": dict(gu="umma"),
-                "o_proj on stream_gemm, gate_up on swiglu_gemm": dict(o="stream", gu="umma"),
-                "o_proj and gate_up on stream_gemm": dict(o="stream", gu="stream")}
+    engine = dict(qkv="thin", o="thin", gu="stream" if M <= 16 else ("thin" if M <= 32 else "cublas"))
+    e = lambda **kw: dict(engine, **kw)      # the engine's chain with one kernel removed or swapped
+    variants = {"engine chain": engine,
+                "engine chain again (order effect of the probe)": engine,
+                "no gate_up": e(gu=None), "no attention": e(attn=False), "no down": e(down=None), "no qkv": e(qkv=None),
+                "no o_proj": e(o=None), "no norm1": e(norm1=False), "no norm2": e(norm2=False),
+                "gate_up on cublas + silu kernel": e(gu="cublas"), "gate_up on thin_swiglu": e(gu="thin"),
+                "gate_up on stream_gemm": e(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": e(gu="umma"),
+                "qkv on skinny_gemm (split-K cluster)": e(qkv="skinny"), "o_proj on cublas": e(o="cublas"),
+                "o_proj on stream_gemm": e(o="stream"), "down on cublas": e(down="cublas"),
+                "before the 8-row-tile kernels: qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}}
     def try_variant(kw):
         try:
             return us_per_layer(**kw)
