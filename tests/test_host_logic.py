@@ -281,3 +281,19 @@ def test_gemm_shape_predicates():
     assert not stream_gemm_supported(65, 9728, 896) and not stream_gemm_supported(8, 100, 896)
     assert swiglu_gemm_supported(32, 4864, 896) and swiglu_gemm_supported(64, 4864, 896)
     assert not swiglu_gemm_supported(65, 4864, 896) and not swiglu_gemm_supported(8, 4864, 900)
+
+
+def test_thin_gemm_shape_predicates():
+    """The 8-row-tile kernels: one CTA per 8 weight rows, per 16 where 8 would be more than one wave of 148 SMs; a CTA's
+    weight rows plus the padded token rows must fit shared memory; gate/up takes at most 32 rows and K <= 1024."""
+    from nanoserve_b200.kernels.fused import thin_gemm_ctas, thin_gemm_supported, thin_swiglu_gemm_supported
+    assert thin_gemm_ctas(1152) == 144 and thin_gemm_ctas(896) == 112          # 0.5B QKV, o_proj: 8 rows per CTA
+    assert thin_gemm_ctas(2048) == 128 and thin_gemm_ctas(1536) == 96          # 1.5B: 16 rows per CTA
+    assert thin_gemm_ctas(1192) == 149                                          # not a multiple of 16: stays at 8 rows
+    assert thin_gemm_supported(64, 1152, 896) and thin_gemm_supported(32, 2048, 1536)
+    assert not thin_gemm_supported(64, 2048, 1536)                              # 16 + 64 rows of K = 1536: 247 KB
+    assert not thin_gemm_supported(65, 896, 896) and not thin_gemm_supported(8, 896, 900) and not thin_gemm_supported(8, 100, 896)
+    assert not thin_gemm_supported(16, 4608, 3584)                              # 7B shape: K too wide for a CTA
+    assert thin_swiglu_gemm_supported(32, 4864, 896) and thin_swiglu_gemm_supported(1, 4864, 1024)
+    assert not thin_swiglu_gemm_supported(33, 4864, 896) and not thin_swiglu_gemm_supported(8, 8960, 1536)
+    assert not thin_swiglu_gemm_supported(8, 4866, 896) and not thin_swiglu_gemm_supported(8, 4 * 9 * 149, 896)
