@@ -205,7 +205,16 @@ def test_config0_fp32_greedy_tokens_match_the_reference():
     assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - 1
 
 
-def test_config0_bf16_greedy_tokens_tie_rule():
+@pytest.mark.parametrize("gemm_mask", [None, "0", "3", "27", "195", "451"])
+def test_config0_bf16_greedy_tokens_tie_rule(gemm_mask, monkeypatch):
+    """BASELINE config 0 on the bf16 graph path: a divergence from the reference's tokens within the first 32 is
+    accepted only at a step whose reference top-2 gap is within the bf16 tie rule. Run with the engine's default choice
+    of decode-GEMM kernels (None) and with each other choice forced for every decode-sized step: 0 = library GEMMs + the
+    separate RoPE / SiLU kernels, 3 = split-K cluster kernel for QKV and down_proj, 27 = + streaming kernel for gate/up
+    and o_proj, 195 = 8-row-tile kernel for QKV and o_proj, 451 = + 8-row-tile gate/up with SiLU*mul."""
+    if gemm_mask is not None:
+        monkeypatch.setenv("NS_SKINNY_MASK", gemm_mask)
+        monkeypatch.setenv("NS_SKINNY_MASK_SMALL", gemm_mask)
     from nanoserve_b200.synthetic import random_state_dict
     gold = json.loads((GOLD / "config0_tokens.json").read_text())
     sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
@@ -219,4 +228,4 @@ def test_config0_bf16_greedy_tokens_tie_rule():
             gap = gold["step_gaps"][j][i]
             report.append((i, j, gap))
             assert gap <= TIE_GAP_BF16, f"request {i} diverges at token {j} where the reference gap is {gap:.3f}"
-    print(f"config 0 bf16: {8 - len(report)}/8 identical over 32 tokens; divergences (req, token, ref gap): {report}")
+    print(f"config 0 bf16, GEMM mask {gemm_mask}: {8 - len(report)}/8 identical over 32 tokens; divergences (req, token, ref gap): {report}")
