@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     // This kernel may be scheduled while the kernel that produces Q and this step's K/V rows (the QKV projection with
     // its RoPE + KV-write epilogue) is still running. Until pdl_wait() below it touches only what earlier steps and
     // the step's plan left behind: the plan records, the block tables and the K/V rows of OLDER tokens.
-    pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
+    if (!p.overlap_prefill) pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     const int32_t* __restrict__ cta_start = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_start);
@@ -87,7 +87,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     __shared__ int pend_last[2 * kMaxKvHeads][2];
     if (threadIdx.x < 2 * kMaxKvHeads) pend_n[threadIdx.x] = 0;
     __syncthreads();                              // the only CTA-wide barrier; everything below is per head group
-    if (u0 >= u1) return;
+    if (u0 >= u1) {
+        if (p.overlap_prefill) pdl_wait();        // an exit counts as the trigger: it must not come before Q exists
+        return;
+    }
 
     const int4* __restrict__ dec_info = reinterpret_cast<const int4*>(p.ws + p.L.dec_info);   // {seq, len, table row, q row}
     const int2* __restrict__ dec_span = reinterpret_cast<const int2*>(p.ws + p.L.dec_span);   // {first CTA, CTAs} per row
@@ -292,6 +295,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
 #pragma unroll
     for (int t = 0; t < STAGES - 1; ++t) issue(t, true);
     pdl_wait();                               // Q and the new token's K/V row exist from here on
+    if (p.overlap_prefill) pdl_launch_dependents();           // the prefill kernel may run beside this one from here on
     if (early_q_i >= 0) {
         qn_row = early_q_i;
         load_q(qn, early_q_row);

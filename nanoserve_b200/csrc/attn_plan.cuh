@@ -91,6 +91,12 @@ struct AttnParams {
     int n_heads, n_kv_heads, group;
     float scale_log2;              // softmax scale * log2(e)
     long long* timeline;           // profiling hook, normally null: 4 globaltimer stamps per decode CTA
+    // Mixed steps: the prefill kernel that follows the decode kernel in the stream does not depend on it (they read the
+    // same Q / pools and write different rows of out). With this flag the decode kernel lets its successor be scheduled
+    // only AFTER its own dependency wait (so Q and the new K/V rows exist when the prefill kernel starts), the prefill
+    // kernel runs beside it and waits for the decode kernel's completion before it exits, which keeps the stream's
+    // order for whatever comes next.
+    int overlap_prefill = 0;
 };
 
 }  // namespace ns

@@ -109,7 +109,10 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
     __shared__ int failed;
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
-    if ((int)blockIdx.x >= hdr->n_prefill_items) return;
+    if ((int)blockIdx.x >= hdr->n_prefill_items) {
+        if (p.overlap_prefill) pdl_wait();        // the grid must not complete before the decode kernel it overlaps
+        return;
+    }
     const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[blockIdx.x];
     const int s = item.x, q_start = item.y, g = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -302,6 +305,7 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
     __syncthreads();
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    if (p.overlap_prefill) pdl_wait();            // complete only after the decode kernel this one ran beside
 }
 
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size) {
@@ -321,6 +325,11 @@ int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st) {
         configured = true;
     }
     dim3 grid((unsigned)max_items, (unsigned)p.n_kv_heads);
+    if (p.overlap_prefill) {
+        cudaError_t e = launch_pdl(prefill_tc_kernel, grid, dim3(tc::kRows), (size_t)smem, st, p);
+        if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): launch failed: %s", cudaGetErrorString(e));
+        return NS_OK;
+    }
     prefill_tc_kernel<<<grid, tc::kRows, smem, st>>>(p);
     return check_launch("prefill_tc");
 }

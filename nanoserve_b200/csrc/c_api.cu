@@ -37,6 +37,7 @@ int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStr
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
 static int g_prefill_impl = 0;          // 0 = tcgen05 where supported, 1 = always the mma.sync kernel
+static int g_overlap_prefill = 1;       // 1 = the tcgen05 prefill kernel of a mixed step runs beside the decode kernel
 
 static long long* g_timeline = nullptr;
 static int g_sm_count = 0;
@@ -69,6 +70,8 @@ extern "C" const char* ns_last_error(void) { return g_err; }
 extern "C" int ns_sm_count(void) { return sm_count(); }
 extern "C" void ns_debug_decode_timeline(long long* device_buffer) { g_timeline = device_buffer; }
 extern "C" void ns_debug_prefill_impl(int impl) { g_prefill_impl = impl; }
+// Debug hook (not part of the public header): 0 = prefill kernel strictly after the decode kernel of the same call.
+extern "C" void ns_debug_overlap_prefill(int on) { g_overlap_prefill = on; }
 
 extern "C" int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim) {
     if (max_seqs <= 0 || max_tokens < 0 || n_heads <= 0 || head_dim <= 0) return -1;
@@ -151,6 +154,9 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     a.pos_stride = pool_pos_stride; a.head_stride = pool_head_stride;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads; a.scale_log2 = scale * kLog2e;
     a.timeline = g_timeline;
+    const bool has_prefill = cu_seqlens != nullptr && n_tokens > n_seqs;
+    const bool tc_prefill = has_prefill && g_prefill_impl == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size);
+    a.overlap_prefill = (tc_prefill && g_overlap_prefill) ? 1 : 0;
     int rc = launch_paged_decode(a, head_dim, sms, st);
     if (rc != NS_OK) return rc;
     if (cu_seqlens != nullptr && n_tokens > n_seqs) {
