@@ -27,7 +27,10 @@ __global__ void __launch_bounds__(256) prefill_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
-    if ((int)blockIdx.x >= hdr->n_prefill_items) return;
+    if ((int)blockIdx.x >= hdr->n_prefill_items) {
+        if (p.overlap_prefill) pdl_wait();        // the grid must not complete before the decode kernel it overlaps
+        return;
+    }
     const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[blockIdx.x];
     const int s = item.x, q_start = item.y;
     const int g = blockIdx.y;
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(256) prefill_mma_kernel(const AttnParams p) {
             *reinterpret_cast<uint32_t*>(p.out + (int64_t)(q0 + tok1) * p.out_stride + (int64_t)h * HD + c) =
                 pack_bf16x2(o[d][2] * i1, o[d][3] * i1);
     }
+    if (p.overlap_prefill) pdl_wait();            // complete only after the decode kernel this one ran beside
 }
 
 template <int HD, int STAGES> static int launch_prefill_cfg(const AttnParams& p, int max_items, cudaStream_t st) {
@@ -189,6 +193,11 @@ template <int HD, int STAGES> static int launch_prefill_cfg(const AttnParams& p,
         configured = true;
     }
     dim3 grid((unsigned)max_items, (unsigned)p.n_kv_heads);
+    if (p.overlap_prefill) {
+        cudaError_t e = launch_pdl(prefill_mma_kernel<HD, STAGES>, grid, dim3((unsigned)(p.group * 32)), (size_t)smem, st, p);
+        if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention: launch failed: %s", cudaGetErrorString(e));
+        return NS_OK;
+    }
     prefill_mma_kernel<HD, STAGES><<<grid, p.group * 32, smem, st>>>(p);
     return check_launch("prefill_mma");
 }

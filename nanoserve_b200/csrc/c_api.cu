@@ -37,7 +37,7 @@ int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStr
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
 static int g_prefill_impl = 0;          // 0 = tcgen05 where supported, 1 = always the mma.sync kernel
-static int g_overlap_prefill = 1;       // 1 = the tcgen05 prefill kernel of a mixed step runs beside the decode kernel
+static int g_overlap_prefill = 1;       // 1 = the prefill kernel of a mixed step runs beside the decode kernel
 
 static long long* g_timeline = nullptr;
 static int g_sm_count = 0;
@@ -155,8 +155,7 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads; a.scale_log2 = scale * kLog2e;
     a.timeline = g_timeline;
     const bool has_prefill = cu_seqlens != nullptr && n_tokens > n_seqs;
-    const bool tc_prefill = has_prefill && g_prefill_impl == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size);
-    a.overlap_prefill = (tc_prefill && g_overlap_prefill) ? 1 : 0;
+    a.overlap_prefill = (has_prefill && g_overlap_prefill) ? 1 : 0;
     int rc = launch_paged_decode(a, head_dim, sms, st);
     if (rc != NS_OK) return rc;
     if (cu_seqlens != nullptr && n_tokens > n_seqs) {
