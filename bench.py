@@ -383,6 +383,49 @@ def launch_probe() -> None:
     print(json.dumps({"probe_steps": kinds, "engine": {k: eng.stats[k] for k in ("graph_steps", "piecewise_steps", "steps")}}))
 
 
+def attn_overlap_probe() -> None:
+    """One ragged paged attention call on mixed batches (decode rows + prefill chunks), with the prefill kernel strictly
+    after the decode kernel and beside it (the library's default; a debug hook switches it off): us per call from a CUDA
+    graph of 20 calls, and whether the two outputs are bit-identical. Prints one JSON object."""
+    import ctypes
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    hook = _lib.load().ns_debug_overlap_prefill
+    hook.argtypes, hook.restype = [ctypes.c_int], None
+    rows = []
+    for nd, npf, chunk, heads in ((31, 1, 300, (14, 2, 64)), (31, 2, 512, (14, 2, 64)), (16, 1, 128, (14, 2, 64)),
+                                  (48, 4, 512, (14, 2, 64)), (31, 1, 300, (12, 2, 128)), (31, 2, 512, (12, 2, 128))):
+        w = attention_workload(n_decode=nd, decode_range=(300, 1200), n_prefill=npf, chunk=chunk, prefill_ctx_range=(0, 512),
+                               num_blocks=8192, seed=3, n_heads=heads[0], n_kv_heads=heads[1], head_dim=heads[2])
+        ws = AttnWorkspace(64, 4096, heads[0], heads[2], "cuda")
+        ws.plan(w.seq_lens, w.cu_seqlens, w.seq_lens.shape[0], 16)
+        us, outs = {}, {}
+        for mode in (0, 1):
+            hook(mode)
+            call = lambda: ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale,
+                                                  workspace=ws, planned=True)
+            for _ in range(3):
+                o = call()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(20):
+                    o = call()
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us[mode], outs[mode] = round(a.elapsed_time(b) * 1e3 / 20, 2), o.clone()
+        hook(1)
+        rows.append({"decode_rows": nd, "prefill_chunks": npf, "chunk_tokens": chunk, "heads": list(heads),
+                     "us_prefill_after_decode": us[0], "us_prefill_beside_decode": us[1],
+                     "identical": bool(torch.equal(outs[0], outs[1]))})
+    print(json.dumps({"attn_overlap_probe": rows}))
+
+
 def layer_probe(rows: int) -> None:
     """Marginal cost of each kernel of one decode layer INSIDE the layer chain: 24 layers of the engine's kernel sequence
     for `rows` one-token sequences (contexts U[400,600], Qwen2.5-0.5B shape, distinct weights per layer) captured in one
@@ -579,6 +622,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launch-probe", action="store_true",
                     help="short run for `ncu --profile-from-start off` launch lists: 2 decode steps at c=32 + 1 mixed step")
+    ap.add_argument("--attn-overlap-probe", action="store_true",
+                    help="mixed-batch attention calls with the prefill kernel after / beside the decode kernel")
     ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS",
                     help="marginal cost of each kernel of one decode layer inside the layer chain, for ROWS sequences")
     ap.add_argument("--roofline-only", action="store_true",
@@ -595,6 +640,8 @@ def main() -> None:
         launch_probe()
     elif args.layer_probe:
         layer_probe(args.layer_probe)
+    elif args.attn_overlap_probe:
+        attn_overlap_probe()
     elif args.roofline_only:
         torch.cuda.set_device(0)
         print(json.dumps({"roofline": decode_attention_roofline(torch.device("cuda", 0))}))
