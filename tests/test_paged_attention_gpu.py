@@ -176,3 +176,52 @@ def test_decode_one_range_per_cta_and_two_virtual_ctas_agree():
             assert (got - want).abs().max().item() <= 1e-2
     finally:
         hook(-1)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(14, 2, 64), (12, 2, 128)])
+def test_prefill_beside_decode_equals_prefill_after_decode(n_heads, n_kv, hd):
+    """In a mixed batch the prefill kernel runs beside the decode kernel of the same call (the decode kernel lets it
+    start after its own dependency wait; the prefill kernel waits for the decode kernel before it exits). Forced off
+    through the library's debug hook, the output must be bit-identical; both are checked against the scalar
+    fp32-accumulating kernel (tolerance 1e-2), eagerly and replayed several times from one CUDA graph, with decode-only
+    and prefill-only batches among the cases (a kernel whose CTAs all leave at once)."""
+    import ctypes
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    hook = _lib.load().ns_debug_overlap_prefill
+    hook.argtypes, hook.restype = [ctypes.c_int], None
+    cases = [dict(n_decode=31, n_prefill=1, chunk=300), dict(n_decode=5, n_prefill=3, chunk=64),
+             dict(n_decode=0, n_prefill=2, chunk=200), dict(n_decode=40, n_prefill=1, chunk=1)]
+    try:
+        for c in cases:
+            w = attention_workload(decode_range=(1, 1500), prefill_ctx_range=(0, 600), num_blocks=8192, seed=11,
+                                   n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, **c)
+            S = w.seq_lens.shape[0]
+            want = ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale,
+                                          simple=True).float()
+            outs = []
+            for mode in (0, 1):
+                hook(mode)
+                ws = AttnWorkspace(64, 4096, n_heads, hd)
+                call = lambda: ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens,
+                                                      w.scale, n_seqs=S, workspace=ws)
+                eager = call()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    call()
+                torch.cuda.current_stream().wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(4):
+                        replayed = call()
+                g.replay()
+                g.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(eager, replayed), (c, mode)
+                assert (eager.float() - want).abs().max().item() <= 1e-2, (c, mode)
+                outs.append(eager)
+            assert torch.equal(outs[0], outs[1]), c
+    finally:
+        hook(1)
