@@ -1,21 +1,21 @@
 // Narrow decode-sized GEMMs (QKV, o_proj: K = hidden size) without any split over K across CTAs.
 //
-// Y[M <= 64, N] = X[M, K] . W[N, K]^T. A CTA owns EIGHT weight rows over the whole of K (one mma n-tile), so a GEMM
-// with N = 896..1152 is 112..144 CTAs: about one per SM. The four warps split K between them and each warp fetches
-// only ITS quarter of the weight rows (before the dependency wait, so they stream while the preceding kernel runs)
-// and of the activation rows (after the wait; every CTA reads all of X: 57 KB at 32 rows, from L2) with 16-byte
-// cp.async copies into padded rows, waits for its own copies only, keeps its partial 16x8 tiles in registers (two
-// independent accumulator sets per m-tile) and meets the other warps once in shared memory: no mbarrier, no
-// thread-block cluster, no distributed shared memory, no barrier but one __syncthreads.
+// Y[M <= 64, N] = X[M, K] . W[N, K]^T. A CTA owns EIGHT weight rows over the whole of K (one mma n-tile; sixteen where
+// eight would be more than one wave of CTAs), so a GEMM with N = 896..1152 is 112..144 CTAs: about one per SM. The four
+// warps split K between them. Each warp fetches its quarter of the weight rows with 16-byte cp.async copies before the
+// dependency wait (they stream while the preceding kernel runs) and waits for its own copies only; after the wait all
+// M activation rows arrive by bulk copies on one mbarrier (every CTA reads all of X: 57 KB at 32 rows, from L2). Every
+// warp keeps its partial 16x8 tiles in registers (two independent accumulator sets per m-tile) and meets the others
+// once in shared memory: no thread-block cluster, no distributed shared memory, one __syncthreads after the k-loop.
 //
 // Why: cycle stamps of the 64-row-tile, 8-way split-K kernel in skinny_gemm.cu inside a decode layer showed where its
-// 4.8 us after the wait go: ~1.0 us issuing 32 activation bulk copies from one warp (a bulk copy costs its issuing
-// lane 60-140 cycles, one after the other), 0.6 us in 7 dependent k-steps, 0.55 us pushing partial tiles to peer CTAs,
-// 0.7 us in the cluster barrier, 1.5 us in the RoPE epilogue behind its loads. This kernel needs ~1.2 us after the wait.
+// 4.8 us after the wait go: ~1.0 us issuing 32 activation bulk copies from one warp, 0.6 us in 7 dependent k-steps,
+// 0.55 us pushing partial tiles to peer CTAs, 0.7 us in the cluster barrier, 1.5 us in the RoPE epilogue behind its
+// loads. This kernel needs 2.3 us after the wait for QKV and 1.5 us for o_proj.
 //
-// Epilogues: bias (optional); or RoPE + paged KV write for a merged QKV projection with 64-wide heads: the CTA's
-// eight rows are then four rows of a head's first half and the matching four of its second half, so every rotation
-// pair (i, i + 32) is finished by one thread. Rounding points are those of the unfused ops.
+// Epilogues: bias (optional); or RoPE + paged KV write for a merged QKV projection with 64- or 128-wide heads: an
+// n-tile is then four rows of a head's first half and the matching four of its second half, so every rotation pair
+// (i, i + head_dim / 2) is finished by one thread. Rounding points are those of the unfused ops.
 #include "common.cuh"
 
 namespace ns {
@@ -86,6 +86,17 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
     float* c_sm = reinterpret_cast<float*>(smem + (size_t)(R + MP) * pitch);      // [4 warps][NT][MP][8] fp32
 
     pdl_launch_dependents();
+    // X arrives by bulk copies (one per token row, issued after the dependency wait, eight per warp at 32 rows) on this
+    // barrier. 16-byte cp.async copies of X (every warp its own K quarter, no barrier at all) were measured slower: the
+    // load/store pipe moves ~36 bytes per clock per SM for cp.async, so 57 KB of X took 0.8 us longer than the bulk copies.
+    __shared__ __align__(8) uint64_t x_bar;
+    const uint32_t mb_x = smem_u32(&x_bar);
+    if (tid == 0) {
+        mbar_init(mb_x, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(mb_x, (uint32_t)p.M * (uint32_t)p.K * 2);
+    }
+    __syncthreads();
     // RoPE epilogue: n-tile g = tile * NT + nt is rows [4 sub, 4 sub + 4) of a head's first half + the matching four of
     // its second half; a head has head_dim / 8 such tiles
     const int half = p.head_dim >> 1, per_head = p.head_dim >> 3;
@@ -106,13 +117,9 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
     }
     cp_async_commit();
     pdl_wait();        // everything above touched only weights; the activations come from the preceding kernel
-    for (int cc = lane; cc < qchunks; cc += 32) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.x) + kbase + cc * 16;
-        const uint32_t dst = x_sm + kbase + cc * 16;
-#pragma unroll 8
-        for (int m = 0; m < p.M; ++m) cp_async16(dst + m * pitch, src + (size_t)m * p.K * 2, 16);
+    if (lane < 8) {
+        for (int m = warp + 4 * lane; m < p.M; m += 32) bulk_g2s(x_sm + m * pitch, p.x + (int64_t)m * p.K, (uint32_t)p.K * 2, mb_x);
     }
-    cp_async_commit();
 
     // ---- epilogue inputs into registers while the activations are on their way -------------------------------------
     // (raw bf16 values: converting here would make the warp wait for the loads before it reaches the k-loop)
@@ -179,8 +186,9 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(acc[s][mt][nt], f.a[s][mt], f.b[nt][2 * s], f.b[nt][2 * s + 1]);
     };
-    cp_async_wait<0>();                                   // this warp's own copies: nobody else reads them
+    cp_async_wait<0>();                                   // this warp's own weight copies: nobody else reads them
     __syncwarp();
+    if (!mbar_wait_bounded(mb_x, 0) && lane == 0) atomicAdd(&g_thin_errors, 1u);
     {
         Frag f0, f1;
         load_frag(f0, 0);
