@@ -94,9 +94,10 @@ int ns_skinny_gemm(const void* x, const void* residual, const void* ln_w, void* 
  *   (8 or 16 + M rounded up to 16, 32 or 64) rows of K must fit 220 KB of shared memory.
  * One CTA per eight weight rows over all of K (sixteen where N / 8 > 148 and N % 16 == 0, so that the grid stays one
  * wave of a 148-SM part): a GEMM with N around 1000 is one CTA per SM; the weight rows are
- * requested before the kernel waits for its predecessor in the stream, every CTA then fetches all of x (16-byte
- * cp.async copies, each warp its own quarter of K), and the four warps' partial tiles are summed through shared
- * memory in a fixed order. No cluster, no barrier a thread could wait on beyond __syncthreads.
+ * requested (16-byte cp.async, each warp its own quarter of K) before the kernel waits for its predecessor in the
+ * stream, every CTA then fetches all of x by bulk copies on one mbarrier (bounded wait, counted in
+ * ns_thin_gemm_errors when it runs out), and the four warps' partial tiles are summed through shared memory in a
+ * fixed order. No thread-block cluster.
  * epilogue 0: out[M, N] = bf16(acc + bias) (bias may be NULL);
  * epilogue 2: as ns_skinny_gemm's epilogue 2 (merged QKV: bias, RoPE, q to out, k / v into one layer's paged pool
  *   at slots[m]) for heads of 64 or 128 (head_dim = N / (n_heads + 2 * n_kv_heads); cos / sin are [M, head_dim]).
