@@ -207,7 +207,7 @@ def test_config0_fp32_greedy_tokens_match_the_reference():
 
 @pytest.mark.parametrize("gemm_mask", [None, "0", "3", "27", "195", "451"])
 def test_config0_bf16_greedy_tokens_tie_rule(gemm_mask, monkeypatch):
-    """BASELINE config 0 on the bf16 graph path: a divergence from the reference's tokens within the first 32 is
+    """Benchmark configuration 0 (0.5B shape, 8 requests x 64 greedy tokens) on the bf16 graph path: a divergence from the reference's tokens within the first 32 is
     accepted only at a step whose reference top-2 gap is within the bf16 tie rule. Run with the engine's default choice
     of decode-GEMM kernels (None) and with each other choice forced for every decode-sized step: 0 = library GEMMs + the
     separate RoPE / SiLU kernels, 3 = split-K cluster kernel for QKV and down_proj, 27 = + streaming kernel for gate/up
