@@ -143,10 +143,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
 
     // Tiles issued before pdl_wait(): the row of the step's new token (always the last of its block) is left out and
     // fetched afterwards; which tile, which row and where from is remembered here.
-    int early_valid[STAGES - 1];
-    int64_t early_base[STAGES - 1];
+    int early_valid[STAGES];
+    int64_t early_base[STAGES];
 #pragma unroll
-    for (int t = 0; t < STAGES - 1; ++t) early_valid[t] = 0;
+    for (int t = 0; t < STAGES; ++t) early_valid[t] = 0;
     int early_q_i = -1, early_q_row = 0;
 
     auto issue = [&](int t, bool early) {
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
             if (early && pf_info.y - 16 * j <= 16) {      // the row's last block: its last token is this step's
                 skip_row = valid - 1;
 #pragma unroll
-                for (int e = 0; e < STAGES - 1; ++e)
+                for (int e = 0; e < STAGES; ++e)
                     if (e == t) {
                         early_valid[e] = valid;
                         early_base[e] = (int64_t)blk * p.blk_stride + (int64_t)g * p.head_stride;
@@ -294,6 +294,12 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     const int my_tiles = (u1 - u0 - stripe + wph - 1) / wph;      // may be <= 0
 #pragma unroll
     for (int t = 0; t < STAGES - 1; ++t) issue(t, true);
+    // Nothing is computed before the wait, so the ring's last stage can carry a tile as well: a warp then has STAGES
+    // tiles in flight while the QKV kernel runs (rows up to 16 x STAGES x warps-per-head tokens arrive completely before
+    // Q exists). Only when this warp's first tile lies in the CTA's first row: otherwise iteration 0 starts with a
+    // flush(), whose scratch is that stage.
+    const bool full_ring = u0 + stripe < rec_b.x;
+    if (full_ring) issue(STAGES - 1, true);
     pdl_wait();                               // Q and the new token's K/V row exist from here on
     if (p.overlap_prefill) pdl_launch_dependents();           // the prefill kernel may run beside this one from here on
     if (early_q_i >= 0) {
@@ -303,7 +309,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     {
         bool patched = false;
 #pragma unroll
-        for (int t = 0; t < STAGES - 1; ++t) {
+        for (int t = 0; t < STAGES; ++t) {
             if (early_valid[t] > 0) {
                 patched = true;
                 const int row = early_valid[t] - 1;
@@ -346,7 +352,10 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 load_q(qa, cc_qrow);          // the prefetch cursor is already rows ahead (very short rows)
             }
         }
-        issue(t + STAGES - 1, false);         // refills the stage computed in iteration t-1
+        if (t == 0 && full_ring)
+            cp_async_commit();                // that tile is already on its way: keep one commit group per iteration
+        else
+            issue(t + STAGES - 1, false);     // refills the stage computed in iteration t-1
         const uint32_t ks = smem_u32(my_stages + (size_t)(t % STAGES) * STAGE_BYTES), vs = ks + KV_TILE;
         const int valid = min(16, cc_len - 16 * (u - cc_lo));
 
