@@ -297,8 +297,7 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
         mbar_expect_tx(mb_x, (uint32_t)M * (uint32_t)K * 2);
     }
     __syncthreads();
-    const int qchunks = K / 32;                           // 16-byte chunks in a quarter of a row
-    const uint32_t kbase = (uint32_t)q * (uint32_t)(K / 4) * 2;
+    const uint32_t kbase = (uint32_t)q * (uint32_t)(K / 4) * 2;      // byte offset of this warp's K quarter in a row
     // This warp's quarter of its three tiles' weight rows, before the dependency wait (they stream while the norm runs),
     // in the order the k-loop uses them: one commit group per iteration (32 columns = 64 bytes of each of the 24 rows;
     // lane = (row, 16-byte chunk)), so the loop can start on the first group while the rest is still on its way.
