@@ -37,3 +37,27 @@ def test_ops_refuse_cpu_tensors():
     from nanoserve_b200.kernels.fused import silu_mul
     with pytest.raises(_lib.NanoserveB200Error):
         silu_mul(torch.zeros(2, 16))
+
+
+def test_decode_gemm_entry_points_validate_before_touching_the_device():
+    """Shape, alignment and epilogue checks of the decode-sized GEMMs come before any CUDA call: they return a status
+    and leave a message, with or without a GPU (the pointers below are never dereferenced)."""
+    lib, P = _lib.load(), ctypes.c_void_p
+    msg = lambda: lib.ns_last_error().decode()
+    x, w, out = P(256), P(512), P(1024)
+    nul = None
+    INVALID, UNSUPPORTED = 1, 2
+    assert lib.ns_thin_gemm(x, w, nul, out, 0, 1152, 896, 0, nul, nul, nul, nul, nul, 0, 0, nul) == 0          # empty step
+    assert lib.ns_thin_gemm(x, w, nul, out, 65, 896, 896, 0, nul, nul, nul, nul, nul, 0, 0, nul) == UNSUPPORTED and "65 token rows" in msg()
+    assert lib.ns_thin_gemm(x, w, nul, out, 8, 896, 900, 0, nul, nul, nul, nul, nul, 0, 0, nul) == UNSUPPORTED and "multiple of 128" in msg()
+    assert lib.ns_thin_gemm(x, w, nul, out, 64, 4608, 3584, 0, nul, nul, nul, nul, nul, 0, 0, nul) == UNSUPPORTED and "shared memory" in msg()
+    assert lib.ns_thin_gemm(x, w, nul, out, 8, 1152, 896, 2, nul, nul, nul, nul, nul, 14, 2, nul) == INVALID and "RoPE epilogue needs" in msg()
+    assert lib.ns_thin_gemm(x, w, nul, out, 8, 1160, 896, 2, x, x, x, x, x, 14, 2, nul) == INVALID and "head_dim" in msg()
+    assert lib.ns_thin_gemm(x, w, nul, out, 8, 1152, 896, 7, nul, nul, nul, nul, nul, 14, 2, nul) == INVALID and "unknown epilogue" in msg()
+    assert lib.ns_thin_gemm(x, nul, nul, out, 8, 1152, 896, 0, nul, nul, nul, nul, nul, 0, 0, nul) == INVALID and "null pointer" in msg()
+    assert lib.ns_thin_swiglu_gemm(x, w, out, 33, 4864, 896, nul) == UNSUPPORTED and "33 token rows" in msg()
+    assert lib.ns_thin_swiglu_gemm(x, w, out, 8, 8960, 1536, nul) == UNSUPPORTED and "shared memory" in msg()
+    assert lib.ns_thin_swiglu_gemm(x, w, P(1028), 8, 4864, 896, nul) == INVALID and "aligned" in msg()
+    assert lib.ns_thin_swiglu_gemm(x, w, out, 8, 4866, 896, nul) == UNSUPPORTED
+    assert lib.ns_skinny_gemm(x, nul, nul, nul, w, nul, out, 65, 896, 896, 8, ctypes.c_float(1e-6), 0, 0, nul, nul, nul, nul, nul,
+                              0, 0, nul) == UNSUPPORTED and "65 token rows" in msg()
