@@ -338,21 +338,23 @@ class Qwen2Model:
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
         T = meta.tokens.shape[0]
         cu = None if meta.decode_only else meta.cu_seqlens
-        # decode-sized steps: down_proj is a pure weight read (K = intermediate size): the bulk-copy skinny GEMM with
-        # an 8-way cluster split over K beats the library GEMM there; everything else stays F.linear
+        # Decode-sized steps (at most SKINNY_MAX_ROWS token rows, bf16): a GEMM is a weight read behind a dependency, and
+        # this library's own kernels can request their weights while the preceding kernel still runs (programmatic
+        # dependent launch). Larger steps keep F.linear everywhere.
         inter = self.layers[0].down_w.shape[1]
         skinny = self.dtype == torch.bfloat16 and T <= SKINNY_MAX_ROWS and self.skinny_gemms
         skinny_down = skinny and inter % 128 == 0 and inter // 8 <= 1024
         hidden = cfg.hidden_size
-        # QKV with the RoPE + KV-write epilogue (64-wide heads) and o_proj: narrow GEMMs whose weights can stream while
-        # the preceding norm / attention kernel still runs (programmatic dependent launch)
         import os
-        # which GEMMs leave the library GEMM (bit 0 down_proj, 1 QKV, 2 o_proj on the skinny kernel; 3 gate/up, 4 o_proj on
-        # the persistent streaming kernel; 5 gate/up on the tcgen05 + TMA kernel; 6 QKV, 7 o_proj on the 8-row-tile kernel
-        # without split-K, which wins over bits 1, 2 and 4). Measured inside a decode layer: the streaming kernel pays off
-        # for gate/up up to 16 rows (-1.8 us per layer at 16, -1.3 at 8), not above (+1.5 at 32, +7 at 64); QKV and o_proj
-        # together on the 8-row-tile kernel take 2.9 us off a layer at 32 rows; bit 8: gate/up + SiLU*mul on the 8-row-tile
-        # kernel (17..32 rows: +5-7 % tok/s at c=32 over the library GEMM + SiLU kernel).
+        # Which kernel serves which GEMM is a bit mask (NS_SKINNY_MASK; NS_SKINNY_MASK_SMALL for steps of at most 16 rows):
+        #   bit 0 down_proj, 1 QKV (+RoPE, KV write), 2 o_proj on the split-K cluster kernel (ns_skinny_gemm);
+        #   bit 3 gate/up + SiLU*mul, 4 o_proj on the persistent streaming kernel (ns_stream_gemm);
+        #   bit 5 gate/up + SiLU*mul on the tcgen05 + TMA kernel (ns_swiglu_gemm; measured slower, never a default);
+        #   bit 6 QKV (+RoPE, KV write), 7 o_proj on the 8-row-tile kernel without split-K (ns_thin_gemm; wins over bits
+        #         1, 2 and 4), bit 8 gate/up + SiLU*mul on the same construction (ns_thin_swiglu_gemm, up to 32 rows).
+        # Defaults from measurements inside a decode layer and at engine level: 8-row-tile kernels for QKV, o_proj and (17..32
+        # rows) gate/up; up to 16 rows the streaming kernel for gate/up; down_proj on the split-K kernel; a GEMM whose
+        # kernel does not take the step's shape falls back to the next choice and finally to F.linear.
         if T <= 16:
             mask = int(os.environ.get("NS_SKINNY_MASK_SMALL", os.environ.get("NS_SKINNY_MASK", "219")))
         else:
