@@ -279,7 +279,34 @@ def main(ref_root: str) -> None:
     print(f"config 0: {eng.stats['steps']} steps, {sum(len(v) for v in outs.values())} tokens in {dt_s:.1f} s")
 
 
+# ---- sampling host pieces: per-request seeds and parameter validation (integers and flags only) -------------------
+SAMPLING_SEEDS = [(0, 0), (1, 0), (0, 1), (12345, 7), (2 ** 62 - 1, 255), (2 ** 63 + 5, 3), (987654321987, 1_000_000),
+                  (2 ** 64 - 1, 2 ** 32), (42, 41), (42, 42), (42, 43)]
+SAMPLING_PARAMS = [dict(), dict(temperature=0.0, top_k=5), dict(temperature=0.7), dict(temperature=1.0, top_k=1),
+                   dict(temperature=0.5, top_p=0.9, top_k=40, seed=7), dict(temperature=-0.1), dict(temperature=float("nan")),
+                   dict(top_p=0.0), dict(top_p=1.0001), dict(top_p=1.0), dict(top_k=-1), dict(top_k=0, temperature=2.0)]
+
+
+def sampling_main(ref_root: str) -> None:
+    """Records the reference's mix_seed values and which SamplingParams it accepts (and whether they are greedy)."""
+    sys.path.insert(0, ref_root)
+    from nanoserve.sampling import SamplingParams, mix_seed
+    seeds = [[s, n, mix_seed(s, n)] for s, n in SAMPLING_SEEDS]
+    params = []
+    for kw in SAMPLING_PARAMS:
+        try:
+            params.append(dict(ok=True, greedy=bool(SamplingParams(**kw).greedy)))
+        except ValueError:
+            params.append(dict(ok=False, greedy=None))
+    (HERE / "sampling.json").write_text(json.dumps(dict(mix_seed=seeds, params=params)))
+    print(f"sampling: {len(seeds)} seeds, {len(params)} parameter sets")
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
-    main(sys.argv[1])
+    if len(sys.argv) == 3 and sys.argv[2] == "sampling":
+        sampling_main(sys.argv[1])
+    elif len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project> [sampling]")
+    else:
+        main(sys.argv[1])
+        sampling_main(sys.argv[1])
