@@ -12,11 +12,19 @@ Reported on one JSON line:
   e2e       the same metric through the public API (LLMEngine.add_request / step): host token lists in, per-step
             upload of the packed step records from pinned memory, per-step device->host read of the sampled tokens;
   roofline  decode paged attention on benchmark configuration 1 (48 decode rows, contexts 128-8192, 14/2 heads, hd 64):
-            algorithmic bytes / CUDA-event time per launch, against the measured HBM copy bandwidth;
-  cpu_baseline  the CPU oracle (a port of the reference's torch path, fp32) on a bounded sample of the same request
-            stream, timed on this box's host cores (rank 0, N=1 only).
-With --gpus N (torchrun, one rank per GPU) every rank runs an independent replica of the engine on its own copy of
-the workload (request-level replicas, no collective on the data path): weak scaling.
+            algorithmic bytes / CUDA-event time per launch, against the measured HBM copy bandwidth; two timings,
+            back-to-back dependent launches (what `frac` uses: the kernel's throughput inside a layer chain, where a
+            launch's prologue runs under its predecessor's tail) and one launch at a time;
+  roofline_prefill  the four 512-token prefill chunks of configuration 1 on the tcgen05 kernel: TFLOP/s against the
+            measured bf16 GEMM peak;
+  cpu_baseline  the CPU oracle (a port of the reference's torch path, fp32) on benchmark configuration 0 (8 requests,
+            prompts 32-256, 64 greedy tokens each, max_num_seqs 8: the reference's own CPU-runnable case), timed on
+            this box's host cores (rank 0, N=1 only), with `gpu_same_workload_tok_s`: this engine on that same request
+            list through the same API, so one like-for-like ratio exists beside the configuration-2 headline.
+`--impl reference` times that CPU arm alone, K passes after W warm-up passes (one pass under torchrun with N > 1,
+where rank 0 alone runs it and the other ranks leave at once).
+With --gpus N (torchrun, one rank per GPU) every rank runs an independent replica of the engine on its own seeded
+request stream (request-level replicas, no collective on the data path): weak scaling.
 """
 from __future__ import annotations
 
@@ -39,21 +47,28 @@ CONCURRENCY = 32
 N_REQUESTS = 64
 METRIC = "output_tok_per_s_c32_qwen2.5-0.5b"
 UNIT = "tok/s"
-CPU_SAMPLE_REQUESTS, CPU_SAMPLE_MAX_NEW = 6, 16
 HBM_FALLBACK_GBS = 6650.0
+BF16_FALLBACK_TFLOPS = 1590.0
+CPU_ARM_TEXT = ("CPU arm (cpu_baseline, --impl reference): BASELINE config 0 - 8 requests, prompts U[32,256], 64 greedy tokens "
+                "each, max_num_seqs 8, chunked prefill 2048 - through the oracle port of the reference's fp32 torch path")
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch on the config-1 batch, from the ncu
 # capture summarised in profiles/paged_decode_kernel_config1.md
 DECODE_DRAM_TRAFFIC_BYTES = 117_000_000
 
 
-def workload():
+def workload(rank: int = 0):
+    """The request stream of one replica: rank 0 serves the seed-0 stream of the single-GPU benchmark, every other
+    replica its own stream from the same distributions."""
+    from nanoserve_b200.replicas import replica_seed
     from nanoserve_b200.synthetic import serving_requests
-    return serving_requests(N_REQUESTS, prompt_range=(64, 1024), output_range=(16, 256), vocab=151936, seed=0)
+    return serving_requests(N_REQUESTS, prompt_range=(64, 1024), output_range=(16, 256), vocab=151936,
+                            seed=replica_seed(0, rank))
 
 
 def config_dict(n_gpus: int) -> dict:
     return {"workload": "BASELINE config 2: Qwen2.5-0.5B shape, 64 requests, prompts U[64,1024], outputs U[16,256], "
                         "closed loop c=32, chunked prefill 2048, CUDA graphs, one step in flight (lookahead)",
+            "cpu_arm_workload": CPU_ARM_TEXT,
             "concurrency": CONCURRENCY, "requests_per_gpu": N_REQUESTS, "parallelism": f"replicas x{n_gpus}",
             "l2": "inputs larger than L2 (988 MB of weights stream every step; roofline leg rotates 4 KV pools)"}
 
@@ -108,53 +123,107 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
+def config0_requests():
+    """Benchmark configuration 0: 8 requests, prompt lengths uniform in 32-256, uniform token ids, 64 greedy tokens
+    (the request list of tests/golden/make_golden.py:config0_requests, restated so the bench imports no test code)."""
+    import random
+    rng = random.Random(0)
+    reqs = []
+    for _ in range(8):
+        n = rng.randint(32, 256)
+        reqs.append(([rng.randrange(151936) for _ in range(n)], 64))
+    return reqs
+
+
+CONFIG0_ENGINE_KW = dict(max_seq_len=2048, max_num_seqs=8, max_num_batched_tokens=2048, block_size=16)
+
+
 def cpu_reference_pass(sd32, cfg, reqs) -> tuple[float, int]:
-    """One pass of the CPU oracle engine over the bounded sample; returns (seconds, output tokens)."""
+    """One pass of the CPU oracle engine over configuration 0; returns (seconds, output tokens)."""
     from oracle.engine import OracleEngine, OracleModel, run_requests
-    eng = OracleEngine(OracleModel(cfg, sd32), max_seq_len=2048, max_num_seqs=len(reqs), max_num_batched_tokens=2048)
+    eng = OracleEngine(OracleModel(cfg, sd32), **CONFIG0_ENGINE_KW)
     t0 = time.perf_counter()
     outs = run_requests(eng, reqs)
     return time.perf_counter() - t0, sum(len(v) for v in outs.values())
 
 
-def cpu_sample_requests():
-    return [(p, min(n, CPU_SAMPLE_MAX_NEW)) for p, n in workload()[:CPU_SAMPLE_REQUESTS]]
+def pick_cpu_threads(sd32, cfg) -> int:
+    """Thread count for the CPU arm: the fastest of a few candidates up to every host core on a short probe (one
+    8-row decode-shaped layer pass), so that a many-core box is neither left idle nor slowed by oversubscription.
+    NS_CPU_THREADS overrides."""
+    if os.environ.get("NS_CPU_THREADS"):
+        return max(1, int(os.environ["NS_CPU_THREADS"]))
+    import torch.nn.functional as F
+    cores = os.cpu_count() or 1
+    x = torch.randn(8, cfg["hidden_size"])
+    ws = [sd32[f"model.layers.{i}.mlp.gate_proj.weight"] for i in range(cfg["n_layers"])]
+    best, best_t = 1, float("inf")
+    for n in sorted({c for c in (4, 8, 16, 32, 64, cores) if c <= cores}):
+        torch.set_num_threads(n)
+        for w in ws[:4]:
+            F.linear(x, w)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            for w in ws:
+                F.linear(x, w)
+        t = time.perf_counter() - t0
+        if t < best_t * 0.97:
+            best, best_t = n, t
+    return best
 
 
-def cpu_sample_text() -> str:
-    return (f"first {CPU_SAMPLE_REQUESTS} requests of the same stream, outputs capped at {CPU_SAMPLE_MAX_NEW} tokens, "
-            f"c={CPU_SAMPLE_REQUESTS}, fp32 (the reference's CPU path is fp32), oracle port of the reference's torch path")
+def cpu_sample_text(threads: int) -> str:
+    return (f"BASELINE config 0 in full (8 requests x 64 greedy tokens, prompts U[32,256], c=8, fp32: the reference's CPU "
+            f"path is fp32), oracle port of the reference's torch path, {threads} torch threads of {os.cpu_count()} host cpus")
 
 
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     from nanoserve_b200.synthetic import random_state_dict
+    os.environ.pop("OMP_NUM_THREADS", None)          # torchrun sets it to 1 for every rank
     sd32, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
-    reqs = cpu_sample_requests()
-    for _ in range(args.warmup):
+    threads = pick_cpu_threads(sd32, cfg)
+    torch.set_num_threads(threads)
+    reqs = config0_requests()
+    # under torchrun the same CPU arm would run once per N of a scaling sweep: one pass is enough there
+    steps, warmup = (args.steps, args.warmup) if world == 1 else (1, 0)
+    for _ in range(warmup):
         cpu_reference_pass(sd32, cfg, reqs)
     total_s, total_tok = 0.0, 0
-    for _ in range(args.steps):
+    for _ in range(steps):
         s, n = cpu_reference_pass(sd32, cfg, reqs)
         total_s += s
         total_tok += n
     value = total_tok / total_s
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": 1e3 * total_s / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": cpu_sample_text()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "threads": threads, "kind": "port",
+                         "workload": "BASELINE config 0", "sample": cpu_sample_text(threads)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "host_cpus": os.cpu_count()}))
 
 
 # ------------------------------------------------------------------------------------------------ roofline leg
+def measured_peak(key: str, fallback: float) -> tuple[float, str]:
+    mp = ROOT / "MEASURED_PEAKS.json"
+    if mp.exists():
+        try:
+            return float(json.loads(mp.read_text())[key]), "measured"
+        except (ValueError, KeyError):
+            pass
+    return fallback, "fallback"
+
+
 def decode_attention_roofline(device) -> dict:
-    """Decode paged attention on benchmark configuration 1, timed alone: R launches rotating over 4 KV pools (inputs larger
-    than the 126 MB L2) inside one CUDA graph, CUDA events around the replay on the launching stream."""
+    """Decode paged attention on benchmark configuration 1, timed alone, two ways, always rotating over 4 KV pools
+    (inputs larger than the 126 MB L2): (a) R launches back to back inside one CUDA graph, CUDA events around the replay
+    on the launching stream - each launch is a programmatic dependent of the one before, as inside a layer chain; (b)
+    one launch at a time, an event pair and a synchronisation around each."""
     from nanoserve_b200.kernels.fused import kv_write
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
     from nanoserve_b200.synthetic import attention_workload
@@ -168,11 +237,14 @@ def decode_attention_roofline(device) -> dict:
     out = torch.empty_like(w.q)
     reps = 5
 
+    def one(k, v):
+        ragged_paged_attention(w.q, k, v, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale, workspace=ws, planned=True,
+                               out=out)
+
     def body():
         for _ in range(reps):
             for k, v in pools:
-                ragged_paged_attention(w.q, k, v, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale, workspace=ws,
-                                       planned=True, out=out)
+                one(k, v)
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -194,20 +266,78 @@ def decode_attention_roofline(device) -> dict:
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b) * 1e-3 / (reps * len(pools)))
     per_launch = sum(times) / len(times)
+    singles = []
+    for i in range(24):
+        k, v = pools[i % len(pools)]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        one(k, v)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 4:
+            singles.append(a.elapsed_time(b) * 1e-3)
+    serial = sorted(singles)[len(singles) // 2]
     nbytes = w.decode_bytes()
-    peak, which = HBM_FALLBACK_GBS, "fallback"
-    mp = ROOT / "MEASURED_PEAKS.json"
-    if mp.exists():
-        try:
-            peak, which = float(json.loads(mp.read_text())["hbm_gbs"]), "measured"
-        except (ValueError, KeyError):
-            pass
+    peak, which = measured_peak("hbm_gbs", HBM_FALLBACK_GBS)
     achieved = nbytes / per_launch / 1e9
     del pools
     return {"bound": "hbm", "kernel": "paged_decode_kernel (decode rows of ns_ragged_paged_attn)", "achieved": achieved,
             "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": DECODE_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": nbytes, "us_per_launch": per_launch * 1e6,
+            "frac_uses": "us_per_launch_back_to_back",
+            "traffic": DECODE_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": nbytes,
+            "us_per_launch": per_launch * 1e6, "us_per_launch_back_to_back": per_launch * 1e6,
+            "us_per_launch_serialised": serial * 1e6, "achieved_serialised": nbytes / serial / 1e9,
+            "frac_serialised": nbytes / serial / 1e9 / peak,
             "workload": "BASELINE config 1 decode rows: 48 rows, contexts U[128,8192], 14q/2kv heads, hd 64, bf16"}
+
+
+def prefill_attention_roofline(device, n_heads: int = 14, n_kv_heads: int = 2, head_dim: int = 64) -> dict:
+    """The four 512-token prefill chunks of benchmark configuration 1 (cached contexts uniform in 0-2048) through
+    ns_ragged_paged_attn, prefill rows only: 10 calls per CUDA-graph replay, CUDA events, FLOP = 4 * heads * head_dim *
+    (keys seen by every query), against the measured bf16 GEMM peak (burst: the kernel is timed alone)."""
+    from nanoserve_b200.kernels.fused import kv_write
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    w = attention_workload(n_decode=0, n_prefill=4, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+                           num_blocks=8192, device=device)
+    kv_write(w.k_new, w.v_new, w.k_pool, w.v_pool, w.slot_mapping)
+    S = w.seq_lens.shape[0]
+    ws = AttnWorkspace(64, 4096, n_heads, head_dim, device)
+    ws.plan(w.seq_lens, w.cu_seqlens, S, 16)
+    out = torch.empty_like(w.q)
+    reps = 10
+
+    def body():
+        for _ in range(reps):
+            ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale, workspace=ws,
+                                   planned=True, out=out)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        body()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(10):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3 / reps)
+    t = sorted(times)[len(times) // 2]
+    flops = w.prefill_flops()
+    peak, which = measured_peak("bf16_tflops", BF16_FALLBACK_TFLOPS)
+    return {"bound": "tensor", "kernel": "prefill attention kernel of ns_ragged_paged_attn", "achieved": flops / t / 1e12,
+            "peak": peak, "peak_source": which, "unit": "TFLOP/s", "frac": flops / t / 1e12 / peak, "traffic": None,
+            "flops_per_launch": flops, "us_per_launch": t * 1e6,
+            "workload": f"BASELINE config 1 prefill rows: 4 chunks x 512 tokens on U[0,2048] cached, {n_heads}q/{n_kv_heads}kv "
+                        f"heads, hd {head_dim}, bf16 (K/V of one layer: L2-resident, tensor-bound by design)"}
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -269,7 +399,7 @@ def run_gpu_arm(args) -> None:
     eng = LLMEngine(model, eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY, max_num_batched_tokens=2048,
                     lookahead=not args.no_lookahead)
     eng.capture_graphs()
-    reqs = workload()
+    reqs = workload(rank)
 
     for _ in range(args.warmup):
         closed_loop(eng, reqs, CONCURRENCY)
@@ -323,218 +453,52 @@ def run_gpu_arm(args) -> None:
     # every engine step reads back one int64 per scheduled sequence
     d2h_per_pass = 8 * sum(len(p[8:8 + 4 * int(p[0])]) // 4 for _, p in log)
 
-    from nanoserve_b200.replicas import max_over_ranks
-    e2e_max, dev_max = max_over_ranks([e2e_s, dev_s], device)
-    total_tokens = tokens * world
+    from nanoserve_b200.replicas import max_over_ranks, sum_over_ranks
+    e2e_max, dev_max, sync_max = max_over_ranks([e2e_s, dev_s, sync_s], device)
+    # replicas serve different streams: whole-job tokens are summed over ranks
+    total_tokens, total_dev_tokens, total_sync_tokens = sum_over_ranks([tokens, pass_tokens * args.steps, sync_tokens], device)
     line = {
-        "metric": METRIC, "value": pass_tokens * args.steps * world / dev_max, "unit": UNIT, "n_gpus": world,
+        "metric": METRIC, "value": total_dev_tokens / dev_max, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dev_max / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
         "e2e": {"value": total_tokens / e2e_max, "unit": UNIT, "h2d_bytes_per_step": h2d_e2e // args.steps,
                 "d2h_bytes_per_step": d2h_per_pass, "ms_per_step": 1e3 * e2e_max / args.steps,
                 "engine_steps_per_pass": engine_steps // args.steps,
                 "ms_per_engine_step": 1e3 * e2e_max / max(engine_steps, 1), "lookahead": eng.lookahead,
-                "value_without_lookahead": sync_tokens * world / max_over_ranks([sync_s], device)[0]},
+                "value_without_lookahead": total_sync_tokens / sync_max},
         "gpu_launches": launches_dev, "gpu_launches_e2e": launches_e2e,
         "output_tokens_per_pass": pass_tokens, "engine": {k: stats[k] for k in ("graph_steps", "piecewise_steps", "steps",
                                                                                  "num_preemptions", "peak_running")},
         "clocks": clocks.summary(), "host_cpus": os.cpu_count(),
     }
+    line["device_status"] = eng.buffers.status_seen       # bounded waits that ran out in any kernel of any step: must be 0
+    if eng.buffers.status_seen:
+        line["invalid"] = "a kernel gave up on a bounded wait during the run: the numbers above are not a measurement"
     if rank == 0:
         if world == 1:
             line["roofline"] = decode_attention_roofline(device)
+            line["roofline_prefill"] = prefill_attention_roofline(device)
+            # like-for-like leg: configuration 0 (what the CPU arm runs) through this engine's public API
+            eng0 = LLMEngine(model, eos_token_ids=[], lookahead=not args.no_lookahead, **CONFIG0_ENGINE_KW)
+            eng0.capture_graphs()
+            reqs0 = config0_requests()
+            timed_pass(eng0, reqs0, 8)
+            secs0, n0 = min(timed_pass(eng0, reqs0, 8) for _ in range(3))
+            del eng0
+            os.environ.pop("OMP_NUM_THREADS", None)
             sd32, cfg32 = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
-            secs, n = cpu_reference_pass(sd32, cfg32, cpu_sample_requests())
-            line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": cpu_sample_text(), "seconds": secs}
+            threads = pick_cpu_threads(sd32, cfg32)
+            torch.set_num_threads(threads)
+            cpu_reference_pass(sd32, cfg32, reqs0)                       # warm (page in the weights, thread pool)
+            secs, n = cpu_reference_pass(sd32, cfg32, reqs0)
+            line["cpu_baseline"] = {"value": n / secs, "unit": UNIT, "cores": threads, "threads": threads, "kind": "port",
+                                    "workload": "BASELINE config 0", "sample": cpu_sample_text(threads), "seconds": secs,
+                                    "gpu_same_workload_tok_s": n0 / secs0,
+                                    "gpu_same_workload": "this engine, bf16, same 8 requests x 64 tokens, c=8, public API, "
+                                                         "best of 3 passes"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
-
-
-def launch_probe() -> None:
-    """A few engine steps of the benchmark's engine inside a profiler range (cudaProfilerStart/Stop): two pure-decode
-    steps at c=32 (contexts ~500) and one mixed step (a 300-token prefill chunk joining 31 decodes)."""
-    from nanoserve_b200.engine import LLMEngine
-    from nanoserve_b200.model import ModelConfig, Qwen2Model
-    from nanoserve_b200.synthetic import random_state_dict, serving_requests
-    torch.cuda.set_device(0)
-    sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.bfloat16, device="cuda")
-    eng = LLMEngine(Qwen2Model(ModelConfig(**cfg), sd), eos_token_ids=[], max_seq_len=2048, max_num_seqs=CONCURRENCY)
-    reqs = serving_requests(33, prompt_range=(400, 600), output_range=(64, 64))
-    for p, n in reqs[:31]:
-        eng.add_request(p, n, ignore_eos=True)
-    for _ in range(12):
-        eng.step()
-    eng.add_request(reqs[31][0][:300], 8, ignore_eos=True)
-    eng.step()                                    # captures the mixed bucket outside the range
-    for _ in range(3):
-        eng.step()
-    assert eng.last_step.n_prefill == 0
-    eng.add_request(reqs[32][0][:300], 8, ignore_eos=True)
-    torch.cuda.synchronize()
-    torch.cuda.cudart().cudaProfilerStart()
-    kinds = []
-    for _ in range(3):
-        eng.step()
-        kinds.append((eng.last_step.n_prefill, eng.last_step.n_decode, eng.last_step.n_tokens))
-    torch.cuda.synchronize()
-    torch.cuda.cudart().cudaProfilerStop()
-    print(json.dumps({"probe_steps": kinds, "engine": {k: eng.stats[k] for k in ("graph_steps", "piecewise_steps", "steps")}}))
-
-
-def attn_overlap_probe() -> None:
-    """One ragged paged attention call on mixed batches (decode rows + prefill chunks), with the prefill kernel strictly
-    after the decode kernel and beside it (the library's default; a debug hook switches it off): us per call from a CUDA
-    graph of 20 calls, and whether the two outputs are bit-identical. Prints one JSON object."""
-    import ctypes
-    from nanoserve_b200 import _lib
-    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
-    from nanoserve_b200.synthetic import attention_workload
-    hook = _lib.load().ns_debug_overlap_prefill
-    hook.argtypes, hook.restype = [ctypes.c_int], None
-    rows = []
-    for nd, npf, chunk, heads in ((31, 1, 300, (14, 2, 64)), (31, 2, 512, (14, 2, 64)), (16, 1, 128, (14, 2, 64)),
-                                  (48, 4, 512, (14, 2, 64)), (31, 1, 300, (12, 2, 128)), (31, 2, 512, (12, 2, 128))):
-        w = attention_workload(n_decode=nd, decode_range=(300, 1200), n_prefill=npf, chunk=chunk, prefill_ctx_range=(0, 512),
-                               num_blocks=8192, seed=3, n_heads=heads[0], n_kv_heads=heads[1], head_dim=heads[2])
-        ws = AttnWorkspace(64, 4096, heads[0], heads[2], "cuda")
-        ws.plan(w.seq_lens, w.cu_seqlens, w.seq_lens.shape[0], 16)
-        us, outs = {}, {}
-        for mode in (0, 1):
-            hook(mode)
-            call = lambda: ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, w.scale,
-                                                  workspace=ws, planned=True)
-            for _ in range(3):
-                o = call()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                for _ in range(20):
-                    o = call()
-            g.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g.replay()
-            b.record()
-            torch.cuda.synchronize()
-            us[mode], outs[mode] = round(a.elapsed_time(b) * 1e3 / 20, 2), o.clone()
-        hook(1)
-        rows.append({"decode_rows": nd, "prefill_chunks": npf, "chunk_tokens": chunk, "heads": list(heads),
-                     "us_prefill_after_decode": us[0], "us_prefill_beside_decode": us[1],
-                     "identical": bool(torch.equal(outs[0], outs[1]))})
-    print(json.dumps({"attn_overlap_probe": rows}))
-
-
-def layer_probe(rows: int) -> None:
-    """Marginal cost of each kernel of one decode layer INSIDE the layer chain: 24 layers of the engine's kernel sequence
-    for `rows` one-token sequences (contexts U[400,600], Qwen2.5-0.5B shape, distinct weights per layer) captured in one
-    CUDA graph and timed with CUDA events; each variant removes or swaps one kernel. Prints one JSON object (us per
-    layer). Also sweeps the planner's lower bound on a decode CTA's range through a debug hook of the library."""
-    import ctypes
-    import torch.nn.functional as F
-    from nanoserve_b200 import _lib
-    from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
-                                              stream_gemm, swiglu_gemm, thin_gemm, thin_swiglu_gemm)
-    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
-    from nanoserve_b200.synthetic import attention_workload
-    M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
-    W = [dict(qkv=torch.randn(1152, H, device=dev, dtype=bf) * .02, b=torch.randn(1152, device=dev, dtype=bf) * .02,
-              o=torch.randn(H, H, device=dev, dtype=bf) * .02, gu=torch.randn(2 * I, H, device=dev, dtype=bf) * .02,
-              down=torch.randn(H, I, device=dev, dtype=bf) * .02, ln=torch.ones(H, device=dev, dtype=bf)) for _ in range(L)]
-    w = attention_workload(n_decode=M, decode_range=(400, 600), n_prefill=0, num_blocks=4096)
-    ws = AttnWorkspace(64, 64, 14, 64, dev)
-    ws.plan(w.seq_lens, None, M, 16)
-    inv = (1.0 / (1e6 ** (torch.arange(0, 64, 2, dtype=torch.float) / 64))).to(dev)
-    cos, sin = rope_cos_sin(torch.arange(M, device=dev), inv, 64, bf)
-    x0 = torch.randn(M, H, device=dev, dtype=bf)
-    m0 = torch.randn(M, I, device=dev, dtype=bf)
-    q0 = torch.randn(M, 14, 64, device=dev, dtype=bf)
-
-    def chain(qkv="skinny", attn=True, o="cublas", norm1=True, gu="cublas", down="skinny", norm2=True):
-        x = h = x0
-        for l in W:
-            q = q0
-            if qkv == "skinny":
-                q = skinny_gemm(h, l["qkv"], l["b"], split_k=8, epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=w.k_pool,
-                                v_cache=w.v_pool, slots=w.slot_mapping, n_heads=14, n_kv_heads=2)
-            elif qkv == "thin":
-                q = thin_gemm(h, l["qkv"], l["b"], epilogue=EPI_ROPE_KV, cos=cos, sin=sin, k_cache=w.k_pool, v_cache=w.v_pool,
-                              slots=w.slot_mapping, n_heads=14, n_kv_heads=2)
-            if attn:
-                q = ragged_paged_attention(q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, None, 0.125, workspace=ws,
-                                           planned=True)
-            o2 = q.view(M, H)
-            a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else (thin_gemm(o2, l["o"]) if o == "thin" else o2))
-            if norm1:
-                h, x = rms_norm(a, l["ln"], 1e-6, residual=x)
-            else:
-                h = a
-            if gu == "cublas":
-                m = silu_mul(F.linear(h, l["gu"]))
-            elif gu == "umma":
-                m = swiglu_gemm(h, l["gu"])
-            elif gu == "thin":
-                m = thin_swiglu_gemm(h, l["gu"])
-            else:
-                m = stream_gemm(h, l["gu"], epilogue=EPI_SILU_MUL) if gu == "stream" else m0
-            d = skinny_gemm(m, l["down"], split_k=8) if down == "skinny" else (F.linear(m, l["down"]) if down == "cublas" else h)
-            if norm2:
-                h, x = rms_norm(d, l["ln"], 1e-6, residual=x)
-            else:
-                h = d
-        return h
-
-    def us_per_layer(**kw) -> float:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            chain(**kw)
-        torch.cuda.current_stream().wait_stream(side)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            chain(**kw)
-        g.replay()
-        torch.cuda.synchronize()
-        ts = []
-        for _ in range(5):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g.replay()
-            b.record()
-            torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b) * 1e3 / L)
-        return round(sorted(ts)[2], 2)
-
-    engine = dict(qkv="thin", o="thin", gu="stream" if M <= 16 else ("thin" if M <= 32 else "cublas"))
-    e = lambda **kw: dict(engine, **kw)      # the engine's chain with one kernel removed or swapped
-    variants = {"engine chain": engine,
-                "engine chain again (order effect of the probe)": engine,
-                "no gate_up": e(gu=None), "no attention": e(attn=False), "no down": e(down=None), "no qkv": e(qkv=None),
-                "no o_proj": e(o=None), "no norm1": e(norm1=False), "no norm2": e(norm2=False),
-                "gate_up on cublas + silu kernel": e(gu="cublas"), "gate_up on thin_swiglu": e(gu="thin"),
-                "gate_up on stream_gemm": e(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": e(gu="umma"),
-                "qkv on skinny_gemm (split-K cluster)": e(qkv="skinny"), "o_proj on cublas": e(o="cublas"),
-                "o_proj on stream_gemm": e(o="stream"), "down on cublas": e(down="cublas"),
-                "before the 8-row-tile kernels: qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}}
-    def try_variant(kw):
-        try:
-            return us_per_layer(**kw)
-        except Exception as e:       # a kernel that does not take this row count
-            torch.cuda.synchronize()
-            return f"n/a ({type(e).__name__})"
-    out = {"rows": M, "us_per_layer": {k: try_variant(kw) for k, kw in variants.items()}}
-    hook = _lib.load().ns_debug_min_blocks
-    hook.argtypes, hook.restype = [ctypes.c_int], None
-    sweep = {}
-    for mb in (32, 16, 8, 4):
-        hook(mb)
-        ws.plan(w.seq_lens, None, M, 16)
-        torch.cuda.synchronize()
-        sweep[str(mb)] = round(us_per_layer() - us_per_layer(attn=False), 2)
-    hook(0)
-    out["attention_us_per_layer_by_min_blocks_per_cta"] = sweep
-    print(json.dumps(out))
 
 
 def timed_pass(eng, reqs, concurrency) -> tuple[float, int]:
@@ -620,14 +584,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--launch-probe", action="store_true",
-                    help="short run for `ncu --profile-from-start off` launch lists: 2 decode steps at c=32 + 1 mixed step")
-    ap.add_argument("--attn-overlap-probe", action="store_true",
-                    help="mixed-batch attention calls with the prefill kernel after / beside the decode kernel")
-    ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS",
-                    help="marginal cost of each kernel of one decode layer inside the layer chain, for ROWS sequences")
     ap.add_argument("--roofline-only", action="store_true",
-                    help="run only the decode-attention roofline leg (the small case used for ncu captures)")
+                    help="run only the decode-attention roofline leg (the case used for ncu captures)")
+    ap.add_argument("--prefill", action="store_true",
+                    help="with --roofline-only: the prefill-attention leg instead (configuration 1's four chunks)")
+    ap.add_argument("--head-dim", type=int, default=64, help="with --roofline-only --prefill: 64 (14/2 heads) or 128 (12/2)")
     ap.add_argument("--workload", default="serve", choices=["serve", "sweep", "prefix", "tp"],
                     help="serve = the benchmark contract's line (default); the others print one JSON object of extras")
     ap.add_argument("--requests", type=int, default=0)
@@ -636,15 +597,14 @@ def main() -> None:
     args = ap.parse_args()
     if args.workload != "serve":
         extra_workload(args)
-    elif args.launch_probe:
-        launch_probe()
-    elif args.layer_probe:
-        layer_probe(args.layer_probe)
-    elif args.attn_overlap_probe:
-        attn_overlap_probe()
     elif args.roofline_only:
         torch.cuda.set_device(0)
-        print(json.dumps({"roofline": decode_attention_roofline(torch.device("cuda", 0))}))
+        dev0 = torch.device("cuda", 0)
+        if args.prefill:
+            heads = (14, 2, 64) if args.head_dim == 64 else (12, 2, 128)
+            print(json.dumps({"roofline_prefill": prefill_attention_roofline(dev0, *heads)}))
+        else:
+            print(json.dumps({"roofline": decode_attention_roofline(dev0)}))
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

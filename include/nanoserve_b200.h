@@ -35,6 +35,30 @@ const char* ns_last_error(void);
 /* Number of SMs of the current device (grid sizing of the persistent kernels); <= 0 on error. */
 int ns_sm_count(void);
 
+/* Process-wide tuning knobs of the attention planner and dispatcher, read on the host when a call is issued (so a
+ * captured CUDA graph keeps the values it was captured with, except those the plan kernel receives as arguments).
+ * They exist for A/B measurements and for tests that force a path; serving code leaves them at their defaults.
+ * No counterpart in the reference (its Triton kernels have a fixed grid, nanoserve/kernels/paged_attention.py:84-105). */
+typedef enum {
+    NS_TUNE_PREFILL_IMPL = 0,        /* 0 (default): tcgen05 prefill kernel where supported; 1: always the mma.sync kernel */
+    NS_TUNE_PREFILL_OVERLAP = 1,     /* 1 (default): a mixed call's prefill kernel runs beside its decode kernel; 0: after it */
+    NS_TUNE_DECODE_SPLIT_BLOCKS = 2, /* decode KV blocks above which a step runs two virtual CTAs per CTA; < 0 (default): built-in */
+    NS_TUNE_DECODE_MIN_BLOCKS = 3,   /* lower bound of a decode CTA's range in KV blocks; <= 0 (default): built-in */
+    NS_TUNE_DECODE_SNAP_BLOCKS = 4,  /* how far a cut may move to reach a row boundary; <= 0 (default): built-in */
+    NS_TUNE_DECODE_BALANCE = 5,      /* 2 (default): row-aligned balanced cuts for large steps; 0: equal cuts snapped to rows */
+    NS_TUNE_COUNT = 6
+} ns_tuning_knob;
+int ns_set_tuning(int knob, int value);
+int ns_get_tuning(int knob);
+
+/* One status word per engine step, written on the device: *status = number of bounded waits that have run out so far
+ * in this library's kernels on the current device (bulk-copy / mbarrier waits of the decode GEMMs, tcgen05 waits of the
+ * prefill attention kernel counted in attn_workspace's plan header; attn_workspace may be NULL). The counts are
+ * cumulative; a caller compares with the value it saw last. Results of a launch that raised the count are undefined.
+ * Graph-capturable once it has run once on the device outside capture (it resolves device symbol addresses then).
+ * No counterpart in the reference (device code there never reports errors, nanoserve/kernels/fused.py). */
+int ns_collect_status(const void* attn_workspace, int64_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused token-wise ops.
  * ---------------------------------------------------------------------------------------------- */

@@ -12,6 +12,9 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libnanoserve_b200.so"
 
 NS_BF16, NS_F32 = 0, 1
+# ns_tuning_knob
+(TUNE_PREFILL_IMPL, TUNE_PREFILL_OVERLAP, TUNE_DECODE_SPLIT_BLOCKS, TUNE_DECODE_MIN_BLOCKS, TUNE_DECODE_SNAP_BLOCKS,
+ TUNE_DECODE_BALANCE) = range(6)
 
 # name -> (restype, argtypes); mirrors include/nanoserve_b200.h declaration by declaration.
 _P, _I32, _I64, _F = c_void_p, c_int32, c_int64, c_float
@@ -19,6 +22,9 @@ SIGNATURES: dict[str, tuple] = {
     "ns_version": (c_int, []),
     "ns_last_error": (c_char_p, []),
     "ns_sm_count": (c_int, []),
+    "ns_set_tuning": (c_int, [c_int, c_int]),
+    "ns_get_tuning": (c_int, [c_int]),
+    "ns_collect_status": (c_int, [_P, _P, _P]),
     "ns_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, _F, c_int, _P]),
     "ns_silu_mul": (c_int, [_P, _P, _I64, _I32, c_int, _P]),
     "ns_rope_cos_sin": (c_int, [_P, _P, _P, _P, _I64, _I32, c_int, _P]),
@@ -84,6 +90,15 @@ def call(name: str, *args) -> None:
     launch_count += _LAUNCHES_PER_CALL.get(name, 1)
     if status != 0:
         raise NanoserveB200Error(f"{name} failed (status {status}): {lib.ns_last_error().decode()}")
+
+
+def set_tuning(knob: int, value: int) -> int:
+    """Set a process-wide tuning knob (ns_set_tuning); returns the previous value."""
+    lib = load()
+    old = lib.ns_get_tuning(knob)
+    if lib.ns_set_tuning(knob, value) != 0:
+        raise NanoserveB200Error(f"ns_set_tuning failed: {lib.ns_last_error().decode()}")
+    return old
 
 
 def note_launches(n: int) -> None:

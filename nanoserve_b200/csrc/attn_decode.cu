@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     // its RoPE + KV-write epilogue) is still running. Until pdl_wait() below it touches only what earlier steps and
     // the step's plan left behind: the plan records, the block tables and the K/V rows of OLDER tokens.
     if (!p.overlap_prefill) pdl_launch_dependents();          // o_proj may start fetching its weights while attention runs
+    if (p.plan_fresh) pdl_wait();                             // the plan is the predecessor's output: nothing is read before
     if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4] = global_ns();
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     const int32_t* __restrict__ cta_start = reinterpret_cast<const int32_t*>(p.ws + p.L.cta_start);
@@ -597,13 +598,13 @@ template <int HD, int NWARPS, int STAGES, int CTAS_PER_SM, int MAX_MODE>
 static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
     constexpr int smem = NWARPS * STAGES * (2 * 16 * HD * 2) + 2 * kMaxKvHeads * (16 * 16 + 16) * 4;
     static_assert(8 * (HD + 4) * 4 <= 2 * 16 * HD * 2, "the combine scratch must fit in one stage");
-    static bool configured = false;
-    if (!configured) {
+    static SmemOptIn optin;
+    if (optin.needs((size_t)smem)) {
         cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "decode attention: cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
-        configured = true;
+        optin.done((size_t)smem);
     }
     launch_pdl(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>, dim3(sms * CTAS_PER_SM), dim3(NWARPS * 32), smem, st, p);
     return check_launch("paged_decode");

@@ -32,7 +32,6 @@ constexpr int kStaticMaxBatch = 64;
 constexpr int kStaticMaxHeads = 32;
 constexpr int kStaticMaxHeadDim = 128;
 constexpr int kStaticMaxCtas = 320;       // persistent decode CTAs the layout has room for (2 per SM up to 160 SMs)
-constexpr int kMaxDevices = 64;
 
 // Upper bound of ws_layout(kStaticMaxBatch, kStaticMaxBatch, kStaticMaxHeads, kStaticMaxHeadDim, kStaticMaxCtas):
 // partials 320*2*32*132*4 = 10.8 MB plus a few KB of plan arrays.
@@ -119,5 +118,6 @@ extern "C" int ns_paged_attn_decode_static(const void* q, const void* k_pool, co
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.timeline = nullptr;
+    a.plan_fresh = 1;                 // the plan kernel above is this launch's direct predecessor
     return launch_paged_decode(a, head_dim, sms, st);
 }

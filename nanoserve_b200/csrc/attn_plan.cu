@@ -243,20 +243,15 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     }
 }
 
-static int g_min_blocks = kMinBlocksPerCta;
-static int g_split_blocks = kSplitBlocks;
-static int g_snap_blocks = kSnapBlocks;
-static int g_balance = 2;
-void debug_set_balance(int on) { g_balance = on; }
-void debug_set_snap_blocks(int n) { g_snap_blocks = n > 0 ? n : kSnapBlocks; }
-void debug_set_min_blocks(int n) { g_min_blocks = n > 0 ? n : kMinBlocksPerCta; }
-void debug_set_split_blocks(int n) { g_split_blocks = n >= 0 ? n : kSplitBlocks; }
+void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance);      // c_api.cu: ns_set_tuning
 
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
                      int block_size, int base_ctas, int max_mode,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
+    int min_blocks, split_blocks, snap_blocks, balance;
+    plan_knobs(&min_blocks, &split_blocks, &snap_blocks, &balance);
     attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, base_ctas, max_mode,
-                                                 g_split_blocks, (uint8_t*)ws, L, max_items, g_min_blocks, g_snap_blocks, g_balance);
+                                                 split_blocks, (uint8_t*)ws, L, max_items, min_blocks, snap_blocks, balance);
     return check_launch("attn_plan");
 }
 

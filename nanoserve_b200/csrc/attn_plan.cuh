@@ -37,6 +37,9 @@ struct PlanHeader {
     int32_t n_seqs;
     int32_t block_size;
     int32_t mode;           // 1: one range per decode CTA; 2: every decode CTA runs two virtual CTAs of half its warps
+    int32_t errors;         // bounded waits of the attention kernels that ran out (cumulative; only the host clears it:
+                            // the plan kernel leaves this word alone, the workspace starts zero-filled)
+    int32_t pad[7];
 };
 
 // Byte offsets inside the workspace; everything 256-byte aligned.
@@ -97,6 +100,12 @@ struct AttnParams {
     // kernel runs beside it and waits for the decode kernel's completion before it exits, which keeps the stream's
     // order for whatever comes next.
     int overlap_prefill = 0;
+    // 1: the plan in `ws` was written by the launch directly before this one in the stream (a call that plans and
+    // attends in one go). A kernel launched with programmatic stream serialization sees its predecessor's writes only
+    // after griddepcontrol.wait, so the decode kernel then waits BEFORE its first read of the workspace instead of
+    // prefetching plan records, block ids and K/V tiles ahead of the wait. 0: the plan is older (an engine step plans
+    // once, several kernels before the first layer's attention) and the early reads are safe.
+    int plan_fresh = 0;
 };
 
 }  // namespace ns

@@ -185,12 +185,12 @@ __global__ void __launch_bounds__(256) prefill_mma_kernel(const AttnParams p) {
 
 template <int HD, int STAGES> static int launch_prefill_cfg(const AttnParams& p, int max_items, cudaStream_t st) {
     constexpr int smem = STAGES * 2 * 64 * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static SmemOptIn optin;
+    if (optin.needs((size_t)smem)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention: cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
-        configured = true;
+        optin.done((size_t)smem);
     }
     dim3 grid((unsigned)max_items, (unsigned)p.n_kv_heads);
     if (p.overlap_prefill) {

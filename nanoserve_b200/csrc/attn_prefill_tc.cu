@@ -299,8 +299,8 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
             *reinterpret_cast<uint4*>(dst + c * 8) = v;
         }
     }
-    if (!ok && tid == 0)        // a wait expired: leave a mark the host can read (plan header, last word)
-        atomicExch(reinterpret_cast<int*>(p.ws + p.L.header) + 7, 1);
+    if (!ok && tid == 0)        // a wait expired: count it where the host can read it (ns_collect_status)
+        atomicAdd(&reinterpret_cast<PlanHeader*>(p.ws + p.L.header)->errors, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
@@ -317,12 +317,12 @@ bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_s
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st) {
     if (max_items <= 0) return NS_OK;
     constexpr int smem = (tc::kRows + 2 * tc::kStages * tc::kKeys + tc::kRows) * 128 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static SmemOptIn optin;
+    if (optin.needs((size_t)smem)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
-        configured = true;
+        optin.done((size_t)smem);
     }
     dim3 grid((unsigned)max_items, (unsigned)p.n_kv_heads);
     if (p.overlap_prefill) {

@@ -36,42 +36,56 @@ bool prefill_mma_supported(int n_heads, int n_kv_heads, int head_dim, int block_
 int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
-static int g_prefill_impl = 0;          // 0 = tcgen05 where supported, 1 = always the mma.sync kernel
-static int g_overlap_prefill = 1;       // 1 = the prefill kernel of a mixed step runs beside the decode kernel
+// Process-wide tuning knobs (ns_set_tuning); read on the host when a call is issued.
+static int g_tuning[NS_TUNE_COUNT] = {0, 1, -1, 0, 0, 2};
+// The workspace / stream of the newest ns_attn_plan issued by this thread that no attention call has used yet: the
+// first attention launch after a plan on the same stream is its direct successor and must not read the plan ahead of
+// its dependency wait (AttnParams::plan_fresh).
+static thread_local const void* g_fresh_plan_ws = nullptr;
+static thread_local cudaStream_t g_fresh_plan_stream = nullptr;
 
-static long long* g_timeline = nullptr;
-static int g_sm_count = 0;
+// Per-device SM count (a process may drive several GPUs).
+static int g_sm_count[kMaxDevices] = {};
 static int sm_count() {
-    if (g_sm_count <= 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-        g_sm_count = n;
-    }
-    return g_sm_count;
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices && g_sm_count[dev] > 0) return g_sm_count[dev];
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices) g_sm_count[dev] = n;
+    return n;
+}
+
+int device_sm_count() { return sm_count(); }
+
+void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance) {
+    *min_blocks = g_tuning[NS_TUNE_DECODE_MIN_BLOCKS] > 0 ? g_tuning[NS_TUNE_DECODE_MIN_BLOCKS] : kMinBlocksPerCta;
+    *split_blocks = g_tuning[NS_TUNE_DECODE_SPLIT_BLOCKS] >= 0 ? g_tuning[NS_TUNE_DECODE_SPLIT_BLOCKS] : kSplitBlocks;
+    *snap_blocks = g_tuning[NS_TUNE_DECODE_SNAP_BLOCKS] > 0 ? g_tuning[NS_TUNE_DECODE_SNAP_BLOCKS] : kSnapBlocks;
+    *balance = g_tuning[NS_TUNE_DECODE_BALANCE];
 }
 
 }  // namespace ns
 
 using namespace ns;
 
-namespace ns { void debug_set_min_blocks(int n); void debug_set_split_blocks(int n); void debug_set_snap_blocks(int n); }
-extern "C" void ns_debug_snap_blocks(int n) { ns::debug_set_snap_blocks(n); }
-namespace ns { void debug_set_balance(int on); }
-// Debug hook (not part of the public header): 0 = equal cuts snapped to row boundaries also for large steps.
-extern "C" void ns_debug_balance(int on) { ns::debug_set_balance(on); }
-// Debug hook (not part of the public header): decode KV blocks above which a step runs two virtual CTAs per CTA (< 0 = default).
-extern "C" void ns_debug_split_blocks(int n) { ns::debug_set_split_blocks(n); }
-// Debug hook (not part of the public header): lower bound of a decode CTA's range in KV blocks (0 = default).
-extern "C" void ns_debug_min_blocks(int n) { ns::debug_set_min_blocks(n); }
+extern "C" int ns_set_tuning(int knob, int value) {
+    NS_REQUIRE(knob >= 0 && knob < NS_TUNE_COUNT, NS_ERR_INVALID_ARG, "set_tuning: unknown knob %d", knob);
+    g_tuning[knob] = value;
+    return NS_OK;
+}
+extern "C" int ns_get_tuning(int knob) { return (knob >= 0 && knob < NS_TUNE_COUNT) ? g_tuning[knob] : 0; }
 
-extern "C" int ns_version(void) { return 100; }
+extern "C" int ns_version(void) { return 101; }
 extern "C" const char* ns_last_error(void) { return g_err; }
 extern "C" int ns_sm_count(void) { return sm_count(); }
+
+#ifdef NS_DEBUG_HOOKS
+static long long* g_timeline = nullptr;
+// Profiling build only: 4 globaltimer stamps per decode CTA are written to this device buffer.
 extern "C" void ns_debug_decode_timeline(long long* device_buffer) { g_timeline = device_buffer; }
-extern "C" void ns_debug_prefill_impl(int impl) { g_prefill_impl = impl; }
-// Debug hook (not part of the public header): 0 = prefill kernel strictly after the decode kernel of the same call.
-extern "C" void ns_debug_overlap_prefill(int on) { g_overlap_prefill = on; }
+#else
+static long long* const g_timeline = nullptr;
+#endif
 
 extern "C" int64_t ns_attn_workspace_bytes(int32_t max_seqs, int32_t max_tokens, int32_t n_heads, int32_t head_dim) {
     if (max_seqs <= 0 || max_tokens < 0 || n_heads <= 0 || head_dim <= 0) return -1;
@@ -94,7 +108,12 @@ static int plan_impl(const int32_t* seq_lens, const int32_t* cu_seqlens, const i
     NS_REQUIRE(ctas * max_mode <= kMaxDecodeCtas, NS_ERR_UNSUPPORTED, "attn_plan: %d decode CTAs exceed the workspace layout",
                ctas * max_mode);
     const int max_items = ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
-    return launch_attn_plan(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, ctas, max_mode, ws, L, max_items, st);
+    const int rc = launch_attn_plan(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, ctas, max_mode, ws, L, max_items, st);
+    if (rc == NS_OK) {
+        g_fresh_plan_ws = ws;
+        g_fresh_plan_stream = st;
+    }
+    return rc;
 }
 
 extern "C" int ns_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows,
@@ -155,7 +174,9 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads; a.scale_log2 = scale * kLog2e;
     a.timeline = g_timeline;
     const bool has_prefill = cu_seqlens != nullptr && n_tokens > n_seqs;
-    a.overlap_prefill = (has_prefill && g_overlap_prefill) ? 1 : 0;
+    a.overlap_prefill = (has_prefill && g_tuning[NS_TUNE_PREFILL_OVERLAP]) ? 1 : 0;
+    a.plan_fresh = (g_fresh_plan_ws == workspace && g_fresh_plan_stream == st) ? 1 : 0;
+    g_fresh_plan_ws = nullptr;
     int rc = launch_paged_decode(a, head_dim, sms, st);
     if (rc != NS_OK) return rc;
     if (cu_seqlens != nullptr && n_tokens > n_seqs) {
@@ -163,7 +184,7 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
         int64_t max_items = n_tokens / kPrefillTileTokens + n_seqs;
         const int64_t cap = (int64_t)ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
         if (max_items > cap) max_items = cap;
-        if (g_prefill_impl == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size))
+        if (g_tuning[NS_TUNE_PREFILL_IMPL] == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size))
             rc = launch_prefill_tc(a, (int)max_items, st);
         else
             rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
@@ -191,4 +212,37 @@ extern "C" int ns_paged_attn_decode(const void* q, const void* k_pool, const voi
                                 n_kv_heads, head_dim, block_size, table_stride, q_stride, out_stride, pool_block_stride,
                                 pool_pos_stride, pool_head_stride, scale, dtype, workspace, workspace_bytes, ws_max_seqs,
                                 ws_max_tokens, stream);
+}
+
+// ---- one status word per engine step -----------------------------------------------------------------------------
+namespace ns {
+int stream_gemm_error_counter(const unsigned int** out);
+int thin_gemm_error_counter(const unsigned int** out);
+int umma_gemm_error_counter(const unsigned int** out);
+int skinny_gemm_error_counter(const unsigned int** out);
+
+__global__ void collect_status_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, const unsigned int* d,
+                                      const int32_t* ws_errors,
+                                      int64_t* out) {
+    if (threadIdx.x == 0)
+        *out = (int64_t)*a + (int64_t)*b + (int64_t)*c + (int64_t)*d + (ws_errors != nullptr ? (int64_t)*ws_errors : 0);
+}
+}  // namespace ns
+
+extern "C" int ns_collect_status(const void* attn_workspace, int64_t* status, void* stream) {
+    NS_REQUIRE(status != nullptr, NS_ERR_INVALID_ARG, "collect_status: null pointer");
+    const unsigned int *a = nullptr, *b = nullptr, *c = nullptr, *d = nullptr;
+    int rc = thin_gemm_error_counter(&a);
+    if (rc == NS_OK) rc = stream_gemm_error_counter(&b);
+    if (rc == NS_OK) rc = umma_gemm_error_counter(&c);
+    if (rc == NS_OK) rc = skinny_gemm_error_counter(&d);
+    if (rc != NS_OK) return rc;
+    const int32_t* ws_errors = nullptr;
+    if (attn_workspace != nullptr) {
+        // the header is the first region of every layout, whatever the sizes it was built for
+        const WsLayout L = ws_layout(1, 1, 1, 1);
+        ws_errors = &reinterpret_cast<const PlanHeader*>(static_cast<const uint8_t*>(attn_workspace) + L.header)->errors;
+    }
+    collect_status_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a, b, c, d, ws_errors, status);
+    return check_launch("collect_status");
 }

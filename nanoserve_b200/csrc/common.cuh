@@ -11,11 +11,26 @@ namespace ns {
 // ---- host-side error plumbing (c_api.cu owns the storage) -------------------------------------------------
 int fail(int status, const char* fmt, ...);
 int check_launch(const char* what);
+int device_sm_count();      // SMs of the current device; <= 0 when none can be queried
 
 #define NS_REQUIRE(cond, status, ...)                 \
     do {                                              \
         if (!(cond)) return ns::fail(status, __VA_ARGS__); \
     } while (0)
+
+// The dynamic shared-memory opt-in (cudaFuncAttributeMaxDynamicSharedMemorySize) is a per-DEVICE attribute of a kernel:
+// a process that drives several GPUs has to repeat it on each one. One static instance per launcher remembers, per
+// device ordinal, the largest size already opted in.
+constexpr int kMaxDevices = 64;
+struct SmemOptIn {
+    size_t have[kMaxDevices] = {};
+    int dev = -1;
+    bool needs(size_t smem) {
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { dev = -1; return true; }
+        return smem > have[dev];
+    }
+    void done(size_t smem) { if (dev >= 0) have[dev] = smem; }
+};
 
 // ---- scalar conversions -------------------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);

@@ -225,7 +225,11 @@ __global__ void __launch_bounds__(256) kv_write_kernel(const T* __restrict__ k_n
     }
 }
 
-static inline unsigned grid_for(int64_t work_items, int threads, int max_ctas = 148 * 8) {
+// Grid of a grid-stride kernel: enough CTAs for the work, at most 8 resident CTAs per SM of the current device.
+static inline unsigned grid_for(int64_t work_items, int threads) {
+    int sms = device_sm_count();
+    if (sms <= 0) sms = 148;
+    const int max_ctas = sms * 8;
     int64_t g = (work_items + threads - 1) / threads;
     if (g < 1) g = 1;
     if (g > max_ctas) g = max_ctas;

@@ -24,6 +24,9 @@ namespace cg = cooperative_groups;
 
 namespace ns {
 
+__device__ unsigned int g_skinny_errors = 0;   // bulk copies that did not land within the bounded wait (never expected)
+
+
 enum GemmEpilogue { kEpiBias = 0, kEpiSiluMul = 1, kEpiRopeKv = 2 };
 
 struct GemmParams {
@@ -201,6 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     __syncthreads();                                     // prologue stores / zero rows visible to every warp
     bool landed = mbar_wait_bounded(mb_w, 0);
     if (p.ln_w == nullptr) landed = mbar_wait_bounded(mb_a, 0) && landed;
+    if (!landed && lane == 0) atomicAdd(&g_skinny_errors, 1u);       // reported through ns_collect_status
     if (landed) {
         // fragments one k-step ahead of the mma that use them (ldmatrix -> mma back to back was ~100 cycles per k-step)
         struct Frag { uint32_t b[4]; uint32_t a[MT][4]; };
@@ -314,12 +318,12 @@ namespace ns {
 template <int MT, int EPI>
 static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
     const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + 128 + (size_t)(16 * MT + 8) * kBN * 4;
-    static size_t configured = 0;
-    if (smem > configured) {
+    static SmemOptIn optin;
+    if (optin.needs(smem)) {
         cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
-        configured = smem;
+        optin.done(smem);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)tiles, (unsigned)split_k, 1);
@@ -344,6 +348,22 @@ template <int EPI> static int dispatch_mt(const GemmParams& p, int tiles, int sp
     if (p.M <= 16) return launch_skinny<1, EPI>(p, tiles, split_k, st);
     if (p.M <= 32) return launch_skinny<2, EPI>(p, tiles, split_k, st);
     return launch_skinny<4, EPI>(p, tiles, split_k, st);
+}
+
+// Device address of this file's error counter on the current device (resolved once per device; the first call on a
+// device must come before any stream capture). Used by ns_collect_status.
+int skinny_gemm_error_counter(const unsigned int** out) {
+    static const unsigned int* addr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(NS_ERR_CUDA, "skinny_gemm_error_counter: no current device");
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_skinny_errors);
+        if (e != cudaSuccess || p == nullptr) return fail(NS_ERR_CUDA, "skinny_gemm_error_counter: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<const unsigned int*>(p);
+    }
+    *out = addr[dev];
+    return NS_OK;
 }
 
 }  // namespace ns

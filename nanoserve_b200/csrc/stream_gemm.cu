@@ -472,12 +472,12 @@ static int launch_stream(const StreamGemmParams& p0, cudaStream_t st) {
     if (stages > per_cta) stages = per_cta < 2 ? 2 : per_cta;
     p.stages = stages;
     const size_t smem = (size_t)stages * STAGE + fixed;
-    static size_t configured = 0;
-    if (smem > configured) {
+    static SmemOptIn optin;
+    if (optin.needs(smem)) {
         cudaError_t e = cudaFuncSetAttribute(stream_gemm_kernel<MT, KS, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "stream_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
-        configured = smem;
+        optin.done(smem);
     }
     cudaError_t e = launch_pdl(stream_gemm_kernel<MT, KS, EPI>, dim3((unsigned)grid), dim3(kSgThreads), smem, st, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "stream_gemm: launch failed: %s", cudaGetErrorString(e));
@@ -538,7 +538,27 @@ extern "C" int ns_stream_gemm(const void* x, const void* residual, const void* l
 }
 
 // Debug hook (not part of the public header): clock64 stamps of CTA 0 thread 0 go to `buf` (device memory, 64 slots).
+#ifdef NS_DEBUG_HOOKS
 extern "C" void ns_debug_stream_gemm_timeline(long long* buf) { g_sg_timeline = buf; }
+#endif
+
+namespace ns {
+// Device address of this file's error counter on the current device (resolved once per device; the first call on a
+// device must come before any stream capture). Used by ns_collect_status.
+int stream_gemm_error_counter(const unsigned int** out) {
+    static const unsigned int* addr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(NS_ERR_CUDA, "stream_gemm_error_counter: no current device");
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_stream_gemm_errors);
+        if (e != cudaSuccess || p == nullptr) return fail(NS_ERR_CUDA, "stream_gemm_error_counter: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<const unsigned int*>(p);
+    }
+    *out = addr[dev];
+    return NS_OK;
+}
+}  // namespace ns
 
 extern "C" int ns_stream_gemm_errors(uint32_t* count) {
     NS_REQUIRE(count != nullptr, NS_ERR_INVALID_ARG, "stream_gemm_errors: null pointer");

@@ -422,12 +422,12 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
 template <int MT>
 int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out, int M, int K, int inter, cudaStream_t st) {
     const size_t smem = (size_t)(16 * MT + kSwTiles * 8) * ((size_t)K * 2 + 16);
-    static size_t configured = 0;
-    if (smem > configured) {
+    static SmemOptIn optin;
+    if (optin.needs(smem)) {
         cudaError_t e = cudaFuncSetAttribute(thin_swiglu_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_swiglu_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
-        configured = smem;
+        optin.done(smem);
     }
     const int grid = (inter / 4 + kSwTiles - 1) / kSwTiles;
     cudaError_t e = launch_pdl(thin_swiglu_kernel<MT>, dim3((unsigned)grid), dim3(kSwThreads), smem, st, x, w, out, M, K, inter);
@@ -435,8 +435,12 @@ int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bflo
     return NS_OK;
 }
 
-// n-tiles per CTA: one while N / 8 CTAs are a single wave of a 148-SM part, else two if that makes them one
-inline int thin_ntiles(int N) { return (N / kThinRows <= 148 || N % (2 * kThinRows) != 0) ? 1 : 2; }
+// n-tiles per CTA: one while N / 8 CTAs are a single wave of the device's SMs, else two if that makes them one
+inline int thin_ntiles(int N) {
+    int sms = device_sm_count();
+    if (sms <= 0) sms = 148;              // no device to ask (argument validation on a machine without one): B200
+    return (N / kThinRows <= sms || N % (2 * kThinRows) != 0) ? 1 : 2;
+}
 inline size_t thin_smem(int mp, int nt, int K) {
     return (size_t)(kThinRows * nt + mp) * ((size_t)K * 2 + 16) + (size_t)4 * nt * mp * 8 * 4;
 }
@@ -444,12 +448,12 @@ inline size_t thin_smem(int mp, int nt, int K) {
 template <int MT, int NT, int EPI>
 int launch_thin(const ThinParams& p, cudaStream_t st) {
     const size_t smem = thin_smem(16 * MT, NT, p.K);
-    static size_t configured = 0;
-    if (smem > configured) {
+    static SmemOptIn optin;
+    if (optin.needs(smem)) {
         cudaError_t e = cudaFuncSetAttribute(thin_gemm_kernel<MT, NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
-        configured = smem;
+        optin.done(smem);
     }
     const int tiles = p.N / (kThinRows * NT);
     cudaError_t e = launch_pdl(thin_gemm_kernel<MT, NT, EPI>, dim3((unsigned)tiles), dim3(kThinThreads), smem, st, p);
@@ -522,6 +526,24 @@ extern "C" int ns_thin_swiglu_gemm(const void* x, const void* w, void* out, int3
     if (M <= 16) return launch_thin_swiglu<1>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
     return launch_thin_swiglu<2>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
 }
+
+namespace ns {
+// Device address of this file's error counter on the current device (resolved once per device; the first call on a
+// device must come before any stream capture). Used by ns_collect_status.
+int thin_gemm_error_counter(const unsigned int** out) {
+    static const unsigned int* addr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(NS_ERR_CUDA, "thin_gemm_error_counter: no current device");
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_thin_errors);
+        if (e != cudaSuccess || p == nullptr) return fail(NS_ERR_CUDA, "thin_gemm_error_counter: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<const unsigned int*>(p);
+    }
+    *out = addr[dev];
+    return NS_OK;
+}
+}  // namespace ns
 
 extern "C" int ns_thin_gemm_errors(int32_t* count) {
     NS_REQUIRE(count != nullptr, NS_ERR_INVALID_ARG, "thin_gemm_errors: null pointer");

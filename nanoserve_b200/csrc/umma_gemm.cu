@@ -333,12 +333,12 @@ static int launch(const void* x, const void* w, Params p, cudaStream_t st) {
     if (rc != NS_OK) return rc;
     rc = make_map(&x_map, x, p.M, p.K, NT);
     if (rc != NS_OK) return rc;
-    static size_t configured = 0;
-    if (smem > configured) {
+    static SmemOptIn optin;
+    if (optin.needs(smem)) {
         cudaError_t e = cudaFuncSetAttribute(swiglu_umma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "swiglu_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
-        configured = smem;
+        optin.done(smem);
     }
     cudaError_t e = launch_pdl(swiglu_umma_kernel<NT>, dim3((unsigned)grid), dim3(kRows), smem, st, w_main, w_one, x_map, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "swiglu_gemm: launch failed: %s", cudaGetErrorString(e));
@@ -368,7 +368,27 @@ extern "C" int ns_swiglu_gemm(const void* x, const void* w_gate_up, void* out, i
 }
 
 // Debug hook (not part of the public header): clock64 stamps of CTA 0 go to `buf` (device memory, 64 slots).
+#ifdef NS_DEBUG_HOOKS
 extern "C" void ns_debug_umma_timeline(long long* buf) { ns::ug::g_timeline = buf; }
+#endif
+
+namespace ns {
+// Device address of this file's error counter on the current device (resolved once per device; the first call on a
+// device must come before any stream capture). Used by ns_collect_status.
+int umma_gemm_error_counter(const unsigned int** out) {
+    static const unsigned int* addr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(NS_ERR_CUDA, "umma_gemm_error_counter: no current device");
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, ug::g_errors);
+        if (e != cudaSuccess || p == nullptr) return fail(NS_ERR_CUDA, "umma_gemm_error_counter: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<const unsigned int*>(p);
+    }
+    *out = addr[dev];
+    return NS_OK;
+}
+}  // namespace ns
 
 extern "C" int ns_umma_gemm_errors(uint32_t* count) {
     NS_REQUIRE(count != nullptr, NS_ERR_INVALID_ARG, "umma_gemm_errors: null pointer");

@@ -30,6 +30,10 @@ _HEADER_INTS = 8
 _SIDE_STREAM = None
 
 
+class DeviceStatusError(_lib.NanoserveB200Error):
+    """A kernel of an engine step gave up on a bounded wait (the library's status word grew)."""
+
+
 def _capture_stream() -> torch.cuda.Stream:
     """One warm-up stream for every capture in the process (a fresh stream per capture keeps a cuBLAS workspace
     alive each, cuda_graphs.py:33-39)."""
@@ -84,10 +88,14 @@ class StepBuffers:
         self.seq_lens = torch.ones(self.max_seqs, **i32)
         self.seat_of = torch.full((self.max_seqs,), self.pad_seat, **i32)
         self.last_rows = torch.zeros(self.max_seqs, **i64)
-        self.sampled = torch.zeros(self.max_seqs, **i64)
+        # word 0: the library's status word of the step (ns_collect_status); words 1..: the sampled tokens. One
+        # device->host copy per step brings back both.
+        self.fetched = torch.zeros(1 + self.max_seqs, **i64)
+        self.sampled = self.fetched[1:]
+        self.status_seen = 0              # status word of the newest step that was read back
         # two pinned landing buffers for sampled tokens and two pinned staging buffers for packed steps, used in
         # turn: with one step in flight the host may fill step t+1's staging buffer while step t's copy is pending
-        self._sampled_host = [torch.zeros(self.max_seqs, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+        self._sampled_host = [torch.zeros(1 + self.max_seqs, dtype=torch.int64, pin_memory=True) for _ in range(2)]
         self._fetch_events = [torch.cuda.Event() for _ in range(2)]
         self._fetch_turn = 0
         self.capacity = _HEADER_INTS + 4 * self.max_seqs + 3 * self.max_seqs * self.table_width + self.max_tokens
@@ -145,9 +153,11 @@ class StepBuffers:
                         decode_only=decode_only)
 
     def sample(self, logits: torch.Tensor, n_seqs: int) -> None:
-        """Greedy token per row into `sampled`, and into last_tokens[seat] for the next step."""
+        """Greedy token per row into `sampled`, and into last_tokens[seat] for the next step; then the library's
+        status word (bounded waits that ran out in any of its kernels) next to the tokens."""
         _lib.call("ns_argmax_rows", logits.data_ptr(), logits.stride(0), n_seqs, logits.shape[1], self.sampled.data_ptr(),
                   self.seat_of.data_ptr(), self.last_tokens.data_ptr(), _lib.dtype_code(logits.dtype), _lib.stream_ptr())
+        _lib.call("ns_collect_status", self.workspace.buf.data_ptr(), self.fetched.data_ptr(), _lib.stream_ptr())
 
     def step(self, n_tokens: int, n_seqs: int, decode_only: bool) -> torch.Tensor:
         """metadata kernel -> forward -> argmax over the first n_tokens / n_seqs rows; returns the logits."""
@@ -161,15 +171,25 @@ class StepBuffers:
         record an event behind it. Returns a handle for wait_fetch. At most two fetches may be outstanding."""
         turn = self._fetch_turn
         self._fetch_turn ^= 1
-        self._sampled_host[turn][:n].copy_(self.sampled[:n], non_blocking=True)
+        self._sampled_host[turn][:n + 1].copy_(self.fetched[:n + 1], non_blocking=True)
         self._fetch_events[turn].record()
         return turn, n
 
     def wait_fetch(self, handle) -> list[int]:
-        """Block until the fetch behind `handle` has landed: the step's only device->host sync."""
+        """Block until the fetch behind `handle` has landed: the step's only device->host sync. Raises
+        DeviceStatusError if the status word that came back with the tokens has grown since the last fetch: a bounded
+        wait ran out inside one of the step's kernels and the step's results are undefined."""
         turn, n = handle
         self._fetch_events[turn].synchronize()
-        return self._sampled_host[turn][:n].tolist()
+        words = self._sampled_host[turn][:n + 1].tolist()
+        status, self.status_seen = words[0], max(self.status_seen, words[0])
+        if status > self._status_ok:
+            grown, self._status_ok = status - self._status_ok, status
+            raise DeviceStatusError(f"{grown} bounded wait(s) ran out inside this step's kernels (status word {status}): "
+                                    "its tokens are undefined")
+        return words[1:]
+
+    _status_ok = 0                       # status word up to which errors have been reported
 
     def fetch_sampled(self, n: int) -> list[int]:
         return self.wait_fetch(self.queue_fetch(n))

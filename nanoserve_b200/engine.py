@@ -23,7 +23,8 @@ from dataclasses import dataclass
 
 import torch
 
-from nanoserve_b200.cuda_graphs import BUCKETS, DecodeGraphRunner, PiecewiseGraphRunner, StepBuffers, step_buckets
+from nanoserve_b200.cuda_graphs import (BUCKETS, DecodeGraphRunner, DeviceStatusError, PiecewiseGraphRunner, StepBuffers,
+                                        step_buckets)
 from nanoserve_b200.kv_manager import PagedKVManager
 from nanoserve_b200.model import Qwen2Model
 from nanoserve_b200.scheduler import Scheduler, Sequence
@@ -105,6 +106,9 @@ class LLMEngine:
                                                          max_seq_len=max_seq_len)
         self.sequences: dict[int, Sequence] = {}
         self.last_step: StepStats | None = None
+        # logits [sequences, vocab] of the newest step, rows in scheduling order: a view of a static graph output,
+        # valid until that graph is replayed again
+        self.last_logits: torch.Tensor | None = None
         self._next_id = 0
         self._stats = {"steps": 0, "graph_steps": 0, "piecewise_steps": 0, "prefill_chunks": 0, "peak_running": 0,
                        "kv_used_tokens_peak": 0, "kv_reserved_tokens_peak": 0, "kv_util_sum": 0.0,
@@ -193,16 +197,16 @@ class LLMEngine:
 
         runner, pw, buf = self.graph_runner, self.piecewise_runner, self.buffers
         if runner is not None and n_tokens == n_seqs and n_seqs <= runner.max_bucket:
-            runner.run_packed(records, appends, token_ids)           # every sequence feeds one token
+            self.last_logits = runner.run_packed(records, appends, token_ids)   # every sequence feeds one token
             self._stats["graph_steps"] += 1
             path = ("decode", runner.last_key)
         elif pw is not None and pw.fits(n_tokens, n_seqs):
-            pw.run_packed(records, appends, token_ids)
+            self.last_logits = pw.run_packed(records, appends, token_ids)
             self._stats["piecewise_steps"] += 1
             path = ("mixed", pw.last_key)
         else:
             buf.upload(records, appends, token_ids, pad_seqs=n_seqs, pad_tokens=n_tokens)
-            buf.step(n_tokens, n_seqs, decode_only=False)
+            self.last_logits = buf.step(n_tokens, n_seqs, decode_only=False)
             path = ("eager", (n_tokens, n_seqs))
         if self.step_log is not None:                                # device-resident replay (see replay_on_device)
             self.step_log.append((path, buf.host_packed[:buf.packed_ints].clone()))
@@ -211,7 +215,11 @@ class LLMEngine:
         self._resolve_pending(outputs)                               # the previous step's tokens, if still out
         run_ahead = self.lookahead and all(s.ignore_eos for s, n in zip(scheduled, chunks)
                                            if s.num_cached + n >= s.num_tokens)
-        next_tokens = None if run_ahead else buf.wait_fetch(handle)
+        try:
+            next_tokens = None if run_ahead else buf.wait_fetch(handle)
+        except DeviceStatusError:
+            self._abort_all()
+            raise
         self._mark("wait")
 
         for seq, n in zip(scheduled, chunks):
@@ -247,11 +255,24 @@ class LLMEngine:
         if self._pending is not None:
             handle, entries = self._pending
             self._pending = None
-            tokens = self.buffers.wait_fetch(handle)
+            try:
+                tokens = self.buffers.wait_fetch(handle)
+            except DeviceStatusError:
+                self._abort_all()
+                raise
             for seq, at, row, finished in entries:
+                if not finished and seq.seq_id not in self.sequences:
+                    continue                                   # aborted while its token was on the way back
                 seq.output_ids[at] = tokens[row]
                 outputs.append(StepOutput(seq.seq_id, tokens[row], finished))
         return outputs
+
+    def _abort_all(self) -> None:
+        """A step's results are undefined (the device reported a failed wait): drop every request and free its KV
+        blocks, as the reference's engine process does when a step raises (nanoserve/engine_process.py:139-149)."""
+        self._pending = None
+        for seq_id in list(self.sequences):
+            self.abort(seq_id)
 
     def _needs_unknown_token(self, scheduled, chunks) -> bool:
         """True if this step's packed record would carry the value of a token that is still on its way back: a
@@ -312,7 +333,16 @@ class LLMEngine:
             T["_ev1"] = torch.cuda.Event(enable_timing=True)
             T["_ev1"].record()
         if phase == "post":
-            T["gpu"] = T.get("gpu", 0.0) + T["_ev0"].elapsed_time(T["_ev1"]) / 1e3
+            # with a step in flight (lookahead) nothing has synchronised yet: keep the event pair and add its time once
+            # the device has passed it
+            T.setdefault("_evs", []).append((T["_ev0"], T["_ev1"]))
+            waiting = []
+            for e0, e1 in T["_evs"]:
+                if e1.query():
+                    T["gpu"] = T.get("gpu", 0.0) + e0.elapsed_time(e1) / 1e3
+                else:
+                    waiting.append((e0, e1))
+            T["_evs"] = waiting
             T["steps"] = T.get("steps", 0) + 1
 
     def _record_stats(self, running: list[Sequence]) -> None:

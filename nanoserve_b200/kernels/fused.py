@@ -132,10 +132,24 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     return (out, r_out) if want_residual else out
 
 
+_sms = 0
+
+
+def sm_count() -> int:
+    """SMs of the current device (ns_sm_count), cached; 148 (B200) where no device can be asked."""
+    global _sms
+    if _sms <= 0:
+        n = _lib.load().ns_sm_count()
+        if n <= 0:
+            return 148
+        _sms = n
+    return _sms
+
+
 def thin_gemm_ctas(N: int) -> int:
-    """CTAs ns_thin_gemm launches for N weight rows: one per 8 rows, or per 16 when that turns more than one wave of a
-    148-SM part into one."""
-    return N // 8 if (N // 8 <= 148 or N % 16) else N // 16
+    """CTAs ns_thin_gemm launches for N weight rows: one per 8 rows, or per 16 when that turns more than one wave of
+    the device's SMs into one."""
+    return N // 8 if (N // 8 <= sm_count() or N % 16) else N // 16
 
 
 def thin_gemm_supported(M: int, N: int, K: int) -> bool:
@@ -171,12 +185,12 @@ def thin_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
 
 def thin_swiglu_gemm_supported(M: int, inter: int, K: int) -> bool:
     """Shapes ns_thin_swiglu_gemm takes: at most 32 rows, K % 128 == 0, inter % 4 == 0, 72 weight rows plus the padded
-    token rows of K columns within 227 KB of shared memory, and at most one wave of CTAs (148)."""
+    token rows of K columns within 227 KB of shared memory, and at most one wave of CTAs (one per SM)."""
     if not (0 < M <= 32 and K % 128 == 0 and inter % 4 == 0):
         return False
     mp = 16 if M <= 16 else 32
     pitch = 2 * K + 16
-    return (mp + 72) * pitch <= 227 * 1024 and 9 * 4 * mp * 32 <= mp * pitch and -(-(inter // 4) // 9) <= 148
+    return (mp + 72) * pitch <= 227 * 1024 and 9 * 4 * mp * 32 <= mp * pitch and -(-(inter // 4) // 9) <= sm_count()
 
 
 def thin_swiglu_gemm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -251,13 +265,13 @@ def stream_gemm_errors() -> int:
     return int(n.value)
 
 
-def swiglu_gemm_supported(M: int, inter: int, K: int, sms: int = 148) -> bool:
+def swiglu_gemm_supported(M: int, inter: int, K: int, sms: int | None = None) -> bool:
     """Shapes ns_swiglu_gemm takes: at most 64 token rows, K a multiple of 64, a per-SM share of the gate rows of at most
     64, and the activations + two weight stages + the exchange buffer within shared memory."""
     if not (0 < M <= 64 and K % 64 == 0 and inter >= 1):
         return False
     nt = 32 if M <= 32 else 64
-    g = min(sms, inter)
+    g = min(sms or sm_count(), inter)
     while -(-inter // g) > 64:
         g += 1
     region = (inter // g + (1 if inter % g else 0) + 7) // 8 * 8

@@ -331,7 +331,7 @@ class Qwen2Model:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
         from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
                                                   rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
-                                                  swiglu_gemm_supported, thin_gemm, thin_gemm_ctas, thin_gemm_supported, thin_swiglu_gemm,
+                                                  sm_count, swiglu_gemm_supported, thin_gemm, thin_gemm_ctas, thin_gemm_supported, thin_swiglu_gemm,
                                                   thin_swiglu_gemm_supported)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
@@ -368,9 +368,9 @@ class Qwen2Model:
         stream_o = skinny and bool(mask & 16) and stream_gemm_supported(T, hidden, nh * hd)
         umma_gu = skinny and bool(mask & 32) and swiglu_gemm_supported(T, inter, hidden)     # tcgen05 + TMA (off: slower)
         # (only where its CTAs - one per 8 weight rows, or per 16 - are one wave of the SMs)
-        thin_qkv = (skinny and hd in (64, 128) and bool(mask & 64) and thin_gemm_ctas((nh + 2 * nkv) * hd) <= 148 and
+        thin_qkv = (skinny and hd in (64, 128) and bool(mask & 64) and thin_gemm_ctas((nh + 2 * nkv) * hd) <= sm_count() and
                     thin_gemm_supported(T, (nh + 2 * nkv) * hd, hidden))
-        thin_o = (skinny and bool(mask & 128) and thin_gemm_ctas(hidden) <= 148 and (nh * hd) % 128 == 0 and
+        thin_o = (skinny and bool(mask & 128) and thin_gemm_ctas(hidden) <= sm_count() and (nh * hd) % 128 == 0 and
                   thin_gemm_supported(T, hidden, nh * hd))
         thin_gu = skinny and bool(mask & 256) and thin_swiglu_gemm_supported(T, inter, hidden)      # bit 8: gate/up + SiLU*mul
         # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's

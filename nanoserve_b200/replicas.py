@@ -19,6 +19,16 @@ def max_over_ranks(seconds: list[float], device="cpu") -> list[float]:
     return t.tolist()
 
 
+def sum_over_ranks(counts: list[float], device="cpu") -> list[float]:
+    """Element-wise sum over all ranks of a short list of counts (identity without a process group): replicas serve
+    different request streams, so their token counts differ."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return list(counts)
+    t = torch.tensor(counts, dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t.tolist()
+
+
 def aggregate_throughput(units_per_rank: int, seconds: float, device="cpu") -> tuple[float, float]:
     """Whole-job throughput of identical replicas: (world_size * units_per_rank / max-over-ranks seconds, that max)."""
     world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1

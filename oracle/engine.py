@@ -175,6 +175,9 @@ class OracleEngine:
         self.preemptions = self.prefix_hit_tokens = self.prefix_query_tokens = 0
         self.next_id, self.trace, self.feed = 0, [], feed
         self.logits_gap: list[float] = []      # top-2 logit gap of every sampled token (tie analysis)
+        self.gaps: dict[int, list[float]] = {}  # the same gaps per request id, indexed by output token
+        self.keep_logits = False               # True: last_logits = {request id: logits row} of the newest step
+        self.last_logits: dict[int, torch.Tensor] = {}
 
     # -- requests
     def add_request(self, prompt, max_new, ignore_eos=False):
@@ -290,6 +293,8 @@ class OracleEngine:
             top2 = logits.float().topk(2, dim=-1).values
             gaps = (top2[:, 0] - top2[:, 1]).tolist()
             nxt = logits.argmax(-1).tolist()
+            if self.keep_logits:
+                self.last_logits = {r.rid: logits[i] for i, r in enumerate(sched)}
         else:
             nxt, gaps = [self.feed(r, len(r.out)) for r in sched], [1.0] * len(sched)
         for r, n in zip(sched, chunks):
@@ -303,6 +308,7 @@ class OracleEngine:
                 continue
             r.out.append(tok)
             self.logits_gap.append(gap)
+            self.gaps.setdefault(r.rid, []).append(gap)
             done = (tok in self.eos and not r.ignore_eos) or len(r.out) >= r.max_new
             if done:
                 self.running.remove(r)

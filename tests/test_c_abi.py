@@ -61,3 +61,20 @@ def test_decode_gemm_entry_points_validate_before_touching_the_device():
     assert lib.ns_thin_swiglu_gemm(x, w, out, 8, 4866, 896, nul) == UNSUPPORTED
     assert lib.ns_skinny_gemm(x, nul, nul, nul, w, nul, out, 65, 896, 896, 8, ctypes.c_float(1e-6), 0, 0, nul, nul, nul, nul, nul,
                               0, 0, nul) == UNSUPPORTED and "65 token rows" in msg()
+
+
+def test_no_undeclared_entry_point_is_exported():
+    """The shipping library exports exactly the header's surface: profiling hooks exist only in a -DNS_DEBUG_HOOKS build."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", str(_lib.LIB_PATH)], capture_output=True, text=True, check=True).stdout
+    exported = sorted({line.split()[-1] for line in out.splitlines() if " T ns_" in line})
+    assert exported == declared_symbols()
+
+
+def test_tuning_knobs_round_trip_without_a_device():
+    lib = _lib.load()
+    assert lib.ns_get_tuning(_lib.TUNE_PREFILL_OVERLAP) == 1 and lib.ns_get_tuning(_lib.TUNE_DECODE_SPLIT_BLOCKS) == -1
+    assert _lib.set_tuning(_lib.TUNE_DECODE_MIN_BLOCKS, 8) == 0
+    assert lib.ns_get_tuning(_lib.TUNE_DECODE_MIN_BLOCKS) == 8
+    _lib.set_tuning(_lib.TUNE_DECODE_MIN_BLOCKS, 0)
+    assert lib.ns_set_tuning(99, 1) == 1 and "unknown knob" in lib.ns_last_error().decode()

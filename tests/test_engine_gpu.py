@@ -1,10 +1,11 @@
 """End-to-end parity of the GPU engine with the CPU oracle (and, through the golden fixtures, the reference).
 
 Gates: device-built step metadata is bit-exact; scheduler decisions, block tables and slots of every step equal
-the oracle's; fp32 greedy tokens are identical (a divergence is tolerated only where the oracle's own top-2 logit
-gap is below 1e-3, i.e. an fp32 summation-order tie); bf16 follows the tie rule of the reference's tests (gap <=
-0.25, reference tests/test_llm_engine.py:17); CUDA graphs change nothing; padding rows touch only the garbage
-block; no KV block leaks."""
+the oracle's; greedy tokens equal the reference's, where a request may part from it only at a token whose reference
+top-2 logit gap AT THAT REQUEST AND TOKEN is below the numerical error of the path (tests/parity.py): 1e-3 for fp32
+(summation order), twice the bf16 path's logit tolerance for bf16, and that tolerance is itself checked against the
+fp32 oracle's logits step by step; CUDA graphs change nothing; padding rows touch only the garbage block; no KV block
+leaks."""
 import json
 import random
 from pathlib import Path
@@ -15,10 +16,17 @@ import torch
 from oracle import ops as O
 from oracle.engine import OracleEngine, OracleModel, run_requests
 from tests.golden import make_golden as G
+from tests.parity import check_tokens
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).parent / "golden"
-TIE_GAP_BF16 = 0.25
+TIE_GAP_F32 = 1e-3
+# Largest |logit(bf16 GPU path) - logit(fp32 oracle, fp32 weights)| allowed on any row of any compared step. With
+# this bound a greedy argmax can differ from the reference's only where the reference's top-2 gap is <= 2x the bound
+# (gpu[g] >= gpu[r] and |gpu - ref| <= E give ref[r] - ref[g] <= 2E). Measured on this model: see the test output.
+LOGIT_TOL_BF16 = 0.06
+LOGIT_TOL_F32 = 2e-4
+TINY_LOGIT_TOL_BF16 = 0.25       # tiny model: logits of magnitude ~10 (embedding std 0.5), bf16 ulp 0.06 there
 
 
 def gpu_model(cfg: dict, sd: dict, dtype):
@@ -29,10 +37,6 @@ def gpu_model(cfg: dict, sd: dict, dtype):
 def make_engine(model, **kw):
     from nanoserve_b200.engine import LLMEngine
     return LLMEngine(model, eos_token_ids=[], **kw)
-
-
-def first_divergence(a, b):
-    return next((k for k in range(min(len(a), len(b))) if a[k] != b[k]), None)
 
 
 def test_device_metadata_matches_cpu_restatement():
@@ -101,10 +105,9 @@ def test_tiny_fp32_engine_equals_oracle_and_reference(graphs):
         assert g["ids"] == w["ids"] and g["chunks"] == w["chunks"] and g["tables"] == w["tables"] and g["slots"] == w["slots"]
     # tokens: identical (the golden file holds the reference's own tokens for the same requests)
     gold = json.loads((GOLD / "tiny_engine.json").read_text())["tokens"]
-    for i, (a, b) in enumerate(zip(got, want)):
-        j = first_divergence(a, b)
-        assert j is None or min(oracle.logits_gap) <= 1e-3, f"request {i} diverges at token {j}"
-    assert got == gold or min(oracle.logits_gap) <= 1e-3
+    assert want == gold                                    # the oracle is pinned to the reference's own run
+    same, accepted = check_tokens(got, gold, lambda i, j: oracle.gaps[i][j], TIE_GAP_F32, what="tiny fp32")
+    assert same == len(gold) - len(accepted)
     st = eng.stats
     assert st["steps"] == len(trace) and (st["graph_steps"] + st["piecewise_steps"] == st["steps"]) == graphs
     assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - (1 if graphs else 0)
@@ -118,9 +121,11 @@ def test_tiny_bf16_graph_engine_follows_the_tie_rule():
     want = run_requests(oracle, G.tiny_requests(), concurrency=4)
     eng = make_engine(gpu_model(cfg, sd16, torch.bfloat16), **G.TINY_ENGINE_KW)
     got = run_requests(eng, G.tiny_requests(), concurrency=4)
-    exact = sum(got[i] == want[i] for i in range(len(want)))
-    print(f"bf16 tiny: {exact}/{len(want)} requests identical to the fp32 oracle on the same bf16 weights")
-    assert exact >= 1
+    n = len(want)
+    same, accepted = check_tokens([got[i] for i in range(n)], [want[i] for i in range(n)],
+                                  lambda i, j: oracle.gaps[i][j], 2 * TINY_LOGIT_TOL_BF16, what="tiny bf16")
+    print(f"bf16 tiny: {same}/{n} requests identical to the fp32 oracle on the same bf16 weights; "
+          f"accepted divergences (request, token, oracle gap): {accepted}")
     assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - 1
 
 
@@ -138,8 +143,10 @@ def test_prefix_caching_on_equals_off_fp32():
     oracle = OracleEngine(OracleModel(cfg, sd), prefix_caching=True, reserve_garbage_block=True, **kw)
     c = run_requests(oracle, reqs, concurrency=3)
     assert on.stats["prefix_hit_tokens"] == oracle.prefix_hit_tokens
-    for i in range(len(reqs)):
-        assert a[i] == b[i] == c[i] or min(oracle.logits_gap) <= 1e-3
+    n = len(reqs)
+    assert [a[i] for i in range(n)] == [b[i] for i in range(n)]
+    check_tokens([a[i] for i in range(n)], [c[i] for i in range(n)], lambda i, j: oracle.gaps[i][j], TIE_GAP_F32,
+                 what="prefix caching fp32")
     assert on.kv.num_free_blocks == on.kv.pool.num_blocks - 1
 
 
@@ -156,8 +163,10 @@ def test_preemption_keeps_tokens_fp32():
                           kv_cache_tokens=256, reserve_garbage_block=True)
     c = run_requests(oracle, reqs)
     assert oracle.preemptions == tight.stats["num_preemptions"]
-    for i in range(len(reqs)):
-        assert a[i] == b[i] == c[i] or min(oracle.logits_gap) <= 1e-3
+    n = len(reqs)
+    assert [a[i] for i in range(n)] == [b[i] for i in range(n)]
+    check_tokens([a[i] for i in range(n)], [c[i] for i in range(n)], lambda i, j: oracle.gaps[i][j], TIE_GAP_F32,
+                 what="preemption fp32")
     assert tight.kv.num_free_blocks == tight.kv.pool.num_blocks - 1
 
 
@@ -187,45 +196,134 @@ def test_padding_touches_only_the_garbage_block():
     assert eng.stats["graph_steps"] > 0 and eng.stats["piecewise_steps"] > 0
 
 
+_CONFIG0_ORACLE: dict = {}
+
+
+def config0_oracle(n_steps: int = 32):
+    """The fp32 CPU oracle on benchmark configuration 0 for the first n_steps engine steps (= the first n_steps
+    generated tokens of every request: all 8 prompts fit the first step's budget): per-step logits [8, vocab] and
+    tokens. Computed once per test process; its tokens must equal the reference's own (golden file)."""
+    if not _CONFIG0_ORACLE:
+        from nanoserve_b200.synthetic import random_state_dict
+        gold = json.loads((GOLD / "config0_tokens.json").read_text())
+        sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
+        eng = OracleEngine(OracleModel(cfg, sd), **G.CONFIG0_ENGINE_KW)
+        eng.keep_logits = True
+        for p, n in G.config0_requests():
+            eng.add_request(p, n, ignore_eos=True)
+        logits, toks = [], [[] for _ in range(8)]
+        for _ in range(n_steps):
+            outs = eng.step()
+            assert len(outs) == 8
+            logits.append(torch.stack([eng.last_logits[i] for i in range(8)]).float())
+            for rid, tok, _ in outs:
+                toks[rid].append(tok)
+        assert toks == [t[:n_steps] for t in gold["tokens"]], "the oracle left the reference's trajectory"
+        _CONFIG0_ORACLE.update(logits=logits, gold=gold, sd=sd, cfg=cfg)
+    return _CONFIG0_ORACLE
+
+
+def run_config0_beside_the_oracle(dtype, first: int = 32):
+    """Runs configuration 0 on the GPU engine and compares, step by step over the first `first` generated tokens, the
+    logits row of every request that still shares the reference's context with the fp32 oracle's row (max-abs over
+    the vocabulary). Returns (tokens per request, worst logit error, KV blocks free / total)."""
+    ora = config0_oracle(first)
+    eng = make_engine(gpu_model(ora["cfg"], ora["sd"], dtype), **G.CONFIG0_ENGINE_KW)
+    order = []
+    orig = eng.scheduler.schedule
+
+    def spy(now):
+        plan = orig(now)
+        order[:] = [s.seq_id for s in plan.scheduled]
+        return plan
+
+    eng.scheduler.schedule = spy
+    for p, n in G.config0_requests():
+        eng.add_request(p, n, ignore_eos=True)
+    gold = ora["gold"]["tokens"]
+    toks = [[] for _ in range(8)]
+    parted: set[int] = set()
+    worst = 0.0
+    step = 0
+    while eng.has_unfinished():
+        outs = eng.step()
+        if step < first:
+            assert sorted(order) == list(range(8))
+            got = eng.last_logits.float()
+            ref = ora["logits"][step].to(got.device)
+            for row, rid in enumerate(order):
+                if rid not in parted:
+                    worst = max(worst, (got[row] - ref[rid]).abs().max().item())
+        for o in outs:
+            toks[o.seq_id].append(o.token)
+            if len(toks[o.seq_id]) <= first and o.token != gold[o.seq_id][len(toks[o.seq_id]) - 1]:
+                parted.add(o.seq_id)
+        step += 1
+    return toks, worst, (eng.kv.num_free_blocks, eng.kv.pool.num_blocks)
+
+
 def test_config0_fp32_greedy_tokens_match_the_reference():
-    """benchmark configuration 0 on the GPU in fp32: the first 32 generated tokens of all 8 requests equal the reference's
-    CPU run (golden file); a divergence is accepted only at a step whose reference top-2 gap is below 1e-3."""
-    from nanoserve_b200.synthetic import random_state_dict
-    gold = json.loads((GOLD / "config0_tokens.json").read_text())
-    sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
-    eng = make_engine(gpu_model(cfg, sd, torch.float32), **G.CONFIG0_ENGINE_KW)
-    outs = run_requests(eng, G.config0_requests())
-    min_gap = min(g for step in gold["step_gaps"] for g in step)
-    same32 = 0
-    for i, want in enumerate(gold["tokens"]):
-        j = first_divergence(outs[i][:32], want[:32])
-        same32 += j is None
-        assert j is None or min_gap <= 1e-3, f"request {i} diverges at token {j} (min reference gap {min_gap:.2e})"
-    print(f"config 0 fp32: {same32}/8 requests identical over the first 32 tokens; min reference gap {min_gap:.2e}")
-    assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - 1
+    """Benchmark configuration 0 on the GPU in fp32: the first 32 generated tokens of all 8 requests equal the
+    reference's CPU run (golden file), a request being allowed to part from it only at a token whose reference top-2
+    gap - that request, that token - is below 1e-3; the logits of every compared step stay within LOGIT_TOL_F32 of the
+    fp32 oracle. (No gap of the first 32 steps of the golden run is below 1e-3, so today all 8 must be identical.)"""
+    toks, worst, (free, total) = run_config0_beside_the_oracle(torch.float32)
+    gold = _CONFIG0_ORACLE["gold"]
+    same, accepted = check_tokens(toks, gold["tokens"], lambda i, j: gold["step_gaps"][j][i], TIE_GAP_F32, first=32,
+                                  what="config 0 fp32")
+    print(f"config 0 fp32: {same}/8 requests identical over the first 32 tokens; accepted divergences {accepted}; "
+          f"worst |logit - oracle| {worst:.2e}")
+    assert same == 8 - len(accepted)
+    assert worst <= LOGIT_TOL_F32, f"fp32 logits differ from the oracle by {worst:.2e}"
+    assert free == total - 1
 
 
 @pytest.mark.parametrize("gemm_mask", [None, "0", "3", "27", "195", "451"])
 def test_config0_bf16_greedy_tokens_tie_rule(gemm_mask, monkeypatch):
-    """Benchmark configuration 0 (0.5B shape, 8 requests x 64 greedy tokens) on the bf16 graph path: a divergence from the reference's tokens within the first 32 is
-    accepted only at a step whose reference top-2 gap is within the bf16 tie rule. Run with the engine's default choice
-    of decode-GEMM kernels (None) and with each other choice forced for every decode-sized step: 0 = library GEMMs + the
-    separate RoPE / SiLU kernels, 3 = split-K cluster kernel for QKV and down_proj, 27 = + streaming kernel for gate/up
-    and o_proj, 195 = 8-row-tile kernel for QKV and o_proj, 451 = + 8-row-tile gate/up with SiLU*mul."""
+    """Benchmark configuration 0 (0.5B shape, 8 requests x 64 greedy tokens) on the bf16 graph path. Two checks over
+    the first 32 generated tokens: (1) every logits row computed on the reference's context is within LOGIT_TOL_BF16
+    (max-abs over the 151,936 logits) of the fp32 oracle, whose tokens equal the reference's; (2) a request parts from
+    the reference's tokens only where the reference's top-2 gap at that request and token is <= 2 * LOGIT_TOL_BF16,
+    the largest gap an error of that size can flip. Run with the engine's default choice of decode-GEMM kernels (None)
+    and with each other choice forced for every decode-sized step: 0 = library GEMMs + the separate RoPE / SiLU
+    kernels, 3 = split-K cluster kernel for QKV and down_proj, 27 = + streaming kernel for gate/up and o_proj, 195 =
+    8-row-tile kernel for QKV and o_proj, 451 = + 8-row-tile gate/up with SiLU*mul."""
     if gemm_mask is not None:
         monkeypatch.setenv("NS_SKINNY_MASK", gemm_mask)
         monkeypatch.setenv("NS_SKINNY_MASK_SMALL", gemm_mask)
-    from nanoserve_b200.synthetic import random_state_dict
-    gold = json.loads((GOLD / "config0_tokens.json").read_text())
-    sd, cfg = random_state_dict("qwen2.5-0.5b", dtype=torch.float32)
-    eng = make_engine(gpu_model(cfg, sd, torch.bfloat16), **G.CONFIG0_ENGINE_KW)
-    outs = run_requests(eng, G.config0_requests())
-    # step k of the reference run = prefill (k == 0) then one decode per step, all 8 requests in order
-    report = []
-    for i, want in enumerate(gold["tokens"]):
-        j = first_divergence(outs[i][:32], want[:32])
-        if j is not None:
-            gap = gold["step_gaps"][j][i]
-            report.append((i, j, gap))
-            assert gap <= TIE_GAP_BF16, f"request {i} diverges at token {j} where the reference gap is {gap:.3f}"
-    print(f"config 0 bf16, GEMM mask {gemm_mask}: {8 - len(report)}/8 identical over 32 tokens; divergences (req, token, ref gap): {report}")
+    toks, worst, _ = run_config0_beside_the_oracle(torch.bfloat16)
+    gold = _CONFIG0_ORACLE["gold"]
+    same, accepted = check_tokens(toks, gold["tokens"], lambda i, j: gold["step_gaps"][j][i], 2 * LOGIT_TOL_BF16,
+                                  first=32, what=f"config 0 bf16, GEMM mask {gemm_mask}")
+    print(f"config 0 bf16, GEMM mask {gemm_mask}: {same}/8 identical over 32 tokens; worst |logit - oracle| {worst:.4f}; "
+          f"accepted divergences (request, token, reference gap): {accepted}")
+    assert worst <= LOGIT_TOL_BF16, f"bf16 logits differ from the fp32 oracle by {worst:.4f}"
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_device_status_word_reaches_the_host(lookahead):
+    """Every step's read-back carries the library's status word (bounded waits that ran out in its kernels). The
+    failure is injected from the HOST: the attention workspace's error count is raised by one with a device copy
+    between two steps - no kernel is made to time out. The next step whose tokens are read raises, every request is
+    aborted and its KV blocks are freed, and the engine serves new requests afterwards with the tokens of a fresh one."""
+    from nanoserve_b200.cuda_graphs import DeviceStatusError
+    cfg, sd = G.TINY_CFG, G.tiny_state_dict(G.TINY_CFG)
+    model = gpu_model(cfg, sd, torch.float32)
+    eng = make_engine(model, lookahead=lookahead, **G.TINY_ENGINE_KW)
+    reqs = G.tiny_requests()
+    for p, n in reqs[:3]:
+        eng.add_request(p, n, ignore_eos=True)
+    for _ in range(3):
+        eng.step()
+    assert eng.buffers.status_seen == 0
+    errors_word = eng.buffers.workspace.buf[32:36].view(torch.int32)      # PlanHeader::errors
+    errors_word += 1
+    with pytest.raises(DeviceStatusError):
+        for _ in range(3):
+            eng.step()
+    assert not eng.has_unfinished() and not eng.sequences
+    assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - 1
+    assert eng.buffers.status_seen == 1
+    after = run_requests(eng, reqs[3:6], concurrency=3)
+    fresh = run_requests(make_engine(model, **G.TINY_ENGINE_KW), reqs[3:6], concurrency=3)
+    assert after == fresh
