@@ -266,17 +266,41 @@ def decode_attention_roofline(device) -> dict:
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b) * 1e-3 / (reps * len(pools)))
     per_launch = sum(times) / len(times)
-    singles = []
-    for i in range(24):
-        k, v = pools[i % len(pools)]
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        one(k, v)
-        b.record()
+    # (b) serialised: a one-element fill kernel between launches is an ordinary (non-programmatic) boundary, so no launch
+    # can run any part of itself under its predecessor; the same graph with only the fills is subtracted
+    flag = torch.zeros(1, device=device)
+
+    def timed_graph(fn) -> float:
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        gg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gg):
+            fn()
+        gg.replay()
         torch.cuda.synchronize()
-        if i >= 4:
-            singles.append(a.elapsed_time(b) * 1e-3)
-    serial = sorted(singles)[len(singles) // 2]
+        ts = []
+        for _ in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            gg.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        return sorted(ts)[len(ts) // 2]
+
+    def with_fills():
+        for _ in range(reps):
+            for k, v in pools:
+                flag.zero_()
+                one(k, v)
+
+    def fills_only():
+        for _ in range(reps * len(pools)):
+            flag.zero_()
+
+    serial = (timed_graph(with_fills) - timed_graph(fills_only)) / (reps * len(pools))
     nbytes = w.decode_bytes()
     peak, which = measured_peak("hbm_gbs", HBM_FALLBACK_GBS)
     achieved = nbytes / per_launch / 1e9

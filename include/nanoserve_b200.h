@@ -291,6 +291,22 @@ int ns_build_step_metadata(const int32_t* packed, int32_t packed_ints, int32_t* 
 int ns_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t vocab, int64_t* out,
                    const int32_t* seat_of, int64_t* last_tokens, int dtype, void* stream);
 
+/* Sampling with temperature / top-k / top-p for the rows that ask for it, after ns_argmax_rows has filled `out`:
+ * params is rows x 8 32-bit words {float temperature, float top_p, int32 top_k, int32 enabled, uint32 seed_lo,
+ * uint32 seed_hi, 0, 0}. A row with enabled == 0 keeps its greedy token. Otherwise x = float(logit) / temperature;
+ * top_k > 0 keeps x >= the k-th largest x; top_p < 1 keeps, in descending order of x, the tokens whose softmax mass
+ * ranked above them is < top_p (equal values together; the best token always survives); the token is
+ * argmax_j(x_j + g_j) over the survivors with Gumbel noise g_j = -log(-log(u_j)), u_j in [1e-20, 1 - 1e-7] drawn from a
+ * counter-based generator keyed by (seed, j) - so a row's token depends only on its logits, its parameters and its
+ * seed, never on its neighbours or its row index. The caller passes seed = mix_seed(request seed, tokens generated so
+ * far). out / seat_of / last_tokens as in ns_argmax_rows. threshold_out (float [rows]) and kept_out (int32 [rows]) may
+ * be NULL; when given they receive the smallest surviving x and the number of survivors of every enabled row.
+ * Replaces: nanoserve/sampling.py:54-90 sample (called at nanoserve/engine.py:233-237). Individual draws differ from
+ * the reference's (another random stream); kept set and distribution are the same. */
+int ns_sample_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t vocab, const void* params,
+                   int64_t* out, const int32_t* seat_of, int64_t* last_tokens, float* threshold_out,
+                   int32_t* kept_out, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

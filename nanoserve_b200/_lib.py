@@ -52,6 +52,7 @@ SIGNATURES: dict[str, tuple] = {
                                             _I64, _I64, _I64, _I64, _I64, _F, c_int, _P]),
     "ns_build_step_metadata": (c_int, [_P, _I32, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _P]),
     "ns_argmax_rows": (c_int, [_P, _I64, _I32, _I32, _P, _P, _P, c_int, _P]),
+    "ns_sample_rows": (c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _P, c_int, _P]),
 }
 
 _lib = None

@@ -93,6 +93,13 @@ class StepBuffers:
         self.fetched = torch.zeros(1 + self.max_seqs, **i64)
         self.sampled = self.fetched[1:]
         self.status_seen = 0              # status word of the newest step that was read back
+        # per-row sampling parameters read by the sampling kernel inside the graphs (8 words per row, all zero = every
+        # row greedy); uploaded only on steps that sample and on the first all-greedy step after one
+        self.sample_params = torch.zeros(8 * self.max_seqs, **i32)
+        self._sample_staging = [torch.zeros(8 * self.max_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._sample_np = [(t.numpy(), t.numpy().view(np.float32)) for t in self._sample_staging]
+        self._sample_turn = 0
+        self._sample_live = False         # the device copy holds an enabled row
         # two pinned landing buffers for sampled tokens and two pinned staging buffers for packed steps, used in
         # turn: with one step in flight the host may fill step t+1's staging buffer while step t's copy is pending
         self._sampled_host = [torch.zeros(1 + self.max_seqs, dtype=torch.int64, pin_memory=True) for _ in range(2)]
@@ -133,6 +140,22 @@ class StepBuffers:
         self.packed_ints = n
         self.dev_packed[:n].copy_(self.host_packed[:n], non_blocking=True)
 
+    def set_sampling(self, rows: list[tuple]) -> None:
+        """rows: (row, temperature, top_p, top_k, 63-bit draw seed) for every sequence row of the coming step that
+        samples with temperature > 0; every other row stays greedy. Stream-ordered before the step."""
+        if not rows and not self._sample_live:
+            return
+        self._sample_turn ^= 1
+        ints, floats = self._sample_np[self._sample_turn]
+        ints[:] = 0
+        for row, temperature, top_p, top_k, seed in rows:
+            o = 8 * row
+            floats[o], floats[o + 1] = temperature, top_p
+            ints[o + 2], ints[o + 3] = top_k, 1
+            ints[o + 4:o + 6] = np.array([seed & 0xFFFFFFFF, seed >> 32], dtype=np.uint32).view(np.int32)
+        self.sample_params.copy_(self._sample_staging[self._sample_turn], non_blocking=True)
+        self._sample_live = bool(rows)
+
     @staticmethod
     def _count_tokens(records: list[int]) -> int:
         return sum(records[2::4])
@@ -153,10 +176,13 @@ class StepBuffers:
                         decode_only=decode_only)
 
     def sample(self, logits: torch.Tensor, n_seqs: int) -> None:
-        """Greedy token per row into `sampled`, and into last_tokens[seat] for the next step; then the library's
-        status word (bounded waits that ran out in any of its kernels) next to the tokens."""
+        """Greedy token per row into `sampled`, and into last_tokens[seat] for the next step; rows whose request samples
+        (set_sampling) are then redrawn with temperature / top-k / top-p; then the library's status word (bounded waits that ran out in any of its kernels) next to the tokens."""
         _lib.call("ns_argmax_rows", logits.data_ptr(), logits.stride(0), n_seqs, logits.shape[1], self.sampled.data_ptr(),
                   self.seat_of.data_ptr(), self.last_tokens.data_ptr(), _lib.dtype_code(logits.dtype), _lib.stream_ptr())
+        _lib.call("ns_sample_rows", logits.data_ptr(), logits.stride(0), n_seqs, logits.shape[1], self.sample_params.data_ptr(),
+                  self.sampled.data_ptr(), self.seat_of.data_ptr(), self.last_tokens.data_ptr(), None, None,
+                  _lib.dtype_code(logits.dtype), _lib.stream_ptr())
         _lib.call("ns_collect_status", self.workspace.buf.data_ptr(), self.fetched.data_ptr(), _lib.stream_ptr())
 
     def step(self, n_tokens: int, n_seqs: int, decode_only: bool) -> torch.Tensor:

@@ -1,4 +1,5 @@
-"""Inference engine: scheduler + one batched forward per step + greedy sampling.
+"""Inference engine: scheduler + one batched forward per step + sampling (greedy argmax, or temperature / top-k / top-p per
+request) on the device.
 
 `LLMEngine` keeps the reference's constructor keywords, methods and counters (nanoserve/engine.py:46-298):
 `add_request`, `abort`, `has_unfinished`, `step() -> list[StepOutput]`, `capture_graphs`, `stats`, `last_step`,
@@ -27,6 +28,7 @@ from nanoserve_b200.cuda_graphs import (BUCKETS, DecodeGraphRunner, DeviceStatus
                                         step_buckets)
 from nanoserve_b200.kv_manager import PagedKVManager
 from nanoserve_b200.model import Qwen2Model
+from nanoserve_b200.sampling import mix_seed
 from nanoserve_b200.scheduler import Scheduler, Sequence
 
 
@@ -153,8 +155,6 @@ class LLMEngine:
         if len(prompt_ids) + max_new_tokens > self.max_seq_len:
             raise ValueError(f"prompt ({len(prompt_ids)}) + max_new_tokens ({max_new_tokens}) "
                              f"exceeds max_seq_len ({self.max_seq_len})")
-        if sampling is not None and not getattr(sampling, "greedy", True):
-            raise NotImplementedError("only greedy decoding is built on this path")
         seed = sampling.seed if (sampling is not None and getattr(sampling, "seed", None) is not None) \
             else random.getrandbits(62)
         seq = Sequence(seq_id=self._next_id, prompt_ids=list(prompt_ids), max_new_tokens=max_new_tokens,
@@ -196,6 +196,11 @@ class LLMEngine:
         self._mark("prepare", gpu_start=True)
 
         runner, pw, buf = self.graph_runner, self.piecewise_runner, self.buffers
+        # draw n of request r is keyed by mix_seed(seed_r, n), n = tokens generated so far: the same text whatever the
+        # batch, and across a preemption + recompute (nanoserve/engine.py:233-237)
+        buf.set_sampling([(row, s.sampling.temperature, s.sampling.top_p, s.sampling.top_k, mix_seed(s.seed, len(s.output_ids)))
+                          for row, (s, n) in enumerate(zip(scheduled, chunks))
+                          if s.sampling is not None and not s.sampling.greedy and s.num_cached + n >= s.num_tokens])
         if runner is not None and n_tokens == n_seqs and n_seqs <= runner.max_bucket:
             self.last_logits = runner.run_packed(records, appends, token_ids)   # every sequence feeds one token
             self._stats["graph_steps"] += 1

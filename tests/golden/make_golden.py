@@ -287,10 +287,26 @@ SAMPLING_PARAMS = [dict(), dict(temperature=0.0, top_k=5), dict(temperature=0.7)
                    dict(top_p=0.0), dict(top_p=1.0001), dict(top_p=1.0), dict(top_k=-1), dict(top_k=0, temperature=2.0)]
 
 
+SAMPLING_SUPPORT_CASES = [
+    dict(seed=0, vocab=64, temperature=1.0, top_k=0, top_p=1.0, draws=4000),
+    dict(seed=1, vocab=64, temperature=0.7, top_k=8, top_p=1.0, draws=4000),
+    dict(seed=2, vocab=64, temperature=1.3, top_k=0, top_p=0.6, draws=4000),
+    dict(seed=3, vocab=64, temperature=0.9, top_k=12, top_p=0.8, draws=4000),
+    dict(seed=4, vocab=64, temperature=2.0, top_k=3, top_p=0.3, draws=2000),
+    dict(seed=5, vocab=200, temperature=0.5, top_k=0, top_p=0.95, draws=4000),
+]
+
+
+def sampling_logits(seed: int, vocab: int) -> torch.Tensor:
+    """A seeded fp32 logits row (standard deviation 2: a few tokens dominate, as in a language model's output)."""
+    return torch.randn(vocab, generator=torch.Generator().manual_seed(1000 + seed)) * 2.0
+
+
 def sampling_main(ref_root: str) -> None:
-    """Records the reference's mix_seed values and which SamplingParams it accepts (and whether they are greedy)."""
+    """Records the reference's mix_seed values, which SamplingParams it accepts (and whether they are greedy), and how
+    often its sample() picked each token of seeded logits rows over thousands of seeds (its support and frequencies)."""
     sys.path.insert(0, ref_root)
-    from nanoserve.sampling import SamplingParams, mix_seed
+    from nanoserve.sampling import SamplingParams, mix_seed, sample
     seeds = [[s, n, mix_seed(s, n)] for s, n in SAMPLING_SEEDS]
     params = []
     for kw in SAMPLING_PARAMS:
@@ -298,8 +314,20 @@ def sampling_main(ref_root: str) -> None:
             params.append(dict(ok=True, greedy=bool(SamplingParams(**kw).greedy)))
         except ValueError:
             params.append(dict(ok=False, greedy=None))
-    (HERE / "sampling.json").write_text(json.dumps(dict(mix_seed=seeds, params=params)))
-    print(f"sampling: {len(seeds)} seeds, {len(params)} parameter sets")
+    # which tokens the reference's sample() can produce: its support over many seeds, per (logits row, parameters)
+    support = []
+    for case in SAMPLING_SUPPORT_CASES:
+        logits = sampling_logits(case["seed"], case["vocab"])
+        p = SamplingParams(temperature=case["temperature"], top_k=case["top_k"], top_p=case["top_p"])
+        counts = [0] * case["vocab"]
+        B = 8
+        for s in range(0, case["draws"], B):
+            toks = sample(logits[None].repeat(B, 1), [p] * B, list(range(s, s + B)), [3] * B)
+            for t in toks:
+                counts[t] += 1
+        support.append(dict(case=case, counts=counts))
+    (HERE / "sampling.json").write_text(json.dumps(dict(mix_seed=seeds, params=params, support=support)))
+    print(f"sampling: {len(seeds)} seeds, {len(params)} parameter sets, {len(support)} support cases")
 
 
 if __name__ == "__main__":

@@ -144,3 +144,22 @@ def test_token_gate_fails_on_a_wrong_token():
     check_tokens(toks, gold["tokens"], lambda i, j: gold["step_gaps"][j][i], gap, first=32)
     with pytest.raises(AssertionError):
         check_tokens(toks, gold["tokens"], lambda i, j: gold["step_gaps"][j][i], gap / 2, first=32)
+
+
+def test_oracle_sampling_distribution_matches_the_reference_sampler():
+    """The reference's sample() was run over thousands of seeds on seeded logits rows (tests/golden/sampling.json):
+    every token it ever produced is a survivor of the oracle's top-k / top-p masking, every survivor the oracle gives a
+    non-negligible probability was produced, and the observed frequencies sit within 5 standard deviations of the
+    oracle's probabilities."""
+    gold = json.loads((GOLD / "sampling.json").read_text())
+    for entry in gold["support"]:
+        c = entry["case"]
+        logits = G.sampling_logits(c["seed"], c["vocab"])
+        probs = O.sampling_probabilities(logits, c["temperature"], c["top_k"], c["top_p"])
+        counts = torch.tensor(entry["counts"], dtype=torch.float64)
+        n = counts.sum().item()
+        assert n == c["draws"]
+        assert ((counts > 0) <= (probs > 0)).all(), f"the reference produced a token the oracle drops: {c}"
+        assert (counts[probs * n >= 30] > 0).all(), f"a likely survivor was never produced: {c}"
+        sigma = (probs * (1 - probs) / n).sqrt()
+        assert ((counts / n - probs).abs() <= 5 * sigma + 1e-9).all(), c
