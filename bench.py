@@ -602,6 +602,43 @@ def extra_workload(args) -> None:
         os._exit(0)          # graphs hold captured NCCL work: leave without tearing the group down
 
 
+def run_router(args) -> None:
+    """ONE request stream served by N engine processes (one per GPU) behind the least-outstanding router: the serving form
+    of request-level replicas. This process holds no GPU: it submits host token lists and receives tokens through the
+    engine processes' pipes, so the figure is end to end (wall clock, `concurrency` x N requests in flight, K passes
+    after W warm-up passes). Prints one JSON object; the torchrun form (--gpus N) is the no-router upper bound."""
+    from nanoserve_b200.engine_process import EngineSpec
+    from nanoserve_b200.replicas import ReplicaRouter, serve_closed_loop
+    n = args.router
+    specs = [EngineSpec(model="qwen2.5-0.5b", device=i, max_seq_len=2048, max_num_seqs=CONCURRENCY,
+                        max_num_batched_tokens=2048, lookahead=not args.no_lookahead) for i in range(n)]
+    t0 = time.perf_counter()
+    router = ReplicaRouter(specs)
+    start_s = time.perf_counter() - t0
+    try:
+        streams = [workload(r) for r in range(n)]
+        reqs = [streams[r][i] for i in range(N_REQUESTS) for r in range(n)]        # one stream, n x 64 requests
+        for _ in range(args.warmup):
+            serve_closed_loop(router, reqs, CONCURRENCY * n)
+        before = list(router.dispatched)
+        t0 = time.perf_counter()
+        total = 0
+        for _ in range(args.steps):
+            tokens, failed = serve_closed_loop(router, reqs, CONCURRENCY * n)
+            assert not failed, failed
+            total += sum(len(v) for v in tokens.values())
+        secs = time.perf_counter() - t0
+        per_replica = [a - b for a, b in zip(router.dispatched, before)]
+        stats = router.stats()
+        print(json.dumps({"router": {"replicas": n, "tok_per_s": total / secs, "passes": args.steps, "seconds": secs,
+                                     "requests_per_pass": len(reqs), "in_flight": CONCURRENCY * n,
+                                     "dispatched_per_replica": per_replica, "start_s": start_s,
+                                     "engine_steps": [st["engine"]["steps"] for st in stats], "host_cpus": os.cpu_count(),
+                                     "policy": "least outstanding, ties round-robin"}}))
+    finally:
+        router.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -616,10 +653,14 @@ def main() -> None:
     ap.add_argument("--workload", default="serve", choices=["serve", "sweep", "prefix", "tp"],
                     help="serve = the benchmark contract's line (default); the others print one JSON object of extras")
     ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--router", type=int, default=0, metavar="N",
+                    help="serve one request stream through N engine processes (GPUs 0..N-1) behind the replica router")
     ap.add_argument("--no-lookahead", action="store_true",
                     help="serve workload: wait for every step's tokens before scheduling the next (the reference's loop)")
     args = ap.parse_args()
-    if args.workload != "serve":
+    if args.router:
+        run_router(args)
+    elif args.workload != "serve":
         extra_workload(args)
     elif args.roofline_only:
         torch.cuda.set_device(0)

@@ -14,7 +14,7 @@
 // the host generator's stream, so individual samples are not bit-equal to the reference's; the distribution is the same.
 //
 // No sort: the two thresholds are found by radix selection over an order-preserving 32-bit key of x, 8 bits per pass -
-// by element COUNT for top-k and by probability MASS for top-p. Masses are 32.32 fixed-point integers, so the
+// by element COUNT for top-k and by probability MASS for top-p. Masses are integers (exp(x - max) in units of 2^-40), so the
 // histogram sums do not depend on the order of the atomic adds and a row's kept set is reproducible bit for bit.
 #include "common.cuh"
 
@@ -56,7 +56,7 @@ __device__ __forceinline__ void hist_mass(unsigned long long* hist, bool active,
     const unsigned mask = __ballot_sync(0xffffffffu, active);
     if (active) {
         const unsigned peers = __match_any_sync(mask, digit);
-        // fx <= 2^32: two limbs whose 32-lane sums fit 32 bits
+        // fx <= 2^40: two 20-bit limbs whose 32-lane sums fit 32 bits
         const uint32_t lo = __reduce_add_sync(peers, (uint32_t)(fx & 0xFFFFFu));
         const uint32_t hi = __reduce_add_sync(peers, (uint32_t)(fx >> 20));
         if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], (unsigned long long)lo + ((unsigned long long)hi << 20));
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const T* __
     // ---- top-p: key of the lowest token whose mass ranked above it is < p, by radix selection on mass -------------------
     uint32_t key_p = 0;
     if (sp.top_p < 1.0f) {
-        auto fixed_mass = [&](float x) { return (uint64_t)__float2ull_rn(expf(x - m) * 4294967296.0f); };
+        auto fixed_mass = [&](float x) { return (uint64_t)__float2ull_rn(expf(x - m) * 1099511627776.0f); };   // 2^40
         unsigned long long z = 0;
         for (int i = tid; i < vocab; i += kSampleThreads) {
             const float x = x_at(i);

@@ -232,6 +232,21 @@ class _GraphRunner:
         self.mempool = None
 
     def _capture(self, key, n_tokens: int, n_seqs: int, decode_only: bool) -> None:
+        """Warm up and capture one step shape. A capture that the runtime invalidates (an unrelated call elsewhere in the
+        process while the stream was capturing) is repeated once from the warm-up; a second failure is raised."""
+        for attempt in (0, 1):
+            try:
+                self._capture_once(key, n_tokens, n_seqs, decode_only)
+                return
+            except (RuntimeError, _lib.NanoserveB200Error) as e:
+                if attempt or "capture" not in str(e):
+                    raise
+                self.capture_retries += 1
+                torch.cuda.synchronize()
+
+    capture_retries = 0
+
+    def _capture_once(self, key, n_tokens: int, n_seqs: int, decode_only: bool) -> None:
         buf = self.buffers
         # warm-up and capture run on an all-padding step: nothing but the garbage block is written
         buf.upload([], [], [], pad_seqs=n_seqs, pad_tokens=n_tokens)
@@ -245,10 +260,13 @@ class _GraphRunner:
             self.mempool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         before = _lib.launch_count
-        with torch.cuda.graph(graph, pool=self.mempool):
-            out = buf.step(n_tokens, n_seqs, decode_only)
-        self.launches[key] = _lib.launch_count - before
-        _lib.note_launches(-self.launches[key])       # captured, not executed
+        try:
+            with torch.cuda.graph(graph, pool=self.mempool):
+                out = buf.step(n_tokens, n_seqs, decode_only)
+        finally:
+            captured = _lib.launch_count - before
+            _lib.note_launches(-captured)             # captured, not executed
+        self.launches[key] = captured
         self.graphs[key], self.outputs[key] = graph, out
 
     def replay(self, key) -> None:

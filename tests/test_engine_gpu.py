@@ -29,7 +29,9 @@ TIE_GAP_F32 = 1e-3
 # twice the error MEASURED in the same run, which itself must stay below this bound.
 LOGIT_TOL_BF16 = 0.10
 LOGIT_TOL_F32 = 2e-4
-TINY_LOGIT_TOL_BF16 = 0.25       # tiny model: logits of magnitude ~10 (embedding std 0.5), bf16 ulp 0.06 there
+# tiny model: logits reach +-25 (embedding std 0.5), where a bf16 ulp is 0.125; torch's own CPU bf16 path differs from the
+# fp32 oracle by 0.93 on these requests
+TINY_LOGIT_TOL_BF16 = 1.5
 
 
 def gpu_model(cfg: dict, sd: dict, dtype):
