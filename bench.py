@@ -584,17 +584,63 @@ def extra_workload(args) -> None:
             init_nccl(device)
         else:
             dist.init_process_group("gloo", rank=0, world_size=1, init_method="tcp://127.0.0.1:29533")
-        model = random_tp_model("qwen2.5-7b", device=device)
-        reqs = serving_requests(args.requests or 256, prompt_range=(256, 4096), output_range=(64, 512), vocab=152064, seed=4)
+        # the job's ranks form world / tp tensor-parallel replicas of tp ranks each; every replica serves its share of
+        # the 256 requests at c=64 (benchmark configuration 4: TP = 1 / 2 / 4, and two TP=4 replicas on 8 GPUs)
+        tp = args.tp_size or world
+        if world % tp:
+            raise SystemExit(f"--tp-size {tp} does not divide the {world} ranks of this job")
+        n_groups, my_group = world // tp, rank // tp
+        group = None
+        for g in range(n_groups):
+            ranks = list(range(g * tp, (g + 1) * tp))
+            h = dist.new_group(ranks) if world > 1 else None
+            if g == my_group:
+                group = h
+        model = random_tp_model("qwen2.5-7b", group=group, device=device)
+        all_reqs = serving_requests(args.requests or 256, prompt_range=(256, 4096), output_range=(64, 512), vocab=152064, seed=4)
+        reqs = all_reqs[my_group::n_groups]
         eng = LLMEngine(model, eos_token_ids=[], max_seq_len=4608, max_num_seqs=64, max_num_batched_tokens=2048,
                         kv_cache_tokens=64 * 4608, lookahead=not args.no_lookahead)
         eng.capture_graphs()
         timed_pass(eng, reqs[:64], 64)
+        if world > 1:
+            dist.barrier()
         secs, n = timed_pass(eng, reqs, 64)
         t = torch.tensor([secs], dtype=torch.float64, device=device)
+        toks = torch.tensor([n if rank % tp == 0 else 0], dtype=torch.float64, device=device)   # one count per replica
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        res["tp"] = {"tp_degree": world, "tok_per_s": n / t.item(), "requests": len(reqs), "engine_steps": eng.stats["steps"]}
+            dist.all_reduce(toks, op=dist.ReduceOp.SUM)
+        res["tp"] = {"tp_degree": tp, "replicas": n_groups, "tok_per_s": toks.item() / t.item(), "requests": len(all_reqs),
+                     "requests_per_replica": len(reqs), "output_tokens": int(toks.item()), "seconds": t.item(),
+                     "engine_steps": eng.stats["steps"], "graph_steps": eng.stats["graph_steps"],
+                     "mixed_steps": eng.stats["piecewise_steps"], "device_status": eng.buffers.status_seen}
+        # share of a decode step spent in the 2 x 28 all-reduces: the same 64-row decode graph, captured once with the
+        # all-reduces and once without them (results of the second are wrong, its timing is what is wanted), replayed
+        # 30 times each on the pool as the run left it
+        if tp > 1 and args.allreduce_share:
+            runner = eng.graph_runner
+
+            def decode_graph_us() -> float:
+                runner.graphs.pop(64, None)
+                runner._capture(64, 64, 64, True)
+                torch.cuda.synchronize()
+                dist.barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(30):
+                    runner.replay(64)
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) * 1e3 / 30
+
+            with_ar = decode_graph_us()
+            model_in_graph = eng.model
+            saved, model_in_graph.tp_group = model_in_graph.tp_group, None
+            without_ar = decode_graph_us()
+            model_in_graph.tp_group = saved
+            res["tp"]["decode_step_us_bucket64"] = {"with_all_reduce": with_ar, "without_all_reduce": without_ar,
+                                                    "all_reduce_share": 1 - without_ar / with_ar}
     if rank == 0:
         print(json.dumps(res))
     if world > 1:
@@ -653,6 +699,9 @@ def main() -> None:
     ap.add_argument("--workload", default="serve", choices=["serve", "sweep", "prefix", "tp"],
                     help="serve = the benchmark contract's line (default); the others print one JSON object of extras")
     ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--tp-size", type=int, default=0, help="tp workload: ranks per tensor-parallel replica (default: all)")
+    ap.add_argument("--allreduce-share", action="store_true",
+                    help="tp workload: also time a 64-row decode graph with and without its all-reduces")
     ap.add_argument("--router", type=int, default=0, metavar="N",
                     help="serve one request stream through N engine processes (GPUs 0..N-1) behind the replica router")
     ap.add_argument("--no-lookahead", action="store_true",

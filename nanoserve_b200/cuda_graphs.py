@@ -99,6 +99,7 @@ class StepBuffers:
         self._sample_staging = [torch.zeros(8 * self.max_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._sample_np = [(t.numpy(), t.numpy().view(np.float32)) for t in self._sample_staging]
         self._sample_turn = 0
+        self._sample_done = [torch.cuda.Event() for _ in range(2)]
         self._sample_live = False         # the device copy holds an enabled row
         # two pinned landing buffers for sampled tokens and two pinned staging buffers for packed steps, used in
         # turn: with one step in flight the host may fill step t+1's staging buffer while step t's copy is pending
@@ -109,6 +110,7 @@ class StepBuffers:
         self._staging = [torch.zeros(self.capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._staging_np = [t.numpy() for t in self._staging]
         self._staging_turn = 0
+        self._staging_done = [torch.cuda.Event() for _ in range(2)]
         self.host_packed = self._staging[0]          # the staging buffer of the latest upload
         self.dev_packed = torch.zeros(self.capacity, **i32)
         nh = cfg.n_heads // getattr(model, "tp_size", 1)
@@ -123,6 +125,9 @@ class StepBuffers:
                              f"({self.max_seqs} / {self.max_tokens})")
         self._staging_turn ^= 1
         self.host_packed = self._staging[self._staging_turn]
+        # the copy that last read this pinned buffer must have run before the host writes it again (a caller that issues
+        # several steps without reading anything back, like a chain of draft steps, gets here with copies still queued)
+        self._staging_done[self._staging_turn].synchronize()
         a = self._staging_np[self._staging_turn]
         a[:_HEADER_INTS] = (n_seqs, n_tokens, pad_seqs, pad_tokens, n_app, self.garbage_block, self.block_size,
                             self.table_width)
@@ -139,6 +144,7 @@ class StepBuffers:
             a[o:o + len(token_ids)] = token_ids
         self.packed_ints = n
         self.dev_packed[:n].copy_(self.host_packed[:n], non_blocking=True)
+        self._staging_done[self._staging_turn].record()
 
     def set_sampling(self, rows: list[tuple]) -> None:
         """rows: (row, temperature, top_p, top_k, 63-bit draw seed) for every sequence row of the coming step that
@@ -146,6 +152,7 @@ class StepBuffers:
         if not rows and not self._sample_live:
             return
         self._sample_turn ^= 1
+        self._sample_done[self._sample_turn].synchronize()
         ints, floats = self._sample_np[self._sample_turn]
         ints[:] = 0
         for row, temperature, top_p, top_k, seed in rows:
@@ -154,6 +161,7 @@ class StepBuffers:
             ints[o + 2], ints[o + 3] = top_k, 1
             ints[o + 4:o + 6] = np.array([seed & 0xFFFFFFFF, seed >> 32], dtype=np.uint32).view(np.int32)
         self.sample_params.copy_(self._sample_staging[self._sample_turn], non_blocking=True)
+        self._sample_done[self._sample_turn].record()
         self._sample_live = bool(rows)
 
     @staticmethod
