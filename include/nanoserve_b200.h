@@ -53,11 +53,24 @@ int ns_get_tuning(int knob);
 
 /* One status word per engine step, written on the device: *status = number of bounded waits that have run out so far
  * in this library's kernels on the current device (bulk-copy / mbarrier waits of the decode GEMMs, tcgen05 waits of the
- * prefill attention kernel counted in attn_workspace's plan header; attn_workspace may be NULL). The counts are
+ * prefill attention kernel counted in attn_workspace's plan header; attn_workspace may be NULL) plus the violations
+ * ns_check_step_metadata has counted. The counts are
  * cumulative; a caller compares with the value it saw last. Results of a launch that raised the count are undefined.
  * Graph-capturable once it has run once on the device outside capture (it resolves device symbol addresses then).
  * No counterpart in the reference (device code there never reports errors, nanoserve/kernels/fused.py). */
 int ns_collect_status(const void* attn_workspace, int64_t* status, void* stream);
+
+/* Bounds check of one step's device metadata (the stand-in for a memory checker on this path; one small kernel): block
+ * ids of every sequence's context < num_blocks; cu_seqlens starts at 0, is non-decreasing and stays within n_tokens; every
+ * seq_len >= its query length; when slot_mapping and positions are given (both or neither), every new token's position
+ * is context + its index and its slot is table[pos / block_size] * block_size + pos % block_size, inside the pool; when
+ * tokens is given, ids lie in [0, vocab). Violations are counted into the status word of ns_collect_status; nothing
+ * traps and no access is skipped. cu_seqlens / table_rows may be NULL as in ns_ragged_paged_attn.
+ * No counterpart in the reference (its device code checks nothing; it would run under compute-sanitizer instead). */
+int ns_check_step_metadata(const int32_t* block_tables, const int32_t* table_rows, int64_t table_stride,
+                           const int32_t* seq_lens, const int32_t* cu_seqlens, const int64_t* slot_mapping,
+                           const int64_t* positions, const int64_t* tokens, int32_t n_seqs, int64_t n_tokens,
+                           int32_t num_blocks, int32_t block_size, int32_t vocab, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Fused token-wise ops.

@@ -102,6 +102,62 @@ __global__ void __launch_bounds__(kMetaThreads) build_step_metadata_kernel(
     }
 }
 
+// Bounds check of one step's device metadata, the stand-in for a memory checker on this path: every block id a
+// sequence's context touches is < num_blocks, every slot is < num_blocks * block_size and is the slot its table gives for
+// its position, cu_seqlens starts at 0, is non-decreasing and stays within n_tokens, every sequence's length is at least its query length,
+// token ids are inside the vocabulary. A violation is COUNTED (g_check_errors, reported through ns_collect_status) -
+// nothing traps and nothing is skipped: the caller decides what a non-zero count means.
+__device__ unsigned int g_check_errors = 0;
+
+__global__ void __launch_bounds__(256) check_step_metadata_kernel(
+    const int32_t* __restrict__ block_tables, const int32_t* __restrict__ table_rows, int64_t table_stride,
+    const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ cu_seqlens, const int64_t* __restrict__ slot_mapping,
+    const int64_t* __restrict__ positions, const int64_t* __restrict__ tokens, int n_seqs, int64_t n_tokens,
+    int num_blocks, int block_size, int vocab) {
+    unsigned bad = 0;
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    for (int s = tid; s < n_seqs; s += nthreads) {
+        const int q0 = cu_seqlens ? cu_seqlens[s] : s, q1 = cu_seqlens ? cu_seqlens[s + 1] : s + 1;
+        const int len = seq_lens[s];
+        if (q1 < q0 || len < q1 - q0 || len < 0) { ++bad; continue; }
+        if (q1 > n_tokens) ++bad;                  // (a padded step may leave rows past the last sequence unused)
+        if (s == 0 && q0 != 0) ++bad;
+        const int32_t* row = block_tables + (int64_t)(table_rows ? table_rows[s] : s) * table_stride;
+        const int nb = (len + block_size - 1) / block_size;
+        if (nb > table_stride) { ++bad; continue; }
+        for (int j = 0; j < nb; ++j)
+            if (row[j] < 0 || row[j] >= num_blocks) ++bad;
+        // this step's new tokens: position = ctx + j, slot = table[pos / bs] * bs + pos % bs
+        if (slot_mapping != nullptr && positions != nullptr)
+            for (int t = q0; t < q1; ++t) {
+                const int64_t pos = positions[t], slot = slot_mapping[t];
+                if (pos != (int64_t)(len - (q1 - q0)) + (t - q0)) { ++bad; continue; }
+                if (slot < 0 || slot >= (int64_t)num_blocks * block_size) { ++bad; continue; }
+                const int32_t b = row[pos / block_size];
+                if (b >= 0 && b < num_blocks && slot != (int64_t)b * block_size + pos % block_size) ++bad;
+            }
+    }
+    if (tokens != nullptr && vocab > 0)
+        for (int64_t t = tid; t < n_tokens; t += nthreads)
+            if (tokens[t] < 0 || tokens[t] >= vocab) ++bad;
+    if (bad) atomicAdd(&g_check_errors, bad);
+}
+
+// Device address of the check counter on the current device (resolved once per device, outside stream capture).
+int check_error_counter(const unsigned int** out) {
+    static const unsigned int* addr[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(NS_ERR_CUDA, "check_error_counter: no current device");
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_check_errors);
+        if (e != cudaSuccess || p == nullptr) return fail(NS_ERR_CUDA, "check_error_counter: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        addr[dev] = static_cast<const unsigned int*>(p);
+    }
+    *out = addr[dev];
+    return NS_OK;
+}
+
 // Greedy sampling: a cluster of CTAs per logits row (each scans a share of the vocabulary; the candidates meet in the
 // first CTA's shared memory through DSMEM, no global scratch); ties resolve to the lowest index. The token is stored
 // to out[row] and, when seat_of != NULL, to last_tokens[seat_of[row]] so the next step can read it without a host
@@ -228,4 +284,21 @@ extern "C" int ns_argmax_rows(const void* logits, int64_t row_stride, int32_t ro
         return fail(NS_ERR_UNSUPPORTED, "argmax_rows: dtype %d", dtype);
     }
     return check_launch("argmax_rows");
+}
+
+extern "C" int ns_check_step_metadata(const int32_t* block_tables, const int32_t* table_rows, int64_t table_stride,
+                                      const int32_t* seq_lens, const int32_t* cu_seqlens, const int64_t* slot_mapping,
+                                      const int64_t* positions, const int64_t* tokens, int32_t n_seqs, int64_t n_tokens,
+                                      int32_t num_blocks, int32_t block_size, int32_t vocab, void* stream) {
+    NS_REQUIRE(block_tables && seq_lens, NS_ERR_INVALID_ARG, "check_step_metadata: null pointer");
+    NS_REQUIRE(n_seqs >= 0 && n_tokens >= 0 && num_blocks > 0 && block_size > 0 && table_stride > 0, NS_ERR_INVALID_ARG,
+               "check_step_metadata: bad shape");
+    NS_REQUIRE((slot_mapping == nullptr) == (positions == nullptr), NS_ERR_INVALID_ARG,
+               "check_step_metadata: slot_mapping and positions go together");
+    if (n_seqs == 0) return NS_OK;
+    const int grid = (int)((n_tokens > n_seqs ? n_tokens : n_seqs) + 255) / 256;
+    check_step_metadata_kernel<<<grid < 1 ? 1 : (grid > 64 ? 64 : grid), 256, 0, (cudaStream_t)stream>>>(
+        block_tables, table_rows, table_stride, seq_lens, cu_seqlens, slot_mapping, positions, tokens, n_seqs, n_tokens,
+        num_blocks, block_size, vocab);
+    return check_launch("check_step_metadata");
 }

@@ -16,6 +16,8 @@ What changed underneath:
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -176,6 +178,16 @@ class StepBuffers:
                   self.slots.data_ptr(), self.cu_seqlens.data_ptr(), self.seq_lens.data_ptr(), self.seat_of.data_ptr(),
                   self.last_rows.data_ptr(), self.max_seqs, self.max_tokens, _lib.stream_ptr())
 
+    # NS_BOUNDS_CHECK=1 adds ns_check_step_metadata to every step (and to every captured graph): block ids, slots,
+    # positions, cu_seqlens and token ids are verified on the device and violations arrive with the step's status word
+    bounds_check = os.environ.get("NS_BOUNDS_CHECK", "0") not in ("", "0")
+
+    def check(self, n_tokens: int, n_seqs: int) -> None:
+        _lib.call("ns_check_step_metadata", self.mirror.data_ptr(), self.seat_of.data_ptr(), self.mirror.stride(0),
+                  self.seq_lens.data_ptr(), self.cu_seqlens.data_ptr(), self.slots.data_ptr(), self.positions.data_ptr(),
+                  self.tokens.data_ptr(), n_seqs, n_tokens, self.pool.num_blocks, self.block_size,
+                  self.model.cfg.vocab_size, _lib.stream_ptr())
+
     def meta(self, n_tokens: int, n_seqs: int, decode_only: bool) -> StepMeta:
         return StepMeta(tokens=self.tokens[:n_tokens], positions=self.positions[:n_tokens],
                         slot_mapping=self.slots[:n_tokens], cu_seqlens=self.cu_seqlens[:n_seqs + 1],
@@ -196,6 +208,8 @@ class StepBuffers:
     def step(self, n_tokens: int, n_seqs: int, decode_only: bool) -> torch.Tensor:
         """metadata kernel -> forward -> argmax over the first n_tokens / n_seqs rows; returns the logits."""
         self.build()
+        if self.bounds_check:
+            self.check(n_tokens, n_seqs)
         logits = self.model.forward_step(self.meta(n_tokens, n_seqs, decode_only), self.pool)
         self.sample(logits, n_seqs)
         return logits

@@ -4,6 +4,7 @@
     python -m nanoserve_b200.probes --layer-probe 32        # marginal cost of each kernel of a decode layer, 32 rows
     python -m nanoserve_b200.probes --attn-overlap-probe    # prefill kernel after / beside the decode kernel
     python -m nanoserve_b200.probes --fused-ops 2048        # the token-wise fused ops at a 2048-token step, GB/s each
+    python -m nanoserve_b200.probes --decode-step-probe qwen2.5-7b --rows 64 --layers 4    # decode steps of another shape
 
 Each prints one JSON object. The launch probe brackets its steps with cudaProfilerStart/Stop so that
 `ncu --profile-from-start off` lists exactly those launches.
@@ -261,12 +262,54 @@ def fused_ops_probe(tokens: int, reps: int = 20) -> None:
     print(json.dumps(out))
 
 
+def decode_step_probe(shape: str, rows: int, layers: int, ctx: int) -> None:
+    """`rows` sequences of about `ctx` context tokens decoding on a random-init model of the named architecture (first
+    `layers` layers), bf16: three decode steps inside a profiler range (cudaProfilerStart/Stop) for a launch list, then
+    the device time of 20 graph replays of that step."""
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.model import ModelConfig, Qwen2Model
+    from nanoserve_b200.synthetic import random_state_dict, serving_requests
+    sd, cfg = random_state_dict(shape, dtype=torch.bfloat16, device="cuda", n_layers=layers)
+    eng = LLMEngine(Qwen2Model(ModelConfig(**cfg), sd), eos_token_ids=[], max_seq_len=ctx + 256, max_num_seqs=rows,
+                    kv_cache_tokens=rows * (ctx + 256))
+    for p, n in serving_requests(rows, prompt_range=(ctx - 50, ctx + 50), output_range=(64, 64), vocab=cfg["vocab_size"]):
+        eng.add_request(p, n, ignore_eos=True)
+    while eng.last_step is None or eng.last_step.n_prefill:
+        eng.step()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    key = eng.graph_runner.last_key
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        eng.graph_runner.replay(key)
+    b.record()
+    torch.cuda.synchronize()
+    weights = sum(t.numel() * t.element_size() for n, t in sd.items() if "embed" not in n)
+    if cfg["tie_word_embeddings"]:
+        weights += cfg["vocab_size"] * cfg["hidden_size"] * 2          # the LM head reads the embedding matrix
+    us = a.elapsed_time(b) * 1e3 / 20
+    print(json.dumps({"shape": shape, "layers": layers, "rows": rows, "ctx": ctx, "bucket": key, "decode_step_us": round(us, 1),
+                      "launches_per_step": eng.graph_runner.launches[key], "weight_bytes": weights,
+                      "weights_over_measured_hbm_us": round(weights / 6542.1e9 * 1e6, 1)}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--launch-probe", action="store_true")
     ap.add_argument("--attn-overlap-probe", action="store_true")
     ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS")
     ap.add_argument("--fused-ops", type=int, default=0, metavar="TOKENS")
+    ap.add_argument("--decode-step-probe", default="", metavar="SHAPE", help="e.g. qwen2.5-7b")
+    ap.add_argument("--rows", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=1000)
     args = ap.parse_args()
     torch.cuda.set_device(0)
     if args.launch_probe:
@@ -277,6 +320,8 @@ def main() -> None:
         attn_overlap_probe()
     elif args.fused_ops:
         fused_ops_probe(args.fused_ops)
+    elif args.decode_step_probe:
+        decode_step_probe(args.decode_step_probe, args.rows, args.layers, args.ctx)
     else:
         ap.error("choose a probe")
 

@@ -16,6 +16,10 @@ SHAPES = {
     "qwen2.5-0.5b": (24, 896, 14, 2, 64, 4864, 151936, True),
     "qwen2.5-1.5b": (28, 1536, 12, 2, 128, 8960, 151936, True),
     "qwen2.5-7b": (28, 3584, 28, 4, 128, 18944, 152064, False),
+    # one rank's shard of the 7B shape under tensor parallelism by KV head (hidden size unchanged): for single-GPU
+    # measurements of a shard's kernels, without the all-reduces
+    "qwen2.5-7b-tp2": (28, 3584, 14, 2, 128, 9472, 152064, False),
+    "qwen2.5-7b-tp4": (28, 3584, 7, 1, 128, 4736, 152064, False),
 }
 
 

@@ -334,3 +334,57 @@ def test_device_status_word_reaches_the_host(lookahead):
     after = run_requests(eng, reqs[3:6], concurrency=3)
     fresh = run_requests(make_engine(model, **G.TINY_ENGINE_KW), reqs[3:6], concurrency=3)
     assert after == fresh
+
+
+def _status_word() -> int:
+    from nanoserve_b200 import _lib
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    _lib.call("ns_collect_status", None, out.data_ptr(), _lib.stream_ptr())
+    return int(out.item())
+
+
+def test_bounds_check_counts_bad_metadata_and_stays_silent_on_good_steps(monkeypatch):
+    """ns_check_step_metadata, the memory checker's stand-in: corrupted tables / slots / cu_seqlens / token ids (plain
+    data handed to the check kernel, which never follows a block id into the pool) are counted into the status word; an
+    engine run with NS_BOUNDS_CHECK=1 carries the check in every step and graph, reports nothing and samples the same
+    tokens."""
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.cuda_graphs import StepBuffers
+    i32 = dict(dtype=torch.int32, device="cuda")
+    tables = torch.tensor([[3, 7, 0, 0], [5, 0, 0, 0], [9, 2, 4, 0]], **i32)
+    seq_lens = torch.tensor([20, 1, 35], **i32)                     # seq 0: chunk of 4 on 16 cached; 1: fresh token; 2: decode
+    cu = torch.tensor([0, 4, 5, 6], **i32)
+    positions = torch.tensor([16, 17, 18, 19, 0, 34], dtype=torch.int64, device="cuda")
+    slots = torch.tensor([7 * 16 + 0, 7 * 16 + 1, 7 * 16 + 2, 7 * 16 + 3, 5 * 16, 4 * 16 + 2], dtype=torch.int64, device="cuda")
+    tokens = torch.tensor([1, 2, 3, 4, 5, 6], dtype=torch.int64, device="cuda")
+
+    def count(tb=tables, sl=seq_lens, c=cu, pos=positions, slt=slots, tok=tokens, num_blocks=10):
+        before = _status_word()
+        _lib.call("ns_check_step_metadata", tb.data_ptr(), None, tb.stride(0), sl.data_ptr(), c.data_ptr(), slt.data_ptr(),
+                  pos.data_ptr(), tok.data_ptr(), 3, 6, num_blocks, 16, 512, _lib.stream_ptr())
+        return _status_word() - before
+
+    assert count() == 0
+    assert count(num_blocks=9) == 1                                  # block 9 of sequence 2 is outside a 9-block pool
+    bad = tables.clone(); bad[0, 1] = -1
+    assert count(tb=bad) == 1                                        # (its slots are then not compared with that entry)
+    bad = slots.clone(); bad[5] = 4 * 16 + 3
+    assert count(slt=bad) == 1                                       # a slot that is not the table's slot for its position
+    bad = slots.clone(); bad[4] = 10 * 16
+    assert count(slt=bad) == 1                                       # a slot past the pool
+    bad = cu.clone(); bad[1] = 7
+    assert count(c=bad) >= 1                                         # cu_seqlens not monotone / outside the step
+    bad = tokens.clone(); bad[2] = 512
+    assert count(tok=bad) == 1
+    bad = seq_lens.clone(); bad[0] = 3
+    assert count(sl=bad) == 1                                        # fewer tokens in the sequence than it feeds this step
+
+    cfg, sd = G.TINY_CFG, G.tiny_state_dict(G.TINY_CFG)
+    model = gpu_model(cfg, sd, torch.float32)
+    plain = run_requests(make_engine(model, **G.TINY_ENGINE_KW), G.tiny_requests(), concurrency=4)
+    monkeypatch.setattr(StepBuffers, "bounds_check", True)
+    before = _lib.launch_count
+    eng = make_engine(model, **G.TINY_ENGINE_KW)
+    checked = run_requests(eng, G.tiny_requests(), concurrency=4)
+    assert checked == plain and eng.buffers.status_seen == _status_word()
+    assert eng.stats["graph_steps"] > 0 and eng.stats["piecewise_steps"] > 0
