@@ -495,8 +495,8 @@ def run_gpu_arm(args) -> None:
                                                                                  "num_preemptions", "peak_running")},
         "clocks": clocks.summary(), "host_cpus": os.cpu_count(),
     }
-    line["device_status"] = eng.buffers.status_seen       # bounded waits that ran out in any kernel of any step: must be 0
-    if eng.buffers.status_seen:
+    line["device_status"] = eng.buffers.device_errors       # bounded waits that ran out in any kernel of any step: must be 0
+    if eng.buffers.device_errors:
         line["invalid"] = "a kernel gave up on a bounded wait during the run: the numbers above are not a measurement"
     if rank == 0:
         if world == 1:
@@ -614,7 +614,7 @@ def extra_workload(args) -> None:
         res["tp"] = {"tp_degree": tp, "replicas": n_groups, "tok_per_s": toks.item() / t.item(), "requests": len(all_reqs),
                      "requests_per_replica": len(reqs), "output_tokens": int(toks.item()), "seconds": t.item(),
                      "engine_steps": eng.stats["steps"], "graph_steps": eng.stats["graph_steps"],
-                     "mixed_steps": eng.stats["piecewise_steps"], "device_status": eng.buffers.status_seen}
+                     "mixed_steps": eng.stats["piecewise_steps"], "device_status": eng.buffers.device_errors}
         # share of a decode step spent in the 2 x 28 all-reduces: the same 64-row decode graph, captured once with the
         # all-reduces and once without them (results of the second are wrong, its timing is what is wanted), replayed
         # 30 times each on the pool as the run left it

@@ -33,7 +33,8 @@ _SIDE_STREAM = None
 
 
 class DeviceStatusError(_lib.NanoserveB200Error):
-    """A kernel of an engine step gave up on a bounded wait (the library's status word grew)."""
+    """A kernel of an engine step gave up on a bounded wait, or the step's bounds check found a violation (the library's
+    status word grew)."""
 
 
 def _capture_stream() -> torch.cuda.Stream:
@@ -94,7 +95,7 @@ class StepBuffers:
         # device->host copy per step brings back both.
         self.fetched = torch.zeros(1 + self.max_seqs, **i64)
         self.sampled = self.fetched[1:]
-        self.status_seen = 0              # status word of the newest step that was read back
+        self.status_seen = 0              # status word of the newest step that was read back (process-wide, cumulative)
         # per-row sampling parameters read by the sampling kernel inside the graphs (8 words per row, all zero = every
         # row greedy); uploaded only on steps that sample and on the first all-greedy step after one
         self.sample_params = torch.zeros(8 * self.max_seqs, **i32)
@@ -117,6 +118,9 @@ class StepBuffers:
         self.dev_packed = torch.zeros(self.capacity, **i32)
         nh = cfg.n_heads // getattr(model, "tp_size", 1)
         self.workspace = AttnWorkspace(self.max_seqs, self.max_tokens, nh, cfg.head_dim, dev)
+        # the library's counters are process-wide and cumulative: this engine reports what is counted from now on
+        _lib.call("ns_collect_status", self.workspace.buf.data_ptr(), self.fetched.data_ptr(), _lib.stream_ptr())
+        self.status_base = self.status_seen = self._status_ok = int(self.fetched[0].item())
 
     def upload(self, records: list[int], appends: list[int], token_ids: list[int], pad_seqs: int, pad_tokens: int) -> None:
         """Fill the pinned staging buffer and start its copy to the device (stream-ordered before the graph)."""
@@ -233,11 +237,14 @@ class StepBuffers:
         status, self.status_seen = words[0], max(self.status_seen, words[0])
         if status > self._status_ok:
             grown, self._status_ok = status - self._status_ok, status
-            raise DeviceStatusError(f"{grown} bounded wait(s) ran out inside this step's kernels (status word {status}): "
-                                    "its tokens are undefined")
+            raise DeviceStatusError(f"{grown} device-side error(s) in this step's kernels - bounded waits that ran out, or "
+                                    f"bounds-check violations (status word {status}): its tokens are undefined")
         return words[1:]
 
-    _status_ok = 0                       # status word up to which errors have been reported
+    @property
+    def device_errors(self) -> int:
+        """Failed bounded waits / bounds-check violations counted since this object was built."""
+        return self.status_seen - self.status_base
 
     def fetch_sampled(self, n: int) -> list[int]:
         return self.wait_fetch(self.queue_fetch(n))

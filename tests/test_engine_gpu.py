@@ -322,7 +322,7 @@ def test_device_status_word_reaches_the_host(lookahead):
         eng.add_request(p, n, ignore_eos=True)
     for _ in range(3):
         eng.step()
-    assert eng.buffers.status_seen == 0
+    assert eng.buffers.device_errors == 0
     errors_word = eng.buffers.workspace.buf[32:36].view(torch.int32)      # PlanHeader::errors
     errors_word += 1
     with pytest.raises(DeviceStatusError):
@@ -330,7 +330,7 @@ def test_device_status_word_reaches_the_host(lookahead):
             eng.step()
     assert not eng.has_unfinished() and not eng.sequences
     assert eng.kv.num_free_blocks == eng.kv.pool.num_blocks - 1
-    assert eng.buffers.status_seen == 1
+    assert eng.buffers.device_errors == 1
     after = run_requests(eng, reqs[3:6], concurrency=3)
     fresh = run_requests(make_engine(model, **G.TINY_ENGINE_KW), reqs[3:6], concurrency=3)
     assert after == fresh
@@ -386,5 +386,5 @@ def test_bounds_check_counts_bad_metadata_and_stays_silent_on_good_steps(monkeyp
     before = _lib.launch_count
     eng = make_engine(model, **G.TINY_ENGINE_KW)
     checked = run_requests(eng, G.tiny_requests(), concurrency=4)
-    assert checked == plain and eng.buffers.status_seen == _status_word()
+    assert checked == plain and eng.buffers.device_errors == 0
     assert eng.stats["graph_steps"] > 0 and eng.stats["piecewise_steps"] > 0
