@@ -46,7 +46,9 @@ typedef enum {
     NS_TUNE_DECODE_MIN_BLOCKS = 3,   /* lower bound of a decode CTA's range in KV blocks; <= 0 (default): built-in */
     NS_TUNE_DECODE_SNAP_BLOCKS = 4,  /* how far a cut may move to reach a row boundary; <= 0 (default): built-in */
     NS_TUNE_DECODE_BALANCE = 5,      /* 2 (default): row-aligned balanced cuts for large steps; 0: equal cuts snapped to rows */
-    NS_TUNE_COUNT = 6
+    NS_TUNE_DECODE_CLUSTER = 6,      /* 1 (default): small decode steps give every row a thread-block cluster of CTAs; 0: off */
+    NS_TUNE_DECODE_CLUSTER_BLOCKS = 7, /* decode KV blocks up to which a step may run in cluster mode; <= 0 (default): built-in */
+    NS_TUNE_COUNT = 8
 } ns_tuning_knob;
 int ns_set_tuning(int knob, int value);
 int ns_get_tuning(int knob);

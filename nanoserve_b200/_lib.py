@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libnanoserve_b200.so"
 NS_BF16, NS_F32 = 0, 1
 # ns_tuning_knob
 (TUNE_PREFILL_IMPL, TUNE_PREFILL_OVERLAP, TUNE_DECODE_SPLIT_BLOCKS, TUNE_DECODE_MIN_BLOCKS, TUNE_DECODE_SNAP_BLOCKS,
- TUNE_DECODE_BALANCE) = range(6)
+ TUNE_DECODE_BALANCE, TUNE_DECODE_CLUSTER, TUNE_DECODE_CLUSTER_BLOCKS) = range(8)
 
 # name -> (restype, argtypes); mirrors include/nanoserve_b200.h declaration by declaration.
 _P, _I32, _I64, _F = c_void_p, c_int32, c_int64, c_float

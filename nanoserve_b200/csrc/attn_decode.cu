@@ -18,6 +18,8 @@
 
 namespace ns {
 
+bool decode_cluster_enabled();      // c_api.cu: NS_TUNE_DECODE_CLUSTER
+
 __device__ __forceinline__ long long global_ns() {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -38,6 +40,48 @@ template <int HD> __device__ __forceinline__ uint32_t tile_off(int row, int chun
     (void)CPR;
 }
 
+
+// Cluster mode, first CTA of the cluster, after the cluster barrier: pieces[rank][kv head][8 rows][HD + 4] hold every
+// rank's partial of the cluster's decode row (O[HD], m, l; row 0 also carries the query row and a "delivered" flag). Sum
+// them and write the row. A row that one CTA held completely was written by that CTA and delivered nothing.
+template <int HD>
+__device__ __forceinline__ void cluster_combine(const AttnParams& p, const float* pieces, int cm, int tid, int nthreads) {
+    constexpr int RED_ROW = HD + 4, V4 = HD / 4;
+    const int NKV = p.n_kv_heads, GROUP = p.group;
+    for (int e = tid; e < NKV * GROUP * V4; e += nthreads) {
+        const int g = e / (GROUP * V4), rem = e - g * (GROUP * V4);
+        const int r = rem / V4, c4 = rem - r * V4;
+        float M = -INFINITY;
+        int qrow = -1;
+        for (int k = 0; k < cm; ++k) {
+            const float* head = pieces + (size_t)(k * NKV + g) * 8 * RED_ROW;
+            if (head[HD + 3] != 0.f) {
+                qrow = __float_as_int(head[HD + 2]);
+                M = fmaxf(M, head[r * RED_ROW + HD]);
+            }
+        }
+        if (qrow < 0) continue;
+        float Ls = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < cm; ++k) {
+            const float* head = pieces + (size_t)(k * NKV + g) * 8 * RED_ROW;
+            if (head[HD + 3] == 0.f) continue;
+            const float* row = head + r * RED_ROW;
+            const float w = row[HD] > -INFINITY ? fast_exp2(row[HD] - M) : 0.f;
+            const float4 v = *reinterpret_cast<const float4*>(row + 4 * c4);
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
+            Ls = fmaf(w, row[HD + 1], Ls);
+        }
+        const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.out + (int64_t)qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + 4 * c4) = packed;
+    }
+}
 
 // MAX_MODE = 2: the plan may ask every CTA to act as TWO virtual CTAs of NWARPS/2 warps, each with its own range
 // (header field `mode`). Small steps (one CTA per row or less) want all 16 warps on one row; large ones want twice as
@@ -76,6 +120,13 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
             rec_b = b2;
         }
     }
+    // Cluster mode (small steps, chosen by the plan): this CTA's range is one piece of ONE decode row, the other pieces
+    // belong to the other CTAs of its thread-block cluster, and the pieces meet in the first CTA's shared memory
+    // (no global partials, no atomics, no second pass over them). It needs the launch's cluster size to be the plan's.
+    uint32_t crank, csize;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
+    const int cm = (csize > 1 && hdr->cluster == (int)csize) ? (int)csize : 0;
     const int half = split ? warp / HALF_WARPS : 0;           // which virtual CTA of this physical one
     const int vwarps = split ? HALF_WARPS : NWARPS;           // warps of a virtual CTA
     const int lw = warp - half * vwarps;                      // warp index inside it
@@ -87,9 +138,21 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     __shared__ int pend_n[2 * kMaxKvHeads];
     __shared__ int pend_last[2 * kMaxKvHeads][2];
     if (threadIdx.x < 2 * kMaxKvHeads) pend_n[threadIdx.x] = 0;
+    // cluster mode: slot [rank][head][row 0][HD + 3] of the first CTA's staging area says whether that rank delivered a
+    // piece; the first CTA clears the flags before anybody can write them (the cluster barrier below orders it)
+    float* const xstage = reinterpret_cast<float*>(smem + (size_t)NWARPS * STAGES * STAGE_BYTES);
+    if (cm && crank == 0)
+        for (int e = threadIdx.x; e < cm * p.n_kv_heads; e += blockDim.x) xstage[(size_t)e * 8 * RED_ROW + HD + 3] = 0.f;
     __syncthreads();                              // the only CTA-wide barrier; everything below is per head group
+    if (cm) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     if (u0 >= u1) {
-        if (p.overlap_prefill) pdl_wait();        // an exit counts as the trigger: it must not come before Q exists
+        if (p.overlap_prefill || cm) pdl_wait();  // an exit counts as the trigger: it must not come before Q exists
+        if (cm) {                                 // nothing to deliver: keep the cluster's two barriers matched
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (crank == 0) cluster_combine<HD>(p, xstage, cm, threadIdx.x, blockDim.x);
+        }
         return;
     }
 
@@ -208,6 +271,15 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         cp_async_commit();
     };
 
+    float* xremote = xstage;                  // cluster mode: the first CTA's staging area, through distributed shared memory
+    if (cm) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(smem_u32(xstage)));
+        uint64_t generic;
+        asm volatile("cvta.shared::cluster.u64 %0, %1;" : "=l"(generic) : "l"((uint64_t)remote));
+        xremote = reinterpret_cast<float*>(generic);
+    }
+
     // ---- running state of this warp for the current decode row ---------------------------------------------------
     float m_run = -INFINITY, l_run = 0.f;     // row = lane/4; l is this lane's share of the row sum
     float o[HD / 8][2];
@@ -264,12 +336,20 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
                 packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
                 packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
                 *reinterpret_cast<uint2*>(p.out + qrow * p.out_stride + (int64_t)(g * GROUP + r) * HD + c) = packed;
+            } else if (cm) {
+                // this CTA's piece of the row goes straight into the first CTA's shared memory
+                float* dst = xremote + ((size_t)(crank * NKV + g) * 8 + r) * RED_ROW;
+                *reinterpret_cast<float4*>(dst + c) = acc;
+                if (c == 0) {
+                    *reinterpret_cast<float2*>(dst + HD) = make_float2(M, Ls);
+                    if (r == 0) *reinterpret_cast<float2*>(dst + HD + 2) = make_float2(__int_as_float((int)qrow), 1.f);
+                }
             } else {
                 *reinterpret_cast<float4*>(part + r * RED_ROW + c) = acc;
                 if (c == 0) *reinterpret_cast<float2*>(part + r * RED_ROW + HD) = make_float2(M, Ls);
             }
         }
-        if (!complete && gt == 0) {           // cross-CTA work for this row is deferred to the end of the CTA
+        if (!complete && !cm && gt == 0) {    // cross-CTA work for this row is deferred to the end of the CTA
             const int k = pend_n[hg]++;
             pend[hg][k] = make_int4(i, lo, (int)qrow, 0);
             pend_span[hg][k] = cc_span;
@@ -303,6 +383,7 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
     if (full_ring) issue(STAGES - 1, true);
     pdl_wait();                               // Q and the new token's K/V row exist from here on
     if (p.overlap_prefill) pdl_launch_dependents();           // the prefill kernel may run beside this one from here on
+    if (cm) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // the first CTA runs and has cleared its flags
     if (early_q_i >= 0) {
         qn_row = early_q_i;
         load_q(qn, early_q_row);
@@ -427,6 +508,15 @@ __global__ void __launch_bounds__(NWARPS * 32, CTAS_PER_SM) paged_decode_kernel(
         next_row();
     }
     flush();
+
+    if (cm) {
+        // every CTA of the cluster has delivered (or has nothing): the first one sums the pieces and writes the row
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (crank == 0) cluster_combine<HD>(p, xstage, cm, threadIdx.x, blockDim.x);
+        if (p.timeline && threadIdx.x == 0) p.timeline[blockIdx.x * 4 + 3] = global_ns();
+        return;
+    }
 
     // ---- cross-CTA combine of the rows this CTA saw only a part of (at most its first and its last row) ------------
     // The partials were stored by every thread of the group before the barrier that ends flush(); the leader's fence
@@ -606,8 +696,29 @@ static int launch_decode_cfg(const AttnParams& p, int sms, cudaStream_t st) {
                                           smem, cudaGetErrorString(e));
         optin.done((size_t)smem);
     }
-    launch_pdl(paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>, dim3(sms * CTAS_PER_SM), dim3(NWARPS * 32), smem, st, p);
-    return check_launch("paged_decode");
+    // cluster size for small steps: what the plan proposed for this many sequences, as long as the pieces of a row
+    // (cluster x kv heads x 8 rows x (HD + 4) floats) fit the staging area they meet in
+    const int grid = sms * CTAS_PER_SM;
+    int cl = decode_cluster_enabled() ? plan_cluster(p.n_seqs, grid) : 1;
+    constexpr int stage_bytes = 2 * kMaxKvHeads * (16 * 16 + 16) * 4;
+    while (cl > 1 && cl * p.n_kv_heads * 8 * (HD + 4) * 4 > stage_bytes) cl >>= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NWARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cl;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, paged_decode_kernel<HD, NWARPS, STAGES, CTAS_PER_SM, MAX_MODE>, p);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "decode attention: launch failed: %s", cudaGetErrorString(e));
+    return NS_OK;
 }
 
 bool decode_fast_supported(int n_heads, int n_kv_heads, int head_dim, int block_size) {

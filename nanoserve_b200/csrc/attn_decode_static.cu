@@ -118,6 +118,7 @@ extern "C" int ns_paged_attn_decode_static(const void* q, const void* k_pool, co
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.group = n_heads / n_kv_heads;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.timeline = nullptr;
+    a.n_seqs = batch;
     a.plan_fresh = 1;                 // the plan kernel above is this launch's direct predecessor
     return launch_paged_decode(a, head_dim, sms, st);
 }

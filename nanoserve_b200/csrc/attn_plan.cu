@@ -41,7 +41,8 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
                                                                  const int32_t* __restrict__ table_rows, int n_seqs,
                                                                  int block_size, int base_ctas, int max_mode,
                                                                  int split_blocks, uint8_t* ws, WsLayout L, int max_items,
-                                                                 int min_blocks, int snap_blocks, int balance) {
+                                                                 int min_blocks, int snap_blocks, int balance, int cluster,
+                                                                 int cluster_blocks) {
     constexpr int kSmemRows = 2048;            // decode rows whose prefix is mirrored in shared memory
     __shared__ int warp_sums[33];
     __shared__ int indptr_sm[kSmemRows + 1];
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     int32_t* cta_first = reinterpret_cast<int32_t*>(ws + L.cta_first);
     int2* items = reinterpret_cast<int2*>(ws + L.prefill_items);
 
-    int n_dec = 0, dec_blocks = 0, n_items = 0;
+    int n_dec = 0, dec_blocks = 0, n_items = 0, my_max_nb = 0;
     for (int base = 0; base < n_seqs; base += kPlanThreads) {
         const int s = base + threadIdx.x;
         int is_dec = 0, nb = 0, tiles = 0, T = 0, len = 0, qrow = s;
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         const int ioff = block_exclusive_scan(tiles, warp_sums, tot);
         const int i_tot = tot;
         if (is_dec) {
+            my_max_nb = max(my_max_nb, nb);
             dec_info[n_dec + pos] = make_int4(s, len, table_rows ? table_rows[s] : s, qrow);
             dec_indptr[n_dec + pos] = dec_blocks + boff;
             if (n_dec + pos <= kSmemRows) indptr_sm[n_dec + pos] = dec_blocks + boff;
@@ -92,11 +94,16 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         dec_blocks += b_tot;
         n_items += i_tot;
     }
+    __shared__ int max_nb_sm;
     if (threadIdx.x == 0) {
         dec_indptr[n_dec] = dec_blocks;
         if (n_dec <= kSmemRows) indptr_sm[n_dec] = dec_blocks;
+        max_nb_sm = 0;
     }
     __syncthreads();
+    if (my_max_nb > 0) atomicMax(&max_nb_sm, my_max_nb);
+    __syncthreads();
+    const int max_nb = max_nb_sm;                  // blocks of the longest decode row
     const int* ip = n_dec <= kSmemRows ? indptr_sm : dec_indptr;
 
     // Large steps run every decode CTA as two virtual CTAs of half the warps (twice as many, shorter ranges); small
@@ -126,12 +133,36 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
     // and 2 times the average: measured on 48 rows x U[128,8192] tokens the slowest CTA streamed 20.8 us, the median 14.9.)
     // ... and for small steps whose rows are, on average, at least three quarters of a range long (many short rows per
     // range pack better with the equal cuts below: 256 rows x U[64,1024] tokens 19.4 vs 20.9 us)
-    const bool balanced = balance != 0 && n_dec <= kSmemRows &&
+    // Small steps: fewer rows than clusters and not much to stream. One CTA per row would leave most SMs idle and push a
+    // whole row through one SM's load path; instead row c gets cluster c: its blocks are cut into `cluster` equal
+    // contiguous pieces, CTA c * cluster + r takes piece r (the kernel combines the pieces through shared memory).
+    // ... and only while the longest row's piece is not much more than a balanced range would be: a step with a few
+    // very long rows is better cut into equal ranges over ALL CTAs, whose cross-CTA combine costs about as much as
+    // streaming kClusterSlackBlocks blocks.
+    const bool cluster_mode = cluster > 1 && mode == 1 && n_dec > 0 && n_dec * cluster <= base_ctas && n_dec <= kSmemRows &&
+                              dec_blocks <= cluster_blocks &&
+                              (max_nb + cluster - 1) / cluster <= dec_blocks / base_ctas + kClusterSlackBlocks;
+    const bool balanced = !cluster_mode && balance != 0 && n_dec <= kSmemRows &&
                           (mode == 2 || (balance >= 2 && 4LL * dec_blocks >= 3LL * n_dec * per));
     // small steps: a row of up to 2 * min_blocks blocks is never split (a cross-CTA combine costs more than it saves)
     const int no_split = mode == 2 ? 0 : 2 * min_blocks;
     __shared__ int cand_ok[64];
-    if (balanced) {
+    if (cluster_mode) {
+        for (int c = threadIdx.x; c <= decode_ctas; c += kPlanThreads) {
+            const int row = c / cluster, r = c - row * cluster;
+            int cut = dec_blocks;
+            if (row < n_dec) {
+                // pieces differ by at most one block and the empty ones (rows shorter than the cluster) come last, on
+                // the row's end: a CTA between two equal cuts never sits inside a row (the span logic below and the
+                // kernel's fallback to global partials rely on it)
+                const int start = ip[row], len = ip[row + 1] - start;
+                const int piece = len / cluster, extra = len - piece * cluster;
+                cut = start + r * piece + min(r, extra);
+            }
+            cuts_sm[c] = cut;
+            cta_start[c] = cut;
+        }
+    } else if (balanced) {
         if (threadIdx.x < 64) {
             const int T = per + (per * (int)threadIdx.x) / 32;
             int ctas = 0, cur = 0;
@@ -240,18 +271,22 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         hdr->n_seqs = n_seqs;
         hdr->block_size = block_size;
         hdr->mode = mode;
+        hdr->cluster = cluster_mode ? cluster : 0;
     }
 }
 
-void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance);      // c_api.cu: ns_set_tuning
+void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance, int* cluster_on,
+                int* cluster_blocks);      // c_api.cu: ns_set_tuning
 
 int launch_attn_plan(const int32_t* seq_lens, const int32_t* cu_seqlens, const int32_t* table_rows, int n_seqs,
                      int block_size, int base_ctas, int max_mode,
                      void* ws, const WsLayout& L, int max_items, cudaStream_t st) {
-    int min_blocks, split_blocks, snap_blocks, balance;
-    plan_knobs(&min_blocks, &split_blocks, &snap_blocks, &balance);
+    int min_blocks, split_blocks, snap_blocks, balance, cluster_on, cluster_blocks;
+    plan_knobs(&min_blocks, &split_blocks, &snap_blocks, &balance, &cluster_on, &cluster_blocks);
+    const int cluster = cluster_on ? plan_cluster(n_seqs, base_ctas) : 1;
     attn_plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, cu_seqlens, table_rows, n_seqs, block_size, base_ctas, max_mode,
-                                                 split_blocks, (uint8_t*)ws, L, max_items, min_blocks, snap_blocks, balance);
+                                                 split_blocks, (uint8_t*)ws, L, max_items, min_blocks, snap_blocks, balance,
+                                                 cluster, cluster_blocks);
     return check_launch("attn_plan");
 }
 

@@ -25,6 +25,9 @@ constexpr int kSplitBlocks = 15360;       // steps with more decode KV blocks th
                                           // SM is as fast or faster (32 rows x 500 tokens: 6.8 vs 12.1 us; 128 rows x 1400:
                                           // 17.3 vs 20.5; 48 rows x U[128,8192], 14.1K blocks: 24.2 vs 24.4); from ~16K blocks
                                           // two 8-warp halves win (256 rows x 1000: 23.6 vs 25.7; 27.5K blocks: 42.6 vs 44.4)
+constexpr int kClusterBlocks = 6144;      // steps with at most this many decode KV blocks (and few enough rows) run in cluster
+                                          // mode: every row gets a whole cluster of CTAs instead of one CTA
+constexpr int kClusterSlackBlocks = 48;   // cluster mode is kept while (longest row / cluster) <= balanced range + this many blocks
 constexpr int kSnapBlocks = 32;           // ranges up to twice this long per 8 warps may move a cut by half a range to
                                           // reach a row boundary (a whole row needs no partials); longer ranges by an eighth
 
@@ -39,7 +42,10 @@ struct PlanHeader {
     int32_t mode;           // 1: one range per decode CTA; 2: every decode CTA runs two virtual CTAs of half its warps
     int32_t errors;         // bounded waits of the attention kernels that ran out (cumulative; only the host clears it:
                             // the plan kernel leaves this word alone, the workspace starts zero-filled)
-    int32_t pad[7];
+    int32_t cluster;        // > 1: small step in cluster mode - decode row c is streamed by the `cluster` CTAs c*cluster ..
+                            // c*cluster + cluster - 1 (one thread-block cluster when the kernel is launched with that cluster
+                            // size), which combine through the first CTA's shared memory; 0: ranges as cut by the planner
+    int32_t pad[6];
 };
 
 // Byte offsets inside the workspace; everything 256-byte aligned.
@@ -56,6 +62,16 @@ struct WsLayout {
     int64_t partials;       // float[kMaxDecodeCtas*2][n_heads][head_dim+4]
     int64_t total;
 };
+
+// Cluster size proposed for a step of n_seqs sequences on a grid of `ctas` persistent decode CTAs: the largest of 4, 2
+// that divides the grid and leaves a cluster per sequence; 1 = none. The plan and the launch both derive it from the
+// same two numbers, which a CUDA graph fixes at capture.
+__host__ __device__ inline int plan_cluster(int n_seqs, int ctas) {
+    if (n_seqs <= 0) return 1;
+    if (ctas % 4 == 0 && n_seqs <= ctas / 4) return 4;
+    if (ctas % 2 == 0 && n_seqs <= ctas / 2) return 2;
+    return 1;
+}
 
 __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
@@ -106,6 +122,7 @@ struct AttnParams {
     // prefetching plan records, block ids and K/V tiles ahead of the wait. 0: the plan is older (an engine step plans
     // once, several kernels before the first layer's attention) and the early reads are safe.
     int plan_fresh = 0;
+    int n_seqs = 0;                // sequences of the call (sizes the thread-block cluster of small steps)
 };
 
 }  // namespace ns

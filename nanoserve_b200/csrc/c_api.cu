@@ -37,7 +37,7 @@ int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStr
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
 // Process-wide tuning knobs (ns_set_tuning); read on the host when a call is issued.
-static int g_tuning[NS_TUNE_COUNT] = {0, 1, -1, 0, 0, 2};
+static int g_tuning[NS_TUNE_COUNT] = {0, 1, -1, 0, 0, 2, 1, 0};
 // The workspace / stream of the newest ns_attn_plan issued by this thread that no attention call has used yet: the
 // first attention launch after a plan on the same stream is its direct successor and must not read the plan ahead of
 // its dependency wait (AttnParams::plan_fresh).
@@ -57,7 +57,11 @@ static int sm_count() {
 
 int device_sm_count() { return sm_count(); }
 
-void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance) {
+bool decode_cluster_enabled() { return g_tuning[NS_TUNE_DECODE_CLUSTER] != 0; }
+
+void plan_knobs(int* min_blocks, int* split_blocks, int* snap_blocks, int* balance, int* cluster_on, int* cluster_blocks) {
+    *cluster_on = g_tuning[NS_TUNE_DECODE_CLUSTER];
+    *cluster_blocks = g_tuning[NS_TUNE_DECODE_CLUSTER_BLOCKS] > 0 ? g_tuning[NS_TUNE_DECODE_CLUSTER_BLOCKS] : kClusterBlocks;
     *min_blocks = g_tuning[NS_TUNE_DECODE_MIN_BLOCKS] > 0 ? g_tuning[NS_TUNE_DECODE_MIN_BLOCKS] : kMinBlocksPerCta;
     *split_blocks = g_tuning[NS_TUNE_DECODE_SPLIT_BLOCKS] >= 0 ? g_tuning[NS_TUNE_DECODE_SPLIT_BLOCKS] : kSplitBlocks;
     *snap_blocks = g_tuning[NS_TUNE_DECODE_SNAP_BLOCKS] > 0 ? g_tuning[NS_TUNE_DECODE_SNAP_BLOCKS] : kSnapBlocks;
@@ -175,6 +179,7 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     a.timeline = g_timeline;
     const bool has_prefill = cu_seqlens != nullptr && n_tokens > n_seqs;
     a.overlap_prefill = (has_prefill && g_tuning[NS_TUNE_PREFILL_OVERLAP]) ? 1 : 0;
+    a.n_seqs = n_seqs;
     a.plan_fresh = (g_fresh_plan_ws == workspace && g_fresh_plan_stream == st) ? 1 : 0;
     g_fresh_plan_ws = nullptr;
     int rc = launch_paged_decode(a, head_dim, sms, st);

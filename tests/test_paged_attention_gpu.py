@@ -247,3 +247,32 @@ def test_prefill_beside_decode_equals_prefill_after_decode(n_heads, n_kv, hd):
             assert torch.equal(outs[0], outs[1]), c
     finally:
         hook(1)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", CONFIGS)
+@pytest.mark.parametrize("rows", [5, 32, 37, 38, 64, 74, 80])
+def test_decode_small_steps_in_cluster_mode_match_oracle(n_heads, n_kv, hd, rows):
+    """Small decode steps give every row a thread-block cluster of CTAs (4 up to 37 rows, 2 up to 74 on a 148-SM part)
+    whose pieces meet in the first CTA's shared memory. Rows of 1 block (most CTAs of the cluster idle), rows shorter
+    than the cluster, and ordinary serving-sized rows; with the mode on (default) and off (NS_TUNE_DECODE_CLUSTER = 0);
+    twice on one workspace; head layouts whose pieces do not fit the staging area fall back to the planner's ranges."""
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, paged_attention_decode
+    g = torch.Generator().manual_seed(rows * 131 + hd)
+    lens_list = torch.randint(1, 1300, (rows,), generator=g).tolist()
+    lens_list[0], lens_list[-1] = 1, 33
+    if rows > 2:
+        lens_list[1] = 16 * 3
+    q, k, v, tables, lens, _ = make_case(n_heads, n_kv, hd, lens_list, torch.bfloat16, seed=rows)
+    ref = O.paged_attention_decode(q.float(), k.float(), v.float(), tables, lens, hd ** -0.5)
+    args = dev(q, k, v, tables, lens)
+    try:
+        for on in (1, 0):
+            _lib.set_tuning(_lib.TUNE_DECODE_CLUSTER, on)
+            ws = AttnWorkspace(256, 256, n_heads, hd)
+            for _ in range(2):
+                out = paged_attention_decode(*args, hd ** -0.5, workspace=ws).float().cpu()
+                err = (out - ref).abs().max().item()
+                assert err <= 1e-2, (on, err)
+    finally:
+        _lib.set_tuning(_lib.TUNE_DECODE_CLUSTER, 1)
