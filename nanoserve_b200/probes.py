@@ -3,6 +3,7 @@
     python -m nanoserve_b200.probes --launch-probe          # 2 decode steps at c=32 + 1 mixed step inside a profiler range
     python -m nanoserve_b200.probes --layer-probe 32        # marginal cost of each kernel of a decode layer, 32 rows
     python -m nanoserve_b200.probes --attn-overlap-probe    # prefill kernel after / beside the decode kernel
+    python -m nanoserve_b200.probes --attn-alone-probe      # one decode attention call alone, cluster mode on / off
     python -m nanoserve_b200.probes --fused-ops 2048        # the token-wise fused ops at a 2048-token step, GB/s each
     python -m nanoserve_b200.probes --decode-step-probe qwen2.5-7b --rows 64 --layers 4    # decode steps of another shape
 
@@ -262,6 +263,57 @@ def fused_ops_probe(tokens: int, reps: int = 20) -> None:
     print(json.dumps(out))
 
 
+def attn_alone_probe() -> None:
+    """One decode attention call alone (14q/2kv heads, hd 64, bf16) for several step shapes, with small steps in cluster
+    mode (the default) and with one CTA per row (NS_TUNE_DECODE_CLUSTER = 0): 20 calls per CUDA graph, back to back and
+    serialised by a one-element fill kernel between calls (no part of a launch under its predecessor's tail; the fill's
+    share is NOT subtracted here)."""
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    res = {}
+    for rows, rng in ((32, (400, 600)), (32, (64, 1280)), (8, (400, 600)), (64, (400, 600)), (16, (1000, 3000))):
+        w = attention_workload(n_decode=rows, decode_range=rng, n_prefill=0, num_blocks=16384, seed=1)
+        for on in (1, 0):
+            _lib.set_tuning(_lib.TUNE_DECODE_CLUSTER, on)
+            ws = AttnWorkspace(64, 64, 14, 64)
+            ws.plan(w.seq_lens, None, rows, 16)
+            call = lambda: ragged_paged_attention(w.q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, None, 0.125,
+                                                  workspace=ws, planned=True)
+            for _ in range(3):
+                call()
+            flag = torch.zeros(1, device="cuda")
+            out = {}
+            for fill in (False, True):
+                def body():
+                    for _ in range(20):
+                        if fill:
+                            flag.zero_()
+                        call()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    body()
+                torch.cuda.current_stream().wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    body()
+                g.replay()
+                torch.cuda.synchronize()
+                ts = []
+                for _ in range(5):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    g.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    ts.append(a.elapsed_time(b) * 1e3 / 20)
+                out["serialised_us" if fill else "back_to_back_us"] = round(sorted(ts)[2], 2)
+            res[f"{rows} rows x U{list(rng)}, cluster mode {'on' if on else 'off'}"] = out
+    _lib.set_tuning(_lib.TUNE_DECODE_CLUSTER, 1)
+    print(json.dumps(res))
+
+
 def decode_step_probe(shape: str, rows: int, layers: int, ctx: int) -> None:
     """`rows` sequences of about `ctx` context tokens decoding on a random-init model of the named architecture (first
     `layers` layers), bf16: three decode steps inside a profiler range (cudaProfilerStart/Stop) for a launch list, then
@@ -304,6 +356,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--launch-probe", action="store_true")
     ap.add_argument("--attn-overlap-probe", action="store_true")
+    ap.add_argument("--attn-alone-probe", action="store_true")
     ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS")
     ap.add_argument("--fused-ops", type=int, default=0, metavar="TOKENS")
     ap.add_argument("--decode-step-probe", default="", metavar="SHAPE", help="e.g. qwen2.5-7b")
@@ -318,6 +371,8 @@ def main() -> None:
         layer_probe(args.layer_probe)
     elif args.attn_overlap_probe:
         attn_overlap_probe()
+    elif args.attn_alone_probe:
+        attn_alone_probe()
     elif args.fused_ops:
         fused_ops_probe(args.fused_ops)
     elif args.decode_step_probe:
