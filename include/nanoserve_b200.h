@@ -48,7 +48,8 @@ typedef enum {
     NS_TUNE_DECODE_BALANCE = 5,      /* 2 (default): row-aligned balanced cuts for large steps; 0: equal cuts snapped to rows */
     NS_TUNE_DECODE_CLUSTER = 6,      /* 1 (default): small decode steps give every row a thread-block cluster of CTAs; 0: off */
     NS_TUNE_DECODE_CLUSTER_BLOCKS = 7, /* decode KV blocks up to which a step may run in cluster mode; <= 0 (default): built-in */
-    NS_TUNE_COUNT = 8
+    NS_TUNE_PREFILL_CLUSTER = 8,     /* CTAs that share a prefill work item's key tiles: 1, 2 or 4; 0 (default): built-in (4 / 2) */
+    NS_TUNE_COUNT = 9
 } ns_tuning_knob;
 int ns_set_tuning(int knob, int value);
 int ns_get_tuning(int knob);

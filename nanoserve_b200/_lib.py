@@ -9,12 +9,17 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libnanoserve_b200.so"
+import os
+
+# NS_DEBUG_LIB=1 loads the -DNS_DEBUG_HOOKS build (python -m nanoserve_b200.build --debug-hooks) instead: the same
+# entry points plus the profiling hooks
+LIB_PATH = Path(__file__).resolve().parent / "lib" / ("libnanoserve_b200_dbg.so" if os.environ.get("NS_DEBUG_LIB") == "1"
+                                                      else "libnanoserve_b200.so")
 
 NS_BF16, NS_F32 = 0, 1
 # ns_tuning_knob
 (TUNE_PREFILL_IMPL, TUNE_PREFILL_OVERLAP, TUNE_DECODE_SPLIT_BLOCKS, TUNE_DECODE_MIN_BLOCKS, TUNE_DECODE_SNAP_BLOCKS,
- TUNE_DECODE_BALANCE, TUNE_DECODE_CLUSTER, TUNE_DECODE_CLUSTER_BLOCKS) = range(8)
+ TUNE_DECODE_BALANCE, TUNE_DECODE_CLUSTER, TUNE_DECODE_CLUSTER_BLOCKS, TUNE_PREFILL_CLUSTER) = range(9)
 
 # name -> (restype, argtypes); mirrors include/nanoserve_b200.h declaration by declaration.
 _P, _I32, _I64, _F = c_void_p, c_int32, c_int64, c_float

@@ -2,6 +2,7 @@
 
     python -m nanoserve_b200.build            # build if sources are newer than the library
     python -m nanoserve_b200.build --force
+    python -m nanoserve_b200.build --debug-hooks   # a second library with the profiling hooks (not loaded by default)
 
 The library is one C-ABI .so (include/nanoserve_b200.h); the Python package loads it with ctypes.
 """
@@ -37,15 +38,26 @@ def needs_build() -> bool:
     return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+DEBUG_LIB_PATH = LIB_DIR / "libnanoserve_b200_dbg.so"
+
+
+def build(force: bool = False, verbose: bool = False, debug_hooks: bool = False) -> Path:
+    """debug_hooks=True builds lib/libnanoserve_b200_dbg.so with -DNS_DEBUG_HOOKS: the same library plus the profiling
+    entry points (ns_debug_*: in-kernel time stamps) that the shipping library does not export. NS_DEBUG_LIB=1 makes
+    the Python binding load it."""
+    if debug_hooks:
+        return _build(DEBUG_LIB_PATH, PKG / "build_dbg", ["-DNS_DEBUG_HOOKS"], verbose)
     if not force and not needs_build():
         return LIB_PATH
+    return _build(LIB_PATH, PKG / "build", [], verbose)
+
+
+def _build(lib_path: Path, obj_dir: Path, extra_flags: list, verbose: bool) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     objs = []
     procs = []
-    obj_dir = PKG / "build"
     obj_dir.mkdir(exist_ok=True)
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + extra_flags
     for src in SOURCES:
         obj = obj_dir / (src[:-3] + ".o")
         cmd = [_nvcc(), *flags, "-Xcompiler", "-fPIC", "-c", str(CSRC / src), "-o", str(obj)]
@@ -63,12 +75,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(f"--- {src} ---\n{out}\n")
     if failed:
         raise RuntimeError("nvcc failed")
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    tmp = lib_path.with_suffix(".so.tmp")
     subprocess.run([_nvcc(), "-shared", "-o", str(tmp), *objs, "-lcudart_static", "-lpthread", "-ldl", "-lrt"], check=True)
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib_path)
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug_hooks="--debug-hooks" in sys.argv)
     print(path)

@@ -2,28 +2,35 @@
 //
 // Work item = (sequence, 16 query tokens, KV head): the 16 tokens x (up to 8) query heads of the GQA group form the
 // 128 rows of one UMMA tile (row r = token r/8, head r%8), so Q.K^T and P.V are dense 128-row contractions even
-// though each sequence contributes few tokens per head.
-//   S[128 x 64]  = Q[128 x 64] . K_tile[64 keys x 64]^T     tcgen05.mma kind::f16, A and B K-major, SWIZZLE_128B
-//   PV[128 x 64] = P[128 x 64 keys] . V_tile[64 keys x 64]  A K-major (P written to shared memory as bf16),
+// though each sequence contributes few tokens per head. head_dim HD = 64 or 128.
+//   S[128 x 64]  = Q[128 x HD] . K_tile[64 keys x HD]^T     tcgen05.mma kind::f16, A and B K-major, SWIZZLE_128B
+//   PV[128 x HD] = P[128 x 64 keys] . V_tile[64 keys x HD]  A K-major (P written to shared memory as bf16),
 //                                                            B MN-major (V rows are the pool's rows, untransposed)
-// Both accumulators live in TMEM (128 columns per CTA). After each MMA batch a tcgen05.commit arrives on an mbarrier;
-// every thread then reads ITS OWN row with tcgen05.ld (lane = row), so the online softmax needs no shuffles. The
-// running output is kept in registers and rescaled there, PV is accumulated fresh per tile.
-// K/V tiles (4 pool blocks of 16 tokens) are staged with 128-bit cp.async into the XOR-swizzled layout the
-// SWIZZLE_128B descriptors expect (16-byte chunk index ^ row%8, 1024-byte aligned tiles), double buffered.
-// Every mbarrier wait is bounded: on expiry the CTA records an error, skips its stores, frees its TMEM and returns.
+// Software pipeline over the key tiles (S, PV and P are double buffered; every thread owns one row, lane = row):
+//   iteration j:  issue S(j+1)  |  softmax(j) from tensor memory -> P(j) in shared memory  |  issue PV(j)
+//                 |  o = o * alpha(j-1) + PV(j-1)
+// so the tensor cores compute S(j+1) and PV(j-1) while the threads are in softmax(j), and the only exposed waits are
+// the first S and the last PV. One thread issues the MMAs with PRECOMPUTED descriptors (a tcgen05.mma of this size
+// occupies the tensor pipe for ~50 cycles; building two 64-bit descriptors per instruction in a lone thread cost
+// three times that). K/V tiles (4 pool blocks of 16 tokens) are staged by 128-bit cp.async into the XOR-swizzled
+// layout the SWIZZLE_128B descriptors expect (1024-byte aligned 128-byte-wide atoms; a 256-byte head row is two atoms),
+// K three tiles deep, V four (V(j) is still being read by PV(j) when K's buffer is already free). Tiles wholly below
+// every row's causal limit skip the mask. Every mbarrier wait is bounded: on expiry the CTA counts an error in the
+// plan header (ns_collect_status), skips its stores, frees its tensor memory and returns.
 #include "attn_plan.cuh"
 #include "common.cuh"
 
 namespace ns {
 
+int prefill_cluster_size();      // c_api.cu: NS_TUNE_PREFILL_CLUSTER (0 = built-in choice)
+
 namespace tc {
 
-constexpr int kRows = 128;          // UMMA M
+constexpr int kRows = 128;          // UMMA M = softmax threads (one per row)
+constexpr int kThreads = kRows + 32; // + one warp whose first lane issues every tcgen05.mma
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
-constexpr int kHD = 64;             // head_dim handled here
-constexpr int kTmemCols = 128;      // S: columns 0..63, PV: columns 64..127
-constexpr int kStages = 4;          // K/V tiles in shared memory: copies run kStages-1 tiles ahead of the tile in use
+constexpr int kStagesK = 3;         // K tiles in shared memory (copies run two tiles ahead of the tile in softmax)
+constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) while K(j)'s buffer is being refilled
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -44,9 +51,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
     return d;
 }
 
-// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = 64.
-__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kKeys >> 3) << 17) |
+// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(kRows >> 4) << 24);
 }
 
@@ -101,41 +108,57 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 
 }  // namespace tc
 
-__global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnParams p) {
+template <int HD>
+__global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_kernel(const AttnParams p) {
     using namespace tc;
+    constexpr int ATOMS = HD / 64;                  // 128-byte-wide swizzle atoms per head row
+    constexpr int Q_BYTES = kRows * 128 * ATOMS;    // [atom][128 rows][128 B]
+    constexpr int KV_BYTES = kKeys * 128 * ATOMS;   // [atom][64 keys][128 B]
+    constexpr int P_BYTES = kRows * 128;            // [128 rows][64 keys] bf16
+    constexpr uint32_t COL_S = 0, COL_PV = 2 * kKeys;            // tensor memory: S0, S1, PV0, PV1
+    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t mbar;
+    __shared__ __align__(8) uint64_t mbar[4];       // S0, S1, PV0, PV1
     __shared__ uint32_t tmem_slot;
-    __shared__ int failed;
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
-    if ((int)blockIdx.x >= hdr->n_prefill_items) {
+    // The CTAs of a thread-block cluster share one work item: rank r takes the r-th share of its key tiles and the shares
+    // meet in the first CTA's shared memory (an item's cost grows with its context: without the split the longest item
+    // alone set the kernel's duration).
+    uint32_t crank, csize;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
+    const int item_idx = (int)(blockIdx.x / csize);
+    if (item_idx >= hdr->n_prefill_items) {       // the whole cluster leaves together
         if (p.overlap_prefill) pdl_wait();        // the grid must not complete before the decode kernel it overlaps
         return;
     }
-    const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[blockIdx.x];
+    const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[item_idx];
     const int s = item.x, q_start = item.y, g = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5;
+    const bool worker = tid < kRows;              // one softmax thread per row; the fifth warp only issues the MMAs
+    const bool issuer = tid == kRows;
     const int q0 = p.cu_seqlens[s];
     const int T = p.cu_seqlens[s + 1] - q0;
     const int len = p.seq_lens[s];
     const int ctx = len - T;
     const int32_t* table = p.block_tables + (int64_t)(p.table_rows ? p.table_rows[s] : s) * p.table_stride;
     const int kv_end = min(len, ctx + q_start + kPrefillTileTokens);
-    const int n_tiles = (kv_end + kKeys - 1) / kKeys;
+    const int all_tiles = (kv_end + kKeys - 1) / kKeys;
+    const int tile0 = (int)(((long long)all_tiles * crank) / csize);              // this CTA's tiles: [tile0, tile0 + n_tiles)
+    const int n_tiles = (int)(((long long)all_tiles * (crank + 1)) / csize) - tile0;
 
-    // shared memory: 1024-byte aligned tiles (the swizzle pattern repeats every 8 rows x 128 bytes)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sK = sQ + kRows * 128, sV = sK + kStages * kKeys * 128, sP = sV + kStages * kKeys * 128;
-    const uint32_t mbar_s = smem_u32(&mbar);
+    const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + kStagesK * KV_BYTES, sP = sV + kStagesV * KV_BYTES;
+    const uint32_t bar_s0 = smem_u32(&mbar[0]), bar_pv0 = smem_u32(&mbar[2]);
 
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_s) : "memory");
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        failed = 0;
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -145,40 +168,39 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
     const uint32_t t_lane = tmem + ((uint32_t)(32 * warp) << 16);     // this warp's 32 lanes; lane = row
 
     // row of this thread
-    const int tok = q_start + (tid >> 3), hh = tid & 7;
-    const bool row_ok = tok < T && hh < p.group;
+    const int tok = q_start + ((tid & (kRows - 1)) >> 3), hh = tid & 7;
+    const bool row_ok = worker && tok < T && hh < p.group;
     const int h = g * p.group + hh;
 
-    // Q tile: one 128-byte row per thread
-    {
-        const __nv_bfloat16* src = p.q + (int64_t)(q0 + (row_ok ? tok : 0)) * p.q_stride + (int64_t)(row_ok ? h : 0) * kHD;
+    // Q tile: one head row per thread, 128 bytes per atom
+    if (worker) {
+        const __nv_bfloat16* src = p.q + (int64_t)(q0 + (row_ok ? tok : 0)) * p.q_stride + (int64_t)(row_ok ? h : 0) * HD;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            cp_async16(sQ + tid * 128 + ((c ^ (tid & 7)) << 4), src + c * 8, row_ok ? 16 : 0);
+        for (int c = 0; c < 8 * ATOMS; ++c)
+            cp_async16(sQ + (c >> 3) * (kRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4), src + c * 8, row_ok ? 16 : 0);
     }
-    // Block ids of a tile: its 64 keys are 4 pool blocks, the same 4 for every thread (row = it*16 + tid/8). They are
-    // fetched ONE TILE AHEAD of the copies that need them, so no copy waits on a dependent table load (measured: ~500 of
-    // a tile's ~3600 cycles before this).
+    // Block ids of a tile: its 64 keys are 4 pool blocks, the same 4 for every thread. They are fetched one tile ahead of
+    // the copies that need them, so no copy waits on a dependent table load.
     int blk_next[kKeys / 16];
     auto fetch_ids = [&](int kt) {
 #pragma unroll
         for (int it = 0; it < kKeys / 16; ++it) {
-            const int key0 = kt * kKeys + it * 16;
-            blk_next[it] = (kt < n_tiles && key0 < len) ? table[key0 >> 4] : 0;
+            const int key0 = (tile0 + kt) * kKeys + it * 16;
+            blk_next[it] = (worker && kt < n_tiles && key0 < len) ? table[key0 >> 4] : 0;
         }
     };
     auto load_kv = [&](int kt) {                    // uses blk_next (the ids of tile kt), then fetches those of tile kt + 1
-        if (kt < n_tiles) {
-            const uint32_t ks = sK + (kt % kStages) * kKeys * 128, vs = sV + (kt % kStages) * kKeys * 128;
+        if (worker && kt < n_tiles) {
+            const uint32_t ks = sK + (kt % kStagesK) * KV_BYTES, vs = sV + (kt % kStagesV) * KV_BYTES;
 #pragma unroll
-            for (int it = 0; it < (kKeys * 8) / kRows; ++it) {
-                const int qd = it * kRows + tid;
-                const int row = qd >> 3, c = qd & 7;               // row >> 4 == it
-                const int key = kt * kKeys + row;
+            for (int it = 0; it < (kKeys * 8 * ATOMS) / kRows; ++it) {
+                const int qd = it * kRows + tid;                   // 16-byte chunk of the tile
+                const int row = qd / (8 * ATOMS), c = qd % (8 * ATOMS);
+                const int key = (tile0 + kt) * kKeys + row;
                 const bool ok = key < len;
-                const int64_t goff = (int64_t)blk_next[it] * p.blk_stride + (int64_t)(key & 15) * p.pos_stride +
+                const int64_t goff = (int64_t)blk_next[row >> 4] * p.blk_stride + (int64_t)(key & 15) * p.pos_stride +
                                      (int64_t)g * p.head_stride + c * 8;
-                const uint32_t off = row * 128 + ((c ^ (row & 7)) << 4);
+                const uint32_t off = (c >> 3) * (kKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
                 cp_async16(ks + off, p.k_pool + goff, ok ? 16 : 0);
                 cp_async16(vs + off, p.v_pool + goff, ok ? 16 : 0);
             }
@@ -186,59 +208,121 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
         cp_async_commit();
         fetch_ids(kt + 1);
     };
-    static_assert((kKeys * 8) / kRows == kKeys / 16, "one pool block per copy iteration");
     fetch_ids(0);
     load_kv(0);                       // group 0 = Q + tile 0
-#pragma unroll
-    for (int t = 1; t < kStages - 1; ++t) load_kv(t);
+    load_kv(1);
 
-    constexpr uint32_t idesc_s = instr_desc(false), idesc_pv = instr_desc(true);
-    float o[kHD];
+    // descriptors, built once: an instruction's operand is the base plus a byte offset (>> 4) in the address field
+    constexpr uint32_t idesc_s = instr_desc(false, kKeys), idesc_pv = instr_desc(true, HD);
+    const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
+    const uint64_t dP = smem_desc(sP, 16, 1024);
+    const uint64_t dV = smem_desc(sV, kKeys * 128, 1024);          // MN-major B: next 64-column atom kKeys * 128 bytes on
+    auto issue_s = [&](int kt) {                                    // S(kt) = Q . K(kt)^T into S buffer kt & 1
+        const uint64_t k0 = dK + (uint64_t)(((kt % kStagesK) * KV_BYTES) >> 4);
+        const uint32_t d = tmem + COL_S + (uint32_t)((kt & 1) * kKeys);
 #pragma unroll
-    for (int d = 0; d < kHD; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    uint32_t phase = 0;
+        for (int kk = 0; kk < HD / 16; ++kk) {                      // K extent 16 per instruction = 32 bytes inside an atom
+            const uint32_t a_off = (uint32_t)(((kk >> 2) * (kRows * 128) + (kk & 3) * 32) >> 4);
+            const uint32_t b_off = (uint32_t)(((kk >> 2) * (kKeys * 128) + (kk & 3) * 32) >> 4);
+            mma_f16(d, dQ + a_off, k0 + b_off, idesc_s, kk > 0);
+        }
+        mma_commit(bar_s0 + 8 * (kt & 1));
+    };
+    auto issue_pv = [&](int kt) {                                   // PV(kt) = P(kt) . V(kt) into PV buffer kt & 1
+        const uint64_t p0 = dP + (uint64_t)(((kt & 1) * P_BYTES) >> 4);
+        const uint64_t v0 = dV + (uint64_t)(((kt % kStagesV) * KV_BYTES) >> 4);
+        const uint32_t d = tmem + COL_PV + (uint32_t)((kt & 1) * HD);
+#pragma unroll
+        for (int kk = 0; kk < kKeys / 16; ++kk)                     // 16 keys per instruction: 32 bytes of P, 16 rows of V
+            mma_f16(d, p0 + (uint32_t)((kk * 32) >> 4), v0 + (uint32_t)((kk * 2048) >> 4), idesc_pv, kk > 0);
+        mma_commit(bar_pv0 + 8 * (kt & 1));
+    };
+
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
     const int limit = ctx + tok;      // last key this row may see
     bool ok = true;
 
-    for (int kt = 0; kt < n_tiles && ok; ++kt) {
-        load_kv(kt + kStages - 1);                                     // into the buffer tile kt-1 has left
-        cp_async_wait<kStages - 1>();                                  // tile kt (and Q) landed for this thread
+    auto accumulate = [&](int kt, float alpha) {                    // o = o * alpha + PV(kt)
+        if (!mbar_wait(bar_pv0 + 8 * (kt & 1), (uint32_t)((kt >> 1) & 1))) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t src = t_lane + COL_PV + (uint32_t)((kt & 1) * HD);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            float v[32];
+            tmem_ld32(src + 32 * c, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], alpha, v[i]);
+        }
+    };
+
+    // prologue: tile 0 (and Q) in shared memory, S(0) under way
+    cp_async_wait<1>();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (issuer && n_tiles > 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0);
+    }
+
+#ifdef NS_DEBUG_HOOKS
+    // profiling build: clock64 stamps of the first work item's thread 0, 8 per key tile, first 16 tiles
+    long long* stamps = (p.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) ? p.timeline : nullptr;
+#define NS_STAMP(i) do { if (stamps != nullptr && kt < 16) stamps[kt * 8 + (i)] = clock64(); } while (0)
+#else
+#define NS_STAMP(i) do { } while (0)
+#endif
+    for (int kt = 0; kt < n_tiles; ++kt) {
+        NS_STAMP(0);
+        load_kv(kt + 2);                                               // K into the buffer S(kt-1) has left, V into PV(kt-2)'s
+        cp_async_wait<1>();                                            // tiles <= kt + 1 landed for this thread
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        const uint32_t ks = sK + (kt % kStages) * kKeys * 128, vs = sV + (kt % kStages) * kKeys * 128;
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kk = 0; kk < kHD / 16; ++kk)                      // K extent 16 per instruction = 32 bytes
-                mma_f16(tmem, smem_desc(sQ + kk * 32, 16, 1024), smem_desc(ks + kk * 32, 16, 1024), idesc_s, kk > 0);
-            mma_commit(mbar_s);
-        }
-        if (!mbar_wait(mbar_s, phase)) { ok = false; }
-        phase ^= 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        NS_STAMP(1);
         ok = __syncthreads_and(ok);
         if (!ok) break;
+        NS_STAMP(2);
+        if (issuer && kt + 1 < n_tiles) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(kt + 1);                                           // runs while this tile is in the softmax
+        }
+        float alpha = 1.f;
+        if (worker) {
+        if (!mbar_wait(bar_s0 + 8 * (kt & 1), (uint32_t)((kt >> 1) & 1))) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        NS_STAMP(3);
 
         // ---- online softmax on this thread's row ---------------------------------------------------------------
         float sc[kKeys];
         {
             float lo[32], hi[32];
-            tmem_ld32(t_lane, lo);
-            tmem_ld32(t_lane + 32, hi);
+            const uint32_t src = t_lane + COL_S + (uint32_t)((kt & 1) * kKeys);
+            tmem_ld32(src, lo);
+            tmem_ld32(src + 32, hi);
 #pragma unroll
             for (int i = 0; i < 32; ++i) { sc[i] = lo[i]; sc[32 + i] = hi[i]; }
         }
+        NS_STAMP(4);
         float mx = -INFINITY;
+        if ((tile0 + kt) * kKeys + kKeys - 1 <= ctx + q_start) {       // every row of the tile sees every key of it
 #pragma unroll
-        for (int c = 0; c < kKeys; ++c) {
-            const int key = kt * kKeys + c;
-            sc[c] = key <= limit ? sc[c] * p.scale_log2 : -INFINITY;
-            mx = fmaxf(mx, sc[c]);
+            for (int c = 0; c < kKeys; ++c) {
+                sc[c] *= p.scale_log2;
+                mx = fmaxf(mx, sc[c]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < kKeys; ++c) {
+                const int key = (tile0 + kt) * kKeys + c;
+                sc[c] = key <= limit ? sc[c] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, sc[c]);
+            }
         }
         const float m_new = fmaxf(m_run, mx);                          // key 0 is visible to every row: finite
-        const float alpha = ex2(m_run - m_new);
+        alpha = ex2(m_run - m_new);
         float psum = 0.f;
 #pragma unroll
         for (int c = 0; c < kKeys; ++c) {
@@ -247,9 +331,8 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
         }
         l_run = fmaf(l_run, alpha, psum);
         m_run = m_new;
-#pragma unroll
-        for (int d = 0; d < kHD; ++d) o[d] *= alpha;
         // P row as bf16 into shared memory (K-major, swizzled like the other operands)
+        const uint32_t p_dst = sP + (kt & 1) * P_BYTES + tid * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             uint4 v;
@@ -257,40 +340,75 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
             v.y = pack_bf16x2(sc[8 * c + 2], sc[8 * c + 3]);
             v.z = pack_bf16x2(sc[8 * c + 4], sc[8 * c + 5]);
             v.w = pack_bf16x2(sc[8 * c + 6], sc[8 * c + 7]);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + tid * 128 + ((c ^ (tid & 7)) << 4)), "r"(v.x),
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_dst + ((c ^ (tid & 7)) << 4)), "r"(v.x),
                          "r"(v.y), "r"(v.z), "r"(v.w)
                          : "memory");
         }
+        }
+        NS_STAMP(5);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kk = 0; kk < kKeys / 16; ++kk)                    // 16 keys per instruction: 32 bytes of P, 16 rows of V
-                mma_f16(tmem + 64, smem_desc(sP + kk * 32, 16, 1024), smem_desc(vs + kk * 2048, 1024, 1024), idesc_pv, kk > 0);
-            mma_commit(mbar_s);
-        }
-        if (!mbar_wait(mbar_s, phase)) { ok = false; }
-        phase ^= 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         ok = __syncthreads_and(ok);
         if (!ok) break;
-        {
-            float lo[32], hi[32];
-            tmem_ld32(t_lane + 64, lo);
-            tmem_ld32(t_lane + 96, hi);
+        if (issuer) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_pv(kt);
+        }
+        NS_STAMP(6);
+        if (worker && kt > 0) accumulate(kt - 1, alpha_prev);          // PV(kt-1) ran under this tile's softmax
+        alpha_prev = alpha;
+        NS_STAMP(7);
+    }
+    if (ok && worker && n_tiles > 0) accumulate(n_tiles - 1, alpha_prev);
+    cp_async_wait<0>();
+    ok = __syncthreads_and(ok);
+
+    if (csize > 1) {
+        // every CTA of the cluster is through its tiles: the first CTA's shared memory is free to receive the others'
+        // (o, m, l) rows, one row per thread, HD + 4 floats apart
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        constexpr int PART_ROW = HD + 4;
+        if (crank != 0 && worker) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(base));
+            uint64_t generic;
+            asm volatile("cvta.shared::cluster.u64 %0, %1;" : "=l"(generic) : "l"((uint64_t)remote));
+            float* dst = reinterpret_cast<float*>(generic) + ((size_t)(crank - 1) * kRows + tid) * PART_ROW;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { o[i] += lo[i]; o[32 + i] += hi[i]; }
+            for (int c = 0; c < HD / 4; ++c)
+                *reinterpret_cast<float4*>(dst + 4 * c) = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            *reinterpret_cast<float2*>(dst + HD) = make_float2(m_run, l_run);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (crank == 0 && worker) {
+            const float* mine = reinterpret_cast<const float*>(smem_raw + (base - smem_u32(smem_raw)));
+            for (uint32_t r = 1; r < csize; ++r) {
+                const float* src = mine + ((size_t)(r - 1) * kRows + tid) * PART_ROW;
+                const float2 ml = *reinterpret_cast<const float2*>(src + HD);
+                const float m_new = fmaxf(m_run, ml.x);
+                if (m_new == -INFINITY) continue;
+                const float wa = ex2(m_run - m_new), wb = ex2(ml.x - m_new);
+#pragma unroll
+                for (int c = 0; c < HD / 4; ++c) {
+                    const float4 v = *reinterpret_cast<const float4*>(src + 4 * c);
+                    o[4 * c] = fmaf(o[4 * c], wa, v.x * wb);
+                    o[4 * c + 1] = fmaf(o[4 * c + 1], wa, v.y * wb);
+                    o[4 * c + 2] = fmaf(o[4 * c + 2], wa, v.z * wb);
+                    o[4 * c + 3] = fmaf(o[4 * c + 3], wa, v.w * wb);
+                }
+                l_run = fmaf(l_run, wa, ml.y * wb);
+                m_run = m_new;
+            }
         }
     }
-    cp_async_wait<0>();
 
-    if (ok && row_ok) {
+    if (ok && row_ok && crank == 0) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = p.out + (int64_t)(q0 + tok) * p.out_stride + (int64_t)h * kHD;
+        __nv_bfloat16* dst = p.out + (int64_t)(q0 + tok) * p.out_stride + (int64_t)h * HD;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < HD / 8; ++c) {
             uint4 v;
             v.x = pack_bf16x2(o[8 * c + 0] * inv, o[8 * c + 1] * inv);
             v.y = pack_bf16x2(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
@@ -304,34 +422,52 @@ __global__ void __launch_bounds__(tc::kRows, 2) prefill_tc_kernel(const AttnPara
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     if (p.overlap_prefill) pdl_wait();            // complete only after the decode kernel this one ran beside
 }
 
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size) {
     if (block_size != 16 || n_heads % n_kv_heads != 0) return false;
     const int group = n_heads / n_kv_heads;
-    return group >= 1 && group <= 8 && head_dim == tc::kHD;
+    return group >= 1 && group <= 8 && (head_dim == 64 || head_dim == 128);
 }
 
-int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st) {
-    if (max_items <= 0) return NS_OK;
-    constexpr int smem = (tc::kRows + 2 * tc::kStages * tc::kKeys + tc::kRows) * 128 + 1024;
+template <int HD>
+static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t st) {
+    constexpr int atoms = HD / 64;
+    constexpr int smem = tc::kRows * 128 * atoms + (tc::kStagesK + tc::kStagesV) * tc::kKeys * 128 * atoms + 2 * tc::kRows * 128 + 1024;
     static SmemOptIn optin;
     if (optin.needs((size_t)smem)) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): cannot reserve %d bytes of shared memory: %s",
                                           smem, cudaGetErrorString(e));
         optin.done((size_t)smem);
     }
-    dim3 grid((unsigned)max_items, (unsigned)p.n_kv_heads);
-    if (p.overlap_prefill) {
-        cudaError_t e = launch_pdl(prefill_tc_kernel, grid, dim3(tc::kRows), (size_t)smem, st, p);
-        if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): launch failed: %s", cudaGetErrorString(e));
-        return NS_OK;
-    }
-    prefill_tc_kernel<<<grid, tc::kRows, smem, st>>>(p);
-    return check_launch("prefill_tc");
+    // every work item is shared by a cluster of CTAs that split its key tiles (4 for head_dim 64; 2 for 128, whose rows of
+    // 132 floats from three other CTAs would not fit the first CTA's shared memory)
+    const int cl = prefill_cluster_size() > 0 ? prefill_cluster_size() : (HD == 64 ? 4 : 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(max_items * cl), (unsigned)p.n_kv_heads);
+    cfg.blockDim = dim3(tc::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.overlap_prefill ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_tc_kernel<HD>, p);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): launch failed: %s", cudaGetErrorString(e));
+    return NS_OK;
+}
+
+int launch_prefill_tc(const AttnParams& p, int head_dim, int max_items, cudaStream_t st) {
+    if (max_items <= 0) return NS_OK;
+    return head_dim == 64 ? launch_prefill_tc_hd<64>(p, max_items, st) : launch_prefill_tc_hd<128>(p, max_items, st);
 }
 
 }  // namespace ns

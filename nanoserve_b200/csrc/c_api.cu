@@ -35,9 +35,9 @@ int decode_max_mode(int head_dim);
 bool prefill_mma_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
 int launch_prefill_mma(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
 bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_size);
-int launch_prefill_tc(const AttnParams& p, int max_items, cudaStream_t st);
+int launch_prefill_tc(const AttnParams& p, int head_dim, int max_items, cudaStream_t st);
 // Process-wide tuning knobs (ns_set_tuning); read on the host when a call is issued.
-static int g_tuning[NS_TUNE_COUNT] = {0, 1, -1, 0, 0, 2, 1, 0};
+static int g_tuning[NS_TUNE_COUNT] = {0, 1, -1, 0, 0, 2, 1, 0, 0};
 // The workspace / stream of the newest ns_attn_plan issued by this thread that no attention call has used yet: the
 // first attention launch after a plan on the same stream is its direct successor and must not read the plan ahead of
 // its dependency wait (AttnParams::plan_fresh).
@@ -56,6 +56,11 @@ static int sm_count() {
 }
 
 int device_sm_count() { return sm_count(); }
+
+int prefill_cluster_size() {
+    const int v = g_tuning[NS_TUNE_PREFILL_CLUSTER];
+    return (v == 1 || v == 2 || v == 4) ? v : 0;
+}
 
 bool decode_cluster_enabled() { return g_tuning[NS_TUNE_DECODE_CLUSTER] != 0; }
 
@@ -190,7 +195,7 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
         const int64_t cap = (int64_t)ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
         if (max_items > cap) max_items = cap;
         if (g_tuning[NS_TUNE_PREFILL_IMPL] == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size))
-            rc = launch_prefill_tc(a, (int)max_items, st);
+            rc = launch_prefill_tc(a, head_dim, (int)max_items, st);
         else
             rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
     }
