@@ -75,6 +75,20 @@ int ns_check_step_metadata(const int32_t* block_tables, const int32_t* table_row
                            const int64_t* positions, const int64_t* tokens, int32_t n_seqs, int64_t n_tokens,
                            int32_t num_blocks, int32_t block_size, int32_t vocab, void* stream);
 
+/* Tensor parallelism: all-reduce (sum) of every rank's partial [rows, hidden] bf16, fused with what follows it at both
+ * sites of a layer: x_out = residual + sum (rounded), h_out = weight * rmsnorm(x_out). peer_partials[w] / peer_flags[w]
+ * are HOST arrays of `world` device pointers as mapped in the calling process: rank w's partial for THIS call (written
+ * by the kernel before this one on rank w's stream) and rank w's flag array (world x uint32, zero at start, peer
+ * mapped). state: 2 x uint32 of this rank, zero at start. Every rank makes the same sequence of calls; callers alternate
+ * two partial buffers from call to call. The kernel announces its partial to the peers, waits (bounded, on local
+ * memory) for theirs, and reads them with ordinary loads over NVLink in rank order, so the result is bitwise equal on
+ * every rank. world 2, 4 or 8; hidden % 8 == 0, <= 4096; bf16. A wait that runs out is counted in ns_collect_status.
+ * Replaces: torch.distributed.all_reduce + the add + RMSNorm after it at the all-reduce sites nanoserve/model.py:256-257
+ * (the reference lists tensor parallelism and this fusion as not implemented, README.md:252-254). */
+int ns_tp_allreduce_add_rmsnorm(const void* const* peer_partials, void* const* peer_flags, void* state,
+                                const void* residual, const void* weight, void* out_h, void* out_x, int64_t rows,
+                                int32_t hidden, float eps, int32_t rank, int32_t world, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused token-wise ops.
  * ---------------------------------------------------------------------------------------------- */

@@ -30,6 +30,7 @@ SIGNATURES: dict[str, tuple] = {
     "ns_set_tuning": (c_int, [c_int, c_int]),
     "ns_get_tuning": (c_int, [c_int]),
     "ns_collect_status": (c_int, [_P, _P, _P]),
+    "ns_tp_allreduce_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _F, _I32, _I32, _P]),
     "ns_check_step_metadata": (c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P]),
     "ns_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, _F, c_int, _P]),
     "ns_silu_mul": (c_int, [_P, _P, _I64, _I32, c_int, _P]),

@@ -19,7 +19,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libnanoserve_b200.so"
 SOURCES = ["c_api.cu", "fused_ops.cu", "attn_plan.cu", "attn_decode.cu", "attn_decode_static.cu", "attn_prefill_mma.cu", "attn_prefill_tc.cu", "attn_simple.cu",
-           "metadata.cu", "sampling.cu", "skinny_gemm.cu", "thin_gemm.cu", "stream_gemm.cu", "umma_gemm.cu"]
+           "metadata.cu", "sampling.cu", "skinny_gemm.cu", "thin_gemm.cu", "stream_gemm.cu", "umma_gemm.cu", "tp_allreduce.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false"]
 
 

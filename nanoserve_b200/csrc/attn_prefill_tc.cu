@@ -32,6 +32,7 @@ constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P
 constexpr int kStagesK = 3;         // K tiles in shared memory (copies run two tiles ahead of the tile in softmax)
 constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) while K(j)'s buffer is being refilled
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kDefaultCluster = 1;  // CTAs sharing one work item's key tiles (see launch_prefill_tc_hd)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -295,55 +296,59 @@ __global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_ker
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         NS_STAMP(3);
 
-        // ---- online softmax on this thread's row ---------------------------------------------------------------
-        float sc[kKeys];
-        {
-            float lo[32], hi[32];
-            const uint32_t src = t_lane + COL_S + (uint32_t)((kt & 1) * kKeys);
-            tmem_ld32(src, lo);
-            tmem_ld32(src + 32, hi);
+        // ---- online softmax on this thread's row: two passes over the 64 scores in tensor memory, 32 columns at a time
+        // (registers hold the running output; a second read of S is cheaper than spilling). Four independent chains for
+        // the maximum and for the sum; the softmax scale is folded into the exponent's multiply-add.
+        const uint32_t s_src = t_lane + COL_S + (uint32_t)((kt & 1) * kKeys);
+        const bool masked = (tile0 + kt) * kKeys + kKeys - 1 > ctx + q_start;    // else every row sees every key of the tile
+        const int key_base = (tile0 + kt) * kKeys;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { sc[i] = lo[i]; sc[32 + i] = hi[i]; }
+        for (int hf = 0; hf < 2; ++hf) {
+            float v[32];
+            tmem_ld32(s_src + 32 * hf, v);
+            if (masked) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (key_base + 32 * hf + i > limit) v[i] = -INFINITY;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
         }
         NS_STAMP(4);
-        float mx = -INFINITY;
-        if ((tile0 + kt) * kKeys + kKeys - 1 <= ctx + q_start) {       // every row of the tile sees every key of it
-#pragma unroll
-            for (int c = 0; c < kKeys; ++c) {
-                sc[c] *= p.scale_log2;
-                mx = fmaxf(mx, sc[c]);
-            }
-        } else {
-#pragma unroll
-            for (int c = 0; c < kKeys; ++c) {
-                const int key = (tile0 + kt) * kKeys + c;
-                sc[c] = key <= limit ? sc[c] * p.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, sc[c]);
-            }
-        }
-        const float m_new = fmaxf(m_run, mx);                          // key 0 is visible to every row: finite
-        alpha = ex2(m_run - m_new);
-        float psum = 0.f;
-#pragma unroll
-        for (int c = 0; c < kKeys; ++c) {
-            sc[c] = ex2(sc[c] - m_new);
-            psum += sc[c];
-        }
-        l_run = fmaf(l_run, alpha, psum);
-        m_run = m_new;
-        // P row as bf16 into shared memory (K-major, swizzled like the other operands)
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        const float m_new = fmaxf(m_run, mx);
+        // a CTA that holds only late tiles of its item can meet rows that see none of its keys yet
+        const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+        alpha = ex2(m_run - m_ref);
+        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t p_dst = sP + (kt & 1) * P_BYTES + tid * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(sc[8 * c + 0], sc[8 * c + 1]);
-            v.y = pack_bf16x2(sc[8 * c + 2], sc[8 * c + 3]);
-            v.z = pack_bf16x2(sc[8 * c + 4], sc[8 * c + 5]);
-            v.w = pack_bf16x2(sc[8 * c + 6], sc[8 * c + 7]);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_dst + ((c ^ (tid & 7)) << 4)), "r"(v.x),
-                         "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
+        for (int hf = 0; hf < 2; ++hf) {
+            float v[32];
+            tmem_ld32(s_src + 32 * hf, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float e = ex2(fmaf(v[i], p.scale_log2, -m_ref));
+                if (masked && key_base + 32 * hf + i > limit) e = 0.f;
+                v[i] = e;
+                ps4[i & 3] += e;
+            }
+            // P row as bf16 into shared memory (K-major, swizzled like the other operands)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint4 pk;
+                pk.x = pack_bf16x2(v[8 * c + 0], v[8 * c + 1]);
+                pk.y = pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
+                pk.z = pack_bf16x2(v[8 * c + 4], v[8 * c + 5]);
+                pk.w = pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_dst + (((4 * hf + c) ^ (tid & 7)) << 4)),
+                             "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                             : "memory");
+            }
         }
+        l_run = fmaf(l_run, alpha, (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+        m_run = m_new;
         }
         NS_STAMP(5);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -443,9 +448,10 @@ static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t
                                           smem, cudaGetErrorString(e));
         optin.done((size_t)smem);
     }
-    // every work item is shared by a cluster of CTAs that split its key tiles (4 for head_dim 64; 2 for 128, whose rows of
-    // 132 floats from three other CTAs would not fit the first CTA's shared memory)
-    const int cl = prefill_cluster_size() > 0 ? prefill_cluster_size() : (HD == 64 ? 4 : 2);
+    // a work item's key tiles can be shared by a cluster of CTAs (NS_TUNE_PREFILL_CLUSTER); clamped to what fits: the
+    // other CTAs' rows of HD + 4 floats land in the first CTA's shared memory
+    int cl = prefill_cluster_size() > 0 ? prefill_cluster_size() : tc::kDefaultCluster;
+    while (cl > 1 && (cl - 1) * tc::kRows * (HD + 4) * 4 > smem - 1024) cl >>= 1;     // the other CTAs' rows must fit the first one's
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(max_items * cl), (unsigned)p.n_kv_heads);
     cfg.blockDim = dim3(tc::kThreads);

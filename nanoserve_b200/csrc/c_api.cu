@@ -231,23 +231,25 @@ int thin_gemm_error_counter(const unsigned int** out);
 int umma_gemm_error_counter(const unsigned int** out);
 int skinny_gemm_error_counter(const unsigned int** out);
 int check_error_counter(const unsigned int** out);
+int tp_error_counter(const unsigned int** out);
 
 __global__ void collect_status_kernel(const unsigned int* a, const unsigned int* b, const unsigned int* c, const unsigned int* d,
-                                      const unsigned int* e, const int32_t* ws_errors,
+                                      const unsigned int* e, const unsigned int* f, const int32_t* ws_errors,
                                       int64_t* out) {
     if (threadIdx.x == 0)
-        *out = (int64_t)*a + (int64_t)*b + (int64_t)*c + (int64_t)*d + (int64_t)*e + (ws_errors != nullptr ? (int64_t)*ws_errors : 0);
+        *out = (int64_t)*a + (int64_t)*b + (int64_t)*c + (int64_t)*d + (int64_t)*e + (int64_t)*f + (ws_errors != nullptr ? (int64_t)*ws_errors : 0);
 }
 }  // namespace ns
 
 extern "C" int ns_collect_status(const void* attn_workspace, int64_t* status, void* stream) {
     NS_REQUIRE(status != nullptr, NS_ERR_INVALID_ARG, "collect_status: null pointer");
-    const unsigned int *a = nullptr, *b = nullptr, *c = nullptr, *d = nullptr, *e = nullptr;
+    const unsigned int *a = nullptr, *b = nullptr, *c = nullptr, *d = nullptr, *e = nullptr, *f = nullptr;
     int rc = thin_gemm_error_counter(&a);
     if (rc == NS_OK) rc = stream_gemm_error_counter(&b);
     if (rc == NS_OK) rc = umma_gemm_error_counter(&c);
     if (rc == NS_OK) rc = skinny_gemm_error_counter(&d);
     if (rc == NS_OK) rc = check_error_counter(&e);
+    if (rc == NS_OK) rc = tp_error_counter(&f);
     if (rc != NS_OK) return rc;
     const int32_t* ws_errors = nullptr;
     if (attn_workspace != nullptr) {
@@ -255,6 +257,6 @@ extern "C" int ns_collect_status(const void* attn_workspace, int64_t* status, vo
         const WsLayout L = ws_layout(1, 1, 1, 1);
         ws_errors = &reinterpret_cast<const PlanHeader*>(static_cast<const uint8_t*>(attn_workspace) + L.header)->errors;
     }
-    collect_status_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a, b, c, d, e, ws_errors, status);
+    collect_status_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a, b, c, d, e, f, ws_errors, status);
     return check_launch("collect_status");
 }
