@@ -89,6 +89,18 @@ int ns_tp_allreduce_add_rmsnorm(const void* const* peer_partials, void* const* p
                                 const void* residual, const void* weight, void* out_h, void* out_x, int64_t rows,
                                 int32_t hidden, float eps, int32_t rank, int32_t world, void* stream);
 
+/* Set-up of the peer-visible buffers of ns_tp_allreduce_add_rmsnorm. The ONLY entry points of this library that
+ * allocate, map or free device memory; they belong to start-up and shutdown, never to a step or a stream capture.
+ * ns_peer_alloc: cudaMalloc + zero fill on the current device. ns_peer_export: a 64-byte handle of such an allocation
+ * for other processes on this machine. ns_peer_open (in another process, its own GPU current): maps the allocation and
+ * enables peer access to the exporting GPU; the pointer is valid in kernels of the opening process. ns_peer_close /
+ * ns_peer_free undo them. No counterpart in the reference (single GPU). */
+int ns_peer_alloc(int64_t bytes, void** ptr);
+int ns_peer_free(void* ptr);
+int ns_peer_export(void* ptr, void* handle64);
+int ns_peer_open(const void* handle64, void** ptr);
+int ns_peer_close(void* ptr);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused token-wise ops.
  * ---------------------------------------------------------------------------------------------- */

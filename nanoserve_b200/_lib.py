@@ -31,6 +31,11 @@ SIGNATURES: dict[str, tuple] = {
     "ns_get_tuning": (c_int, [c_int]),
     "ns_collect_status": (c_int, [_P, _P, _P]),
     "ns_tp_allreduce_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _F, _I32, _I32, _P]),
+    "ns_peer_alloc": (c_int, [_I64, _P]),
+    "ns_peer_free": (c_int, [_P]),
+    "ns_peer_export": (c_int, [_P, _P]),
+    "ns_peer_open": (c_int, [_P, _P]),
+    "ns_peer_close": (c_int, [_P]),
     "ns_check_step_metadata": (c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P]),
     "ns_add_rmsnorm": (c_int, [_P, _P, _P, _P, _P, _I64, _I32, _F, c_int, _P]),
     "ns_silu_mul": (c_int, [_P, _P, _I64, _I32, c_int, _P]),

@@ -16,6 +16,8 @@
 // the same launch with the same arguments); the last CTA to finish advances it.
 // A wait that runs out (a peer that never arrives) is counted (ns_collect_status), the kernel goes on and returns: its
 // results are then undefined, the context stays usable.
+#include <cstring>
+
 #include "common.cuh"
 
 namespace ns {
@@ -184,4 +186,55 @@ extern "C" int ns_tp_allreduce_add_rmsnorm(const void* const* peer_partials, voi
     else if (world == 4) args(tp_allreduce_add_rmsnorm_kernel<4>);
     else args(tp_allreduce_add_rmsnorm_kernel<8>);
     return check_launch("tp_allreduce_add_rmsnorm");
+}
+
+// ---- set-up of peer-visible buffers (NOT on the serving path: these four calls allocate, map and free) -------------
+// One process per GPU: a rank allocates its partial buffers and flags with ns_peer_alloc (zero-filled), exports a handle,
+// the handles travel through the host (any channel: the caller's process group), and every other rank maps them with
+// ns_peer_open, which also enables peer access from the calling process's current device to the exporting GPU.
+extern "C" int ns_peer_alloc(int64_t bytes, void** ptr) {
+    NS_REQUIRE(ptr != nullptr && bytes > 0, NS_ERR_INVALID_ARG, "peer_alloc: bad arguments");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "peer_alloc: cudaMalloc(%lld): %s", (long long)bytes, cudaGetErrorString(e));
+    e = cudaMemset(p, 0, (size_t)bytes);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(NS_ERR_CUDA, "peer_alloc: cudaMemset: %s", cudaGetErrorString(e));
+    }
+    *ptr = p;
+    return NS_OK;
+}
+
+extern "C" int ns_peer_free(void* ptr) {
+    if (ptr == nullptr) return NS_OK;
+    const cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "peer_free: %s", cudaGetErrorString(e));
+    return NS_OK;
+}
+
+extern "C" int ns_peer_export(void* ptr, void* handle64) {
+    NS_REQUIRE(ptr != nullptr && handle64 != nullptr, NS_ERR_INVALID_ARG, "peer_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    const cudaError_t e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "peer_export: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    return NS_OK;
+}
+
+extern "C" int ns_peer_open(const void* handle64, void** ptr) {
+    NS_REQUIRE(handle64 != nullptr && ptr != nullptr, NS_ERR_INVALID_ARG, "peer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "peer_open: cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    *ptr = p;
+    return NS_OK;
+}
+
+extern "C" int ns_peer_close(void* ptr) {
+    if (ptr == nullptr) return NS_OK;
+    const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    if (e != cudaSuccess) return fail(NS_ERR_CUDA, "peer_close: cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+    return NS_OK;
 }

@@ -155,6 +155,7 @@ class Qwen2Model:
     tp_group = None          # torch.distributed process group when the model is one tensor-parallel shard
     _plan_streams: dict = {}  # one side stream per device for the attention plan (shared by every model)
     tp_size = 1
+    tp_peer = None           # tensor_parallel.PeerReduce: fused all-reduce + add + RMSNorm over peer memory (small steps)
 
     def __init__(self, cfg: ModelConfig, state_dict: dict[str, torch.Tensor]):
         self.cfg = cfg
@@ -376,6 +377,9 @@ class Qwen2Model:
         # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's
         # attention: it runs on a second stream next to the RoPE tables, the embedding, the first norm and the first QKV
         # GEMM (inside a capture this becomes a fork and a join in the graph).
+        # tensor parallel, small steps: the two all-reduces of a layer are fused with the add + RMSNorm after them and
+        # read the peers' partials over NVLink (tensor_parallel.PeerReduce); larger steps use the NCCL all-reduce
+        peer = self.tp_peer if (self.tp_peer is not None and self.tp_group is not None and T <= self.tp_peer.max_rows) else None
         plan_stream = None
         if plan:
             main = torch.cuda.current_stream()
@@ -410,10 +414,22 @@ class Qwen2Model:
                 a = thin_gemm(o2, layer.o_w)
             elif stream_o:
                 a = stream_gemm(o2, layer.o_w)
+            elif skinny_o:
+                a = skinny_gemm(o2, layer.o_w, split_k=8)
+            elif peer is not None:
+                a = None                                    # the library GEMM writes its partial where the peers read it
+                torch.matmul(o2, layer.o_w.t(), out=peer.partial(0, T))
+                h, x = peer.reduce_add_rmsnorm(0, T, x, layer.ln2, eps)
             else:
-                a = skinny_gemm(o2, layer.o_w, split_k=8) if skinny_o else F.linear(o2, layer.o_w)
-            a = self._all_reduce(a)
-            h, x = norm(a, layer.ln2, eps, residual=x)
+                a = F.linear(o2, layer.o_w)
+            if peer is not None and a is None:
+                pass
+            elif peer is not None:
+                peer.partial(0, T).copy_(a)                 # (a GEMM kernel of this library: its output is copied over)
+                h, x = peer.reduce_add_rmsnorm(0, T, x, layer.ln2, eps)
+            else:
+                a = self._all_reduce(a)
+                h, x = norm(a, layer.ln2, eps, residual=x)
             if thin_gu:
                 m = thin_swiglu_gemm(h, layer.gate_up_w)
             elif umma_gu:
@@ -422,7 +438,14 @@ class Qwen2Model:
                 m = stream_gemm(h, layer.gate_up_w, epilogue=EPI_SILU_MUL)
             else:
                 m = silu_mul(F.linear(h, layer.gate_up_w))
-            d = self._all_reduce(skinny_gemm(m, layer.down_w, split_k=8) if skinny_down else F.linear(m, layer.down_w))
             nxt = self.layers[i + 1].ln1 if i + 1 < len(self.layers) else self.norm
-            h, x = norm(d, nxt, eps, residual=x)          # x + mlp, then the next layer's (or the final) norm
+            if peer is not None:
+                if skinny_down:
+                    peer.partial(1, T).copy_(skinny_gemm(m, layer.down_w, split_k=8))
+                else:
+                    torch.matmul(m, layer.down_w.t(), out=peer.partial(1, T))
+                h, x = peer.reduce_add_rmsnorm(1, T, x, nxt, eps)
+            else:
+                d = self._all_reduce(skinny_gemm(m, layer.down_w, split_k=8) if skinny_down else F.linear(m, layer.down_w))
+                h, x = norm(d, nxt, eps, residual=x)      # x + mlp, then the next layer's (or the final) norm
         return F.linear(h.index_select(0, meta.last_rows), self.lm_head)

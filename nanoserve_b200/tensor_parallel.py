@@ -94,3 +94,104 @@ def random_tp_model(shape_name: str, group=None, dtype=torch.bfloat16, device="c
     model = Qwen2Model(loc, sd)
     model.tp_group = group if world > 1 else None
     return model
+
+
+class _DeviceBlock:
+    """A library-owned device allocation seen by torch without a copy (`__cuda_array_interface__`)."""
+
+    def __init__(self, ptr: int, shape: tuple, typestr: str):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3, "strides": None}
+
+
+class PeerReduce:
+    """Peer-mapped partial buffers and flags for `ns_tp_allreduce_add_rmsnorm`: the all-reduce of a tensor-parallel layer
+    fused with the residual add and the RMSNorm that follow it, over NVLink peer loads instead of an NCCL collective.
+
+    Every rank allocates two partial buffers [max_rows, hidden] bf16 (used in turn from call to call), a flag word per
+    peer and two state words, exports them, and maps every peer's. A GEMM writes its partial straight into
+    `partial(k)`; `reduce_add_rmsnorm(k, rows, residual, weight, eps)` returns (h, x). Every rank must make the same
+    sequence of calls with k alternating 0, 1, 0, 1 ... (two all-reduce sites per layer keep that true by themselves).
+    Steps with more than max_rows token rows keep NCCL."""
+
+    def __init__(self, group, hidden: int, max_rows: int, device):
+        from nanoserve_b200 import _lib
+        import ctypes
+        self._lib, self._ct = _lib, ctypes
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.hidden, self.max_rows, self.device = hidden, max_rows, torch.device(device)
+        lib = _lib.load()
+        self.n_calls = 0
+        with torch.cuda.device(self.device):
+            buf_bytes = 2 * max_rows * hidden * 2
+            ctrl_bytes = 256                                   # flags [world] uint32 at 0, state [2] uint32 at 128
+            self._own = []
+            ptrs = []
+            for nbytes in (buf_bytes, ctrl_bytes):
+                p = ctypes.c_void_p()
+                _lib.call("ns_peer_alloc", nbytes, ctypes.byref(p))
+                self._own.append(p.value)
+                ptrs.append(p.value)
+            self._buf_ptr, self._ctrl_ptr = ptrs
+            handles = []
+            for p in ptrs:
+                h = ctypes.create_string_buffer(64)
+                _lib.call("ns_peer_export", p, h)
+                handles.append(bytes(h.raw))
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, handles, group=group)
+            self._opened = []
+            self.peer_buf, self.peer_ctrl = [0] * self.world, [0] * self.world
+            for w, (hb, hc) in enumerate(gathered):
+                if w == self.rank:
+                    self.peer_buf[w], self.peer_ctrl[w] = self._buf_ptr, self._ctrl_ptr
+                    continue
+                for which, h in ((self.peer_buf, hb), (self.peer_ctrl, hc)):
+                    p = ctypes.c_void_p()
+                    _lib.call("ns_peer_open", ctypes.create_string_buffer(h, 64), ctypes.byref(p))
+                    which[w] = p.value
+                    self._opened.append(p.value)
+            # torch views of this rank's own partial buffers: what the GEMMs write into
+            self._partials = torch.as_tensor(_DeviceBlock(self._buf_ptr, (2, max_rows, hidden), "<i2"), device=self.device).view(torch.bfloat16)
+            dist.barrier(group=group)                           # every mapping exists before the first call
+        P = ctypes.c_void_p
+        self._flag_args = (P * self.world)(*self.peer_ctrl)
+        self._partial_args = [[(P * self.world)(*[b + k * max_rows * hidden * 2 for b in self.peer_buf]) for k in (0, 1)]]
+        self._state_ptr = self._ctrl_ptr + 128
+
+    def partial(self, k: int, rows: int) -> torch.Tensor:
+        """This rank's k-th partial buffer, [rows, hidden]: the output of the GEMM before the all-reduce."""
+        return self._partials[k, :rows]
+
+    def reduce_add_rmsnorm(self, k: int, rows: int, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+        """(h, x): x = residual + sum over ranks of partial(k), h = weight * rmsnorm(x)."""
+        h = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        x = torch.empty_like(h)
+        self._lib.call("ns_tp_allreduce_add_rmsnorm", self._partial_args[0][k], self._flag_args, self._state_ptr,
+                       residual.data_ptr(), weight.data_ptr(), h.data_ptr(), x.data_ptr(), rows, self.hidden, float(eps),
+                       self.rank, self.world, self._lib.stream_ptr())
+        return h, x
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (after a barrier: nobody may still be reading them)."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self._lib.call("ns_peer_close", p)
+            dist.barrier(group=self.group)
+            self._partials = None
+            for p in self._own:
+                self._lib.call("ns_peer_free", p)
+        self._own = None
+
+
+def enable_fused_allreduce(model: Qwen2Model, max_rows: int = 256) -> PeerReduce | None:
+    """Give a tensor-parallel model the fused all-reduce + add + RMSNorm path for steps of at most max_rows token rows
+    (bf16 only). Returns the PeerReduce it now owns, or None when the model is not tensor parallel."""
+    if model.tp_group is None or model.dtype != torch.bfloat16:
+        return None
+    model.tp_peer = PeerReduce(model.tp_group, model.cfg.hidden_size, max_rows, model.device)
+    return model.tp_peer

@@ -101,3 +101,89 @@ def test_two_rank_tp_engine_matches_the_oracle():
     from tests.parity import check_tokens
     check_tokens(gathered[0], [want[i] for i in range(len(want))], lambda i, j: oracle.gaps[i][j], 1e-3,
                  what="TP=2 fp32")
+
+
+def _fused_worker(rank, world, port, out):
+    """Kernel level: W ranks with random partials -> every rank's (h, x) equals the torch restatement of
+    all-reduce(sum, rounded to bf16) + residual add + RMSNorm, bitwise equal across ranks, over several calls that
+    alternate the two buffers; then a bf16 engine with the fused path against one with NCCL all-reduces."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.tensor_parallel import PeerReduce, build_tp_model, enable_fused_allreduce
+    from oracle import ops as O
+    from oracle.engine import run_requests
+    dev = torch.device("cuda", rank)
+    hidden, max_rows = 896, 64
+    peer = PeerReduce(dist.group.WORLD, hidden, max_rows, dev)
+    worst, equal = 0.0, True
+    for call in range(7):
+        rows = [1, 64, 17, 32, 5, 64, 8][call]
+        g = torch.Generator().manual_seed(100 + call)                  # every rank draws ALL ranks' partials
+        parts = [(torch.randn(rows, hidden, generator=g) * 0.5).to(torch.bfloat16) for _ in range(world)]
+        res = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+        k = call & 1
+        peer.partial(k, rows).copy_(parts[rank].to(dev))
+        h, x = peer.reduce_add_rmsnorm(k, rows, res.to(dev), w.to(dev), 1e-6)
+        total = sum(p.float() for p in parts).to(torch.bfloat16)       # what an all-reduce of bf16 tensors returns
+        h_ref, x_ref = O.add_rms_norm(total, w, 1e-6, res)
+        worst = max(worst, (x.cpu().float() - x_ref.float()).abs().max().item(), (h.cpu().float() - h_ref.float()).abs().max().item())
+        both = [torch.empty_like(h) for _ in range(world)]
+        dist.all_gather(both, h)
+        equal = equal and all(torch.equal(both[0], b) for b in both)
+    peer.close()
+    # engine level, bf16: fused path vs NCCL path vs the fp32 oracle on the same bf16 weights (tie rule)
+    sd16 = {k: v.to(torch.bfloat16).cuda() for k, v in G.tiny_state_dict(G.TINY_CFG).items()}
+    toks = {}
+    for fused in (False, True):
+        model = build_tp_model(CFG, sd16)
+        if fused:
+            assert enable_fused_allreduce(model, max_rows=64) is not None
+        eng = LLMEngine(model, eos_token_ids=[], **G.TINY_ENGINE_KW)
+        outs = run_requests(eng, G.tiny_requests(), concurrency=4)
+        toks[fused] = ([outs[i] for i in range(len(outs))], eng.stats["graph_steps"], eng.buffers.device_errors)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, toks[True][0])
+    torch.cuda.synchronize()
+    if rank == 0:
+        out.put(dict(worst=worst, equal=equal, toks=toks, ranks_agree=all(g == gathered[0] for g in gathered)))
+        out.close()
+        out.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.gpu
+def test_two_rank_fused_allreduce_add_rmsnorm():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from oracle.engine import OracleEngine, OracleModel, run_requests
+    from tests.parity import check_tokens
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29300 + os.getpid() % 600
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        res = out.get(timeout=300)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    assert all(p.exitcode == 0 for p in procs)
+    # sum and residual are exact roundings; the norm's rsqrt / mean may differ from the CPU's in the last bf16 bit
+    assert res["worst"] <= 0.04 and res["equal"], res["worst"]
+    (plain, _, err0), (fused, graph_steps, err1) = res["toks"][False], res["toks"][True]
+    assert res["ranks_agree"] and graph_steps > 0 and err0 == 0 and err1 == 0
+    sd16 = {k: v.to(torch.bfloat16).float() for k, v in G.tiny_state_dict(G.TINY_CFG).items()}
+    oracle = OracleEngine(OracleModel(G.TINY_CFG, sd16), reserve_garbage_block=True, **G.TINY_ENGINE_KW)
+    want = run_requests(oracle, G.tiny_requests(), concurrency=4)
+    want = [want[i] for i in range(len(want))]
+    for name, got in (("NCCL all-reduce", plain), ("fused all-reduce + norm", fused)):
+        same, accepted = check_tokens(got, want, lambda i, j: oracle.gaps[i][j], 2 * 1.5, what=f"TP=2 bf16, {name}")
+        print(f"TP=2 bf16 {name}: {same}/{len(want)} identical to the oracle, accepted {accepted}")
