@@ -597,6 +597,9 @@ def extra_workload(args) -> None:
             if g == my_group:
                 group = h
         model = random_tp_model("qwen2.5-7b", group=group, device=device)
+        if args.fused_allreduce and tp > 1:
+            from nanoserve_b200.tensor_parallel import enable_fused_allreduce
+            enable_fused_allreduce(model, max_rows=256)     # steps up to 256 token rows: all-reduce + add + norm in one kernel
         all_reqs = serving_requests(args.requests or 256, prompt_range=(256, 4096), output_range=(64, 512), vocab=152064, seed=4)
         reqs = all_reqs[my_group::n_groups]
         eng = LLMEngine(model, eos_token_ids=[], max_seq_len=4608, max_num_seqs=64, max_num_batched_tokens=2048,
@@ -611,7 +614,7 @@ def extra_workload(args) -> None:
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.all_reduce(toks, op=dist.ReduceOp.SUM)
-        res["tp"] = {"tp_degree": tp, "replicas": n_groups, "tok_per_s": toks.item() / t.item(), "requests": len(all_reqs),
+        res["tp"] = {"tp_degree": tp, "replicas": n_groups, "fused_allreduce": bool(args.fused_allreduce and tp > 1), "tok_per_s": toks.item() / t.item(), "requests": len(all_reqs),
                      "requests_per_replica": len(reqs), "output_tokens": int(toks.item()), "seconds": t.item(),
                      "engine_steps": eng.stats["steps"], "graph_steps": eng.stats["graph_steps"],
                      "mixed_steps": eng.stats["piecewise_steps"], "device_status": eng.buffers.device_errors}
@@ -637,7 +640,7 @@ def extra_workload(args) -> None:
             with_ar = decode_graph_us()
             model_in_graph = eng.model
             saved, model_in_graph.tp_group = model_in_graph.tp_group, None
-            without_ar = decode_graph_us()
+            without_ar = decode_graph_us()                      # (tp_group None also switches the fused path off)
             model_in_graph.tp_group = saved
             res["tp"]["decode_step_us_bucket64"] = {"with_all_reduce": with_ar, "without_all_reduce": without_ar,
                                                     "all_reduce_share": 1 - without_ar / with_ar}
@@ -700,6 +703,8 @@ def main() -> None:
                     help="serve = the benchmark contract's line (default); the others print one JSON object of extras")
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--tp-size", type=int, default=0, help="tp workload: ranks per tensor-parallel replica (default: all)")
+    ap.add_argument("--fused-allreduce", action="store_true",
+                    help="tp workload: all-reduce + residual add + RMSNorm in one kernel over NVLink peer loads (steps <= 256 rows)")
     ap.add_argument("--allreduce-share", action="store_true",
                     help="tp workload: also time a 64-row decode graph with and without its all-reduces")
     ap.add_argument("--router", type=int, default=0, metavar="N",
