@@ -1,7 +1,9 @@
 // Decode paged attention for sm_100a: HBM-bound GQA over 16-token KV blocks.
 //
-// Grid  : CTAS_PER_SM persistent CTAs per SM (2 for head_dim 64: 16 warps per SM hide the MMA / shuffle latency). The flattened list of (decode row, KV block) units is cut into equal
-//         contiguous ranges (attn_plan.cuh), so every CTA streams the same number of bytes.
+// Grid  : one persistent CTA per SM (16 warps for head_dim 64, 8 for 128). The flattened list of (decode row, KV block)
+//         units is cut into contiguous ranges by the plan kernel (attn_plan.cuh): balanced whole rows / equal pieces of
+//         long rows for large steps (optionally two virtual 8-warp CTAs per CTA), and for small steps one thread-block
+//         cluster of CTAs per row (cluster mode, see below).
 // Warp  : owns one KV head and every (warps-per-head)-th block of the CTA's range. It runs its own
 //         cp.async ring (STAGES tiles of 16 tokens, K and V, 128-bit copies, XOR-swizzled rows) with no
 //         CTA-wide barrier in the steady state, so up to (STAGES-1) tiles per warp are always in flight.
@@ -12,7 +14,9 @@
 //         bf16 before P.V, the row max is reduced with warp shuffles (online softmax).
 // Split : a row whose blocks span several warps / CTAs is combined in two levels: the warps of one head
 //         through shared memory, CTAs through fp32 partials in the workspace, where the LAST CTA to arrive
-//         (atomic counter, no waiting) does the final reduction. Counters are left at zero.
+//         (atomic counter, no waiting) does the final reduction. Counters are left at zero. In cluster mode the CTAs of a
+//         row's cluster write their pieces into the first CTA's shared memory (DSMEM) instead, and one cluster barrier
+//         later that CTA sums them: no global partials, no atomics.
 #include "attn_plan.cuh"
 #include "common.cuh"
 
