@@ -180,6 +180,17 @@ int ns_thin_gemm(const void* x, const void* w, const void* bias, void* out, int3
  * x arrives by bulk copies whose bounded wait is counted in ns_thin_gemm_errors when it runs out (0 unless a fault).
  * Replaces, fused: nanoserve/model.py:256-257 (gate/up F.linear + silu_mul) for steps of at most 32 token rows. */
 int ns_thin_swiglu_gemm(const void* x, const void* w, void* out, int32_t M, int32_t inter, int32_t K, void* stream);
+/* The o_proj -> residual add -> RMSNorm -> gate/up boundary of a decode layer in two kernels instead of three:
+ * ns_thin_gemm_residual: out = bf16(residual + bf16(x . w^T)) (the new residual stream, [M, N]) and ss_out[M][N / 8] =
+ * the sum of squares of each 8-column piece of out's rows. Shapes and limits as ns_thin_gemm.
+ * ns_thin_swiglu_gemm_norm: as ns_thin_swiglu_gemm, on h = ln_w * bf16(x * rsqrt(sum(x^2) / K + eps)) computed in shared
+ * memory from the ss_parts pieces per row that ns_thin_gemm_residual left (ss_in [M][ss_parts], ss_parts = K / 8).
+ * Rounding points as the unfused ops; the row's sum of squares is added in another order than ns_add_rmsnorm's.
+ * Replace: nanoserve/model.py:256 (o_proj, x + ...), :251 rms_norm, :257 gate/up + silu_mul of steps <= 32 rows. */
+int ns_thin_gemm_residual(const void* x, const void* w, const void* residual, void* out, float* ss_out, int32_t M,
+                          int32_t N, int32_t K, void* stream);
+int ns_thin_swiglu_gemm_norm(const void* x, const float* ss_in, int32_t ss_parts, const void* ln_w, float eps,
+                             const void* w, void* out, int32_t M, int32_t inter, int32_t K, void* stream);
 int ns_thin_gemm_errors(int32_t* count);
 
 /* Persistent weight-streaming GEMM for decode-sized batches (bf16 only):

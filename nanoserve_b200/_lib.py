@@ -46,6 +46,8 @@ SIGNATURES: dict[str, tuple] = {
                                _I32, _P]),
     "ns_thin_gemm": (c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I32, _I32, _P]),
     "ns_thin_swiglu_gemm": (c_int, [_P, _P, _P, _I32, _I32, _I32, _P]),
+    "ns_thin_gemm_residual": (c_int, [_P, _P, _P, _P, _P, _I32, _I32, _I32, _P]),
+    "ns_thin_swiglu_gemm_norm": (c_int, [_P, _P, _I32, _P, _F, _P, _P, _I32, _I32, _I32, _P]),
     "ns_thin_gemm_errors": (c_int, [_P]),
     "ns_stream_gemm": (c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _I32, _I32, _I32, _F, _I32, _P]),
     "ns_stream_gemm_errors": (c_int, [_P]),

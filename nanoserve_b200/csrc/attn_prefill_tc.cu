@@ -6,17 +6,25 @@
 //   S[128 x 64]  = Q[128 x HD] . K_tile[64 keys x HD]^T     tcgen05.mma kind::f16, A and B K-major, SWIZZLE_128B
 //   PV[128 x HD] = P[128 x 64 keys] . V_tile[64 keys x HD]  A K-major (P written to shared memory as bf16),
 //                                                            B MN-major (V rows are the pool's rows, untransposed)
-// Software pipeline over the key tiles (S, PV and P are double buffered; every thread owns one row, lane = row):
-//   iteration j:  issue S(j+1)  |  softmax(j) from tensor memory -> P(j) in shared memory  |  issue PV(j)
-//                 |  o = o * alpha(j-1) + PV(j-1)
-// so the tensor cores compute S(j+1) and PV(j-1) while the threads are in softmax(j), and the only exposed waits are
-// the first S and the last PV. One thread issues the MMAs with PRECOMPUTED descriptors (a tcgen05.mma of this size
-// occupies the tensor pipe for ~50 cycles; building two 64-bit descriptors per instruction in a lone thread cost
-// three times that). K/V tiles (4 pool blocks of 16 tokens) are staged by 128-bit cp.async into the XOR-swizzled
-// layout the SWIZZLE_128B descriptors expect (1024-byte aligned 128-byte-wide atoms; a 256-byte head row is two atoms),
-// K three tiles deep, V four (V(j) is still being read by PV(j) when K's buffer is already free). Tiles wholly below
-// every row's causal limit skip the mask. Every mbarrier wait is bounded: on expiry the CTA counts an error in the
-// plan header (ns_collect_status), skips its stores, frees its tensor memory and returns.
+// Three roles (192 threads):
+//   warps 0-3  one softmax thread per row (lane = row of tensor memory): S(j) -> P(j), o = o * alpha + PV(j-1)
+//   warp 4     lane 0 issues every tcgen05.mma with PRECOMPUTED descriptors (a tcgen05.mma of this size occupies the
+//              tensor pipe for ~50 cycles; building two 64-bit descriptors per instruction in a lone thread cost three
+//              times that)
+//   warp 5     lane 0 fetches the K/V tiles: one tiled TMA load (cp.async.bulk.tensor, no multicast) per pool block of 16
+//              tokens and 128-byte atom from a 4-D tensor map over THIS GPU's pool [head_dim, kv head, position, block],
+//              128-byte swizzle, K three tiles deep and V four; a stage is refilled when the MMA that read it has
+//              committed (tcgen05.commit -> mbarrier). The softmax threads never touch K or V.
+// Pipeline over the key tiles (S, PV and P double buffered): S runs two tiles ahead,
+//   iteration j:  softmax(j) from tensor memory -> P(j) in shared memory | one 160-thread barrier | issue PV(j), S(j+2)
+//                 | o = o * alpha(j-1) + PV(j-1)
+// so the tensor cores compute PV(j-1) and S(j+1) while the threads are in softmax(j). Tiles wholly below every row's
+// causal limit skip the mask. Rows of a sequence's last V tile at or past its length are zeroed in shared memory (a block's
+// unused slots may hold anything, and 0 x NaN would poison the row). Every mbarrier wait is bounded: on expiry the CTA
+// counts an error in the plan header (ns_collect_status), skips its stores, waits for its copies in flight, frees its
+// tensor memory and returns.
+#include <cuda.h>
+
 #include "attn_plan.cuh"
 #include "common.cuh"
 
@@ -27,10 +35,14 @@ int prefill_cluster_size();      // c_api.cu: NS_TUNE_PREFILL_CLUSTER (0 = built
 namespace tc {
 
 constexpr int kRows = 128;          // UMMA M = softmax threads (one per row)
-constexpr int kThreads = kRows + 32; // + one warp whose first lane issues every tcgen05.mma
+constexpr int kThreads = kRows + 64; // + one warp whose first lane issues every tcgen05.mma + one whose first lane copies
+constexpr int kSyncThreads = kRows + 32;   // softmax threads + issuing warp meet once per tile (named barrier 1)
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
-constexpr int kStagesK = 3;         // K tiles in shared memory (copies run two tiles ahead of the tile in softmax)
-constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) while K(j)'s buffer is being refilled
+constexpr int kStagesK = 3;         // K tiles in shared memory (S runs two tiles ahead of the tile in softmax)
+constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) when K(j)'s buffer is long free
+// mbarriers: S0 S1 PV0 PV1 | K full x3 | V full x4 | K free x3 | V free x4
+constexpr int kBarS = 0, kBarPV = 2, kBarKFull = 4, kBarVFull = kBarKFull + kStagesK, kBarKFree = kBarVFull + kStagesV,
+              kBarVFree = kBarKFree + kStagesK, kBars = kBarVFree + kStagesV;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kDefaultCluster = 1;  // CTAs sharing one work item's key tiles (see launch_prefill_tc_hd)
 
@@ -89,9 +101,55 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar_saddr, uint32_t parity) 
     return false;
 }
 
-// 32 consecutive fp32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
+// The copying thread's wait: also gives up when the softmax threads raised the CTA's abort flag.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t mbar_saddr, uint32_t parity, const volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(mbar_saddr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (*abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_saddr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_saddr), "r"(bytes) : "memory");
+}
+
+// One box [64 elements, 1 head, 16 positions, 1 block] of a pool into shared memory (2 KB, 128-byte swizzle).
+__device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* map, int elem, int head, int block, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(map), "r"(elem), "r"(head), "r"(0), "r"(block), "r"(mbar)
+        : "memory");
+}
+
+// Named barrier 1 over the softmax threads and the issuing warp, AND-reducing `ok`.
+__device__ __forceinline__ bool tile_barrier_and(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(r)
+        : "r"((uint32_t)ok), "r"(kSyncThreads)
+        : "memory");
+    return r != 0;
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane, requested only: tmem_ld_wait() before the values are used.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -102,25 +160,40 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+constexpr float kRescaleStep = 8.f;   // the exponent's reference may lag the row maximum by up to 2^8 (see the kernel)
 
 }  // namespace tc
 
 template <int HD>
-__global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
     using namespace tc;
     constexpr int ATOMS = HD / 64;                  // 128-byte-wide swizzle atoms per head row
     constexpr int Q_BYTES = kRows * 128 * ATOMS;    // [atom][128 rows][128 B]
     constexpr int KV_BYTES = kKeys * 128 * ATOMS;   // [atom][64 keys][128 B]
     constexpr int P_BYTES = kRows * 128;            // [128 rows][64 keys] bf16
-    constexpr uint32_t COL_S = 0, COL_PV = 2 * kKeys;            // tensor memory: S0, S1, PV0, PV1
-    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;
+    constexpr uint32_t COL_S = 0, COL_O = 2 * kKeys;             // tensor memory: S0, S1, O
+    constexpr uint32_t TMEM_COLS = 256;                            // 128 + HD rounded up to a power of two
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t mbar[4];       // S0, S1, PV0, PV1
+    __shared__ __align__(8) uint64_t mbar[kBars];
     __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_flag;                 // raised when a bounded wait ran out: the copying thread stops too
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     // The CTAs of a thread-block cluster share one work item: rank r takes the r-th share of its key tiles and the shares
@@ -137,8 +210,9 @@ __global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_ker
     const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[item_idx];
     const int s = item.x, q_start = item.y, g = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool worker = tid < kRows;              // one softmax thread per row; the fifth warp only issues the MMAs
-    const bool issuer = tid == kRows;
+    const bool worker = tid < kRows;              // one softmax thread per row
+    const bool issuer = tid == kRows;             // first lane of warp 4: every tcgen05.mma
+    const bool copier = tid == kRows + 32;        // first lane of warp 5: every K/V copy
     const int q0 = p.cu_seqlens[s];
     const int T = p.cu_seqlens[s + 1] - q0;
     const int len = p.seq_lens[s];
@@ -151,28 +225,23 @@ __global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_ker
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + kStagesK * KV_BYTES, sP = sV + kStagesV * KV_BYTES;
-    const uint32_t bar_s0 = smem_u32(&mbar[0]), bar_pv0 = smem_u32(&mbar[2]);
+    const uint32_t bar0 = smem_u32(&mbar[0]);
+    auto bar = [&](int i) -> uint32_t { return bar0 + 8u * (uint32_t)i; };
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[i])) : "memory");
+        for (int i = 0; i < kBars; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar(i)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        abort_flag = 0;
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = tmem_slot;
-    const uint32_t t_lane = tmem + ((uint32_t)(32 * warp) << 16);     // this warp's 32 lanes; lane = row
-
     // row of this thread
     const int tok = q_start + ((tid & (kRows - 1)) >> 3), hh = tid & 7;
     const bool row_ok = worker && tok < T && hh < p.group;
     const int h = g * p.group + hh;
-
     // Q tile: one head row per thread, 128 bytes per atom
     if (worker) {
         const __nv_bfloat16* src = p.q + (int64_t)(q0 + (row_ok ? tok : 0)) * p.q_stride + (int64_t)(row_ok ? h : 0) * HD;
@@ -180,193 +249,259 @@ __global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1) prefill_tc_ker
         for (int c = 0; c < 8 * ATOMS; ++c)
             cp_async16(sQ + (c >> 3) * (kRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4), src + c * 8, row_ok ? 16 : 0);
     }
-    // Block ids of a tile: its 64 keys are 4 pool blocks, the same 4 for every thread. They are fetched one tile ahead of
-    // the copies that need them, so no copy waits on a dependent table load.
-    int blk_next[kKeys / 16];
-    auto fetch_ids = [&](int kt) {
-#pragma unroll
-        for (int it = 0; it < kKeys / 16; ++it) {
-            const int key0 = (tile0 + kt) * kKeys + it * 16;
-            blk_next[it] = (worker && kt < n_tiles && key0 < len) ? table[key0 >> 4] : 0;
-        }
-    };
-    auto load_kv = [&](int kt) {                    // uses blk_next (the ids of tile kt), then fetches those of tile kt + 1
-        if (worker && kt < n_tiles) {
-            const uint32_t ks = sK + (kt % kStagesK) * KV_BYTES, vs = sV + (kt % kStagesV) * KV_BYTES;
-#pragma unroll
-            for (int it = 0; it < (kKeys * 8 * ATOMS) / kRows; ++it) {
-                const int qd = it * kRows + tid;                   // 16-byte chunk of the tile
-                const int row = qd / (8 * ATOMS), c = qd % (8 * ATOMS);
-                const int key = (tile0 + kt) * kKeys + row;
-                const bool ok = key < len;
-                const int64_t goff = (int64_t)blk_next[row >> 4] * p.blk_stride + (int64_t)(key & 15) * p.pos_stride +
-                                     (int64_t)g * p.head_stride + c * 8;
-                const uint32_t off = (c >> 3) * (kKeys * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-                cp_async16(ks + off, p.k_pool + goff, ok ? 16 : 0);
-                cp_async16(vs + off, p.v_pool + goff, ok ? 16 : 0);
-            }
-        }
-        cp_async_commit();
-        fetch_ids(kt + 1);
-    };
-    fetch_ids(0);
-    load_kv(0);                       // group 0 = Q + tile 0
-    load_kv(1);
-
-    // descriptors, built once: an instruction's operand is the base plus a byte offset (>> 4) in the address field
-    constexpr uint32_t idesc_s = instr_desc(false, kKeys), idesc_pv = instr_desc(true, HD);
-    const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
-    const uint64_t dP = smem_desc(sP, 16, 1024);
-    const uint64_t dV = smem_desc(sV, kKeys * 128, 1024);          // MN-major B: next 64-column atom kKeys * 128 bytes on
-    auto issue_s = [&](int kt) {                                    // S(kt) = Q . K(kt)^T into S buffer kt & 1
-        const uint64_t k0 = dK + (uint64_t)(((kt % kStagesK) * KV_BYTES) >> 4);
-        const uint32_t d = tmem + COL_S + (uint32_t)((kt & 1) * kKeys);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {                      // K extent 16 per instruction = 32 bytes inside an atom
-            const uint32_t a_off = (uint32_t)(((kk >> 2) * (kRows * 128) + (kk & 3) * 32) >> 4);
-            const uint32_t b_off = (uint32_t)(((kk >> 2) * (kKeys * 128) + (kk & 3) * 32) >> 4);
-            mma_f16(d, dQ + a_off, k0 + b_off, idesc_s, kk > 0);
-        }
-        mma_commit(bar_s0 + 8 * (kt & 1));
-    };
-    auto issue_pv = [&](int kt) {                                   // PV(kt) = P(kt) . V(kt) into PV buffer kt & 1
-        const uint64_t p0 = dP + (uint64_t)(((kt & 1) * P_BYTES) >> 4);
-        const uint64_t v0 = dV + (uint64_t)(((kt % kStagesV) * KV_BYTES) >> 4);
-        const uint32_t d = tmem + COL_PV + (uint32_t)((kt & 1) * HD);
-#pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk)                     // 16 keys per instruction: 32 bytes of P, 16 rows of V
-            mma_f16(d, p0 + (uint32_t)((kk * 32) >> 4), v0 + (uint32_t)((kk * 2048) >> 4), idesc_pv, kk > 0);
-        mma_commit(bar_pv0 + 8 * (kt & 1));
-    };
-
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    const int limit = ctx + tok;      // last key this row may see
-    bool ok = true;
-
-    auto accumulate = [&](int kt, float alpha) {                    // o = o * alpha + PV(kt)
-        if (!mbar_wait(bar_pv0 + 8 * (kt & 1), (uint32_t)((kt >> 1) & 1))) ok = false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t src = t_lane + COL_PV + (uint32_t)((kt & 1) * HD);
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            float v[32];
-            tmem_ld32(src + 32 * c, v);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], alpha, v[i]);
-        }
-    };
-
-    // prologue: tile 0 (and Q) in shared memory, S(0) under way
-    cp_async_wait<1>();
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes of Q -> visible to the MMA
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (issuer && n_tiles > 0) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        issue_s(0);
-    }
+    __syncthreads();                                                   // barriers initialised, tensor memory allocated, Q in place
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);     // this warp's 32 lanes; lane = row
+
+    // keys of tile kt that exist in the pool and may be seen by this item: whole blocks up to kv_end
+    auto tile_blocks = [&](int kt) -> int { return min(kKeys / 16, (kv_end - (tile0 + kt) * kKeys + 15) >> 4); };
+    bool ok = true;
+    float m_run = -INFINITY, l_run = 0.f;   // this row's exponent reference and sum (softmax threads)
+    int k_issued = 0, v_issued = 0;   // copying thread: tiles whose copies were issued
+
+    if (copier) {
+        // ---- K/V tiles: block ids one tile ahead of the copies that need them
+        int ids[kKeys / 16], ids_next[kKeys / 16];
+        auto fetch_ids = [&](int kt, int (&dst)[kKeys / 16]) {
+#pragma unroll
+            for (int it = 0; it < kKeys / 16; ++it)
+                dst[it] = (kt < n_tiles && it < tile_blocks(kt)) ? table[(((tile0 + kt) * kKeys) >> 4) + it] : 0;
+        };
+        fetch_ids(0, ids_next);
+        for (int kt = 0; kt < n_tiles; ++kt) {
+#pragma unroll
+            for (int it = 0; it < kKeys / 16; ++it) ids[it] = ids_next[it];
+            fetch_ids(kt + 1, ids_next);
+            const int nb = tile_blocks(kt), sk = kt % kStagesK, sv = kt % kStagesV;
+            const uint32_t bytes = (uint32_t)nb * 16u * 128u * ATOMS;
+            // K(kt) goes where K(kt - 3) was: free once S(kt - 3) has committed
+            if (kt >= kStagesK && !mbar_wait_or_abort(bar(kBarKFree + sk), (uint32_t)((kt / kStagesK - 1) & 1), &abort_flag)) { ok = false; break; }
+            mbar_expect_tx(bar(kBarKFull + sk), bytes);
+#pragma unroll
+            for (int it = 0; it < kKeys / 16; ++it)
+                if (it < nb) {
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a)
+                        tma_load_block(sK + sk * KV_BYTES + a * (kKeys * 128) + it * 2048, &k_map, a * 64, g, ids[it], bar(kBarKFull + sk));
+                }
+            k_issued = kt + 1;
+            if (kt >= kStagesV && !mbar_wait_or_abort(bar(kBarVFree + sv), (uint32_t)((kt / kStagesV - 1) & 1), &abort_flag)) { ok = false; break; }
+            mbar_expect_tx(bar(kBarVFull + sv), bytes);
+#pragma unroll
+            for (int it = 0; it < kKeys / 16; ++it)
+                if (it < nb) {
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a)
+                        tma_load_block(sV + sv * KV_BYTES + a * (kKeys * 128) + it * 2048, &v_map, a * 64, g, ids[it], bar(kBarVFull + sv));
+                }
+            v_issued = kt + 1;
+        }
+        if (!ok) abort_flag = 1;
+    } else if (warp <= 4) {
+        // ---- descriptors, built once: an instruction's operand is the base plus a byte offset (>> 4) in the address field
+        constexpr uint32_t idesc_s = instr_desc(false, kKeys), idesc_pv = instr_desc(true, HD);
+        const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
+        const uint64_t dP = smem_desc(sP, 16, 1024);
+        const uint64_t dV = smem_desc(sV, kKeys * 128, 1024);          // MN-major B: next 64-column atom kKeys * 128 bytes on
+        auto issue_s = [&](int kt) {                                    // S(kt) = Q . K(kt)^T into S buffer kt & 1
+            const int sk = kt % kStagesK;
+            if (!mbar_wait(bar(kBarKFull + sk), (uint32_t)((kt / kStagesK) & 1))) { ok = false; return; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t k0 = dK + (uint64_t)((sk * KV_BYTES) >> 4);
+            const uint32_t d = tmem + COL_S + (uint32_t)((kt & 1) * kKeys);
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {                      // K extent 16 per instruction = 32 bytes inside an atom
+                const uint32_t a_off = (uint32_t)(((kk >> 2) * (kRows * 128) + (kk & 3) * 32) >> 4);
+                const uint32_t b_off = (uint32_t)(((kk >> 2) * (kKeys * 128) + (kk & 3) * 32) >> 4);
+                mma_f16(d, dQ + a_off, k0 + b_off, idesc_s, kk > 0);
+            }
+            mma_commit(bar(kBarS + (kt & 1)));                          // the softmax threads' signal
+            mma_commit(bar(kBarKFree + sk));                            // and the copying thread's: K's buffer is free
+        };
+        auto issue_pv = [&](int kt) {                                   // O += P(kt) . V(kt)
+            const int sv = kt % kStagesV;
+            if (!mbar_wait(bar(kBarVFull + sv), (uint32_t)((kt / kStagesV) & 1))) { ok = false; return; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t p0 = dP + (uint64_t)(((kt & 1) * P_BYTES) >> 4);
+            const uint64_t v0 = dV + (uint64_t)((sv * KV_BYTES) >> 4);
+            const uint32_t d = tmem + COL_O;
+#pragma unroll
+            for (int kk = 0; kk < kKeys / 16; ++kk)                     // 16 keys per instruction: 32 bytes of P, 16 rows of V
+                mma_f16(d, p0 + (uint32_t)((kk * 32) >> 4), v0 + (uint32_t)((kk * 2048) >> 4), idesc_pv, (kt > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(bar(kBarPV + (kt & 1)));
+            mma_commit(bar(kBarVFree + sv));
+        };
+
+        const int limit = ctx + tok;      // last key this row may see
+        const uint32_t t_o = t_lane + COL_O;
+
+        // prologue: S(0) and S(1) under way
+        if (issuer) {
+            if (n_tiles > 0) issue_s(0);
+            if (n_tiles > 1) issue_s(1);
+        }
+        __syncwarp();
 
 #ifdef NS_DEBUG_HOOKS
-    // profiling build: clock64 stamps of the first work item's thread 0, 8 per key tile, first 16 tiles
-    long long* stamps = (p.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) ? p.timeline : nullptr;
+        // profiling build: clock64 stamps of the first work item's thread 0, 8 per key tile, first 16 tiles
+        long long* stamps = (p.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) ? p.timeline : nullptr;
 #define NS_STAMP(i) do { if (stamps != nullptr && kt < 16) stamps[kt * 8 + (i)] = clock64(); } while (0)
 #else
 #define NS_STAMP(i) do { } while (0)
 #endif
-    for (int kt = 0; kt < n_tiles; ++kt) {
-        NS_STAMP(0);
-        load_kv(kt + 2);                                               // K into the buffer S(kt-1) has left, V into PV(kt-2)'s
-        cp_async_wait<1>();                                            // tiles <= kt + 1 landed for this thread
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        NS_STAMP(1);
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        NS_STAMP(2);
-        if (issuer && kt + 1 < n_tiles) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(kt + 1);                                           // runs while this tile is in the softmax
-        }
-        float alpha = 1.f;
-        if (worker) {
-        if (!mbar_wait(bar_s0 + 8 * (kt & 1), (uint32_t)((kt >> 1) & 1))) ok = false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        NS_STAMP(3);
+        for (int kt = 0; kt < n_tiles; ++kt) {
+            NS_STAMP(0);
+            if (worker) {
+                if (!mbar_wait(bar(kBarS + (kt & 1)), (uint32_t)((kt >> 1) & 1))) ok = false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                NS_STAMP(1);
 
-        // ---- online softmax on this thread's row: two passes over the 64 scores in tensor memory, 32 columns at a time
-        // (registers hold the running output; a second read of S is cheaper than spilling). Four independent chains for
-        // the maximum and for the sum; the softmax scale is folded into the exponent's multiply-add.
-        const uint32_t s_src = t_lane + COL_S + (uint32_t)((kt & 1) * kKeys);
-        const bool masked = (tile0 + kt) * kKeys + kKeys - 1 > ctx + q_start;    // else every row sees every key of the tile
-        const int key_base = (tile0 + kt) * kKeys;
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                // ---- softmax on this thread's row, the tile's 64 scores in registers (the running output stays in tensor
+                // memory). Four independent chains for the maximum and for the sum; the softmax scale is folded into the
+                // exponent's multiply-add.
+                const uint32_t s_src = t_lane + COL_S + (uint32_t)((kt & 1) * kKeys);
+                const bool masked = (tile0 + kt) * kKeys + kKeys - 1 > ctx + q_start;    // else every row sees every key of the tile
+                const int key_base = (tile0 + kt) * kKeys;
+                uint32_t sr[2][32];
+                tmem_ld32_issue(s_src, sr[0]);
+                tmem_ld32_issue(s_src + 32, sr[1]);
+                tmem_ld_wait();
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                if (masked) {                                              // scores past the row's causal limit leave the tile
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            float v[32];
-            tmem_ld32(s_src + 32 * hf, v);
-            if (masked) {
+                    for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (key_base + 32 * hf + i > limit) v[i] = -INFINITY;
+                        for (int i = 0; i < 32; ++i)
+                            if (key_base + 32 * hf + i > limit) sr[hf][i] = 0xff800000u;      // -inf: 2^(-inf) = 0 below
+                }
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[hf][i]));
+                NS_STAMP(2);
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                // The exponent's reference m_run follows the row maximum lazily: it moves only when the maximum has grown by
+                // more than kRescaleStep (or was -inf), so p = 2^(s - m_run) <= 2^kRescaleStep and most tiles leave the
+                // output in tensor memory untouched. (o, l) stay consistent with whatever reference they were summed
+                // under: when it moves both are multiplied by 2^(old - new). The decision is per warp (the tensor-memory
+                // accesses are warp-wide); rows that need no move then refresh their reference too.
+                const bool move = __any_sync(0xffffffffu, mx > m_run + kRescaleStep);
+                NS_STAMP(6);
+#ifdef NS_DEBUG_HOOKS
+                if (stamps != nullptr && kt < 16) stamps[kt * 8 + 7] = move ? 1 : 0;
+#endif
+                // P(kt) overwrites the buffer PV(kt-2) read: PV(kt-2) was issued before S(kt) by the same thread, so S(kt)'s
+                // commit, waited for above, covers it. Only a move has to wait for PV(kt-1), issued one barrier ago.
+                if (move) {
+                    const float m_new = fmaxf(m_run, mx);
+                    const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);      // 0 while the row has seen nothing
+                    m_run = m_new;
+                    l_run *= alpha;
+                    if (kt > 0) {
+                        if (!mbar_wait(bar(kBarPV + ((kt - 1) & 1)), (uint32_t)(((kt - 1) >> 1) & 1))) ok = false;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int c = 0; c < HD / 32; ++c) {
+                            uint32_t r[32];
+                            tmem_ld32_issue(t_o + 32 * c, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st32(t_o + 32 * c, r);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                // a CTA that holds only late tiles of its item can meet rows that see none of its keys yet
+                const float m_ref = m_run == -INFINITY ? 0.f : m_run;
+                float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t p_dst = sP + (kt & 1) * P_BYTES + tid * 128;
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float e = ex2(fmaf(__uint_as_float(sr[hf][i]), p.scale_log2, -m_ref));
+                        v[i] = e;
+                        ps4[i & 3] += e;
+                    }
+                    // P row as bf16 into shared memory (K-major, swizzled like the other operands)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(v[8 * c + 0], v[8 * c + 1]);
+                        pk.y = pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
+                        pk.z = pack_bf16x2(v[8 * c + 4], v[8 * c + 5]);
+                        pk.w = pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_dst + (((4 * hf + c) ^ (tid & 7)) << 4)),
+                                     "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                                     : "memory");
+                    }
+                }
+                l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+                NS_STAMP(3);
+                // V rows the copies did not bring (blocks past kv_end) or that lie at or past the sequence's length hold
+                // whatever shared memory or the pool's unused slots held: zero them (their P columns are zero, but 0 x NaN is
+                // NaN). Only a sequence's last tile has such rows.
+                const int v_rows = min(len, key_base + 16 * tile_blocks(kt)) - key_base;
+                if (v_rows < kKeys) {
+                    const int sv = kt % kStagesV;
+                    if (!mbar_wait(bar(kBarVFull + sv), (uint32_t)((kt / kStagesV) & 1))) ok = false;
+                    for (int c = v_rows * 8 * ATOMS + tid; c < kKeys * 8 * ATOMS; c += kRows) {
+                        const int row = c / (8 * ATOMS), cc = c % (8 * ATOMS);   // cc: atom * 8 + 16-byte chunk (the swizzle only permutes chunks inside a row)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sV + sv * KV_BYTES + (cc >> 3) * (kKeys * 128) + row * 128 + ((cc & 7) << 4)),
+                                     "r"(0)
+                                     : "memory");
+                    }
+                }
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-        }
-        NS_STAMP(4);
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-        const float m_new = fmaxf(m_run, mx);
-        // a CTA that holds only late tiles of its item can meet rows that see none of its keys yet
-        const float m_ref = m_new == -INFINITY ? 0.f : m_new;
-        alpha = ex2(m_run - m_ref);
-        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t p_dst = sP + (kt & 1) * P_BYTES + tid * 128;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            float v[32];
-            tmem_ld32(s_src + 32 * hf, v);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float e = ex2(fmaf(v[i], p.scale_log2, -m_ref));
-                if (masked && key_base + 32 * hf + i > limit) e = 0.f;
-                v[i] = e;
-                ps4[i & 3] += e;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of P (and V's tail) -> the MMA
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            ok = tile_barrier_and(ok);
+            if (!ok) break;
+            NS_STAMP(4);
+            if (issuer) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_pv(kt);                                              // P(kt) is complete, the output is where the softmax left it
+                if (kt + 2 < n_tiles) issue_s(kt + 2);                     // S buffer kt & 1 has just been read for the last time
             }
-            // P row as bf16 into shared memory (K-major, swizzled like the other operands)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 pk;
-                pk.x = pack_bf16x2(v[8 * c + 0], v[8 * c + 1]);
-                pk.y = pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
-                pk.z = pack_bf16x2(v[8 * c + 4], v[8 * c + 5]);
-                pk.w = pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_dst + (((4 * hf + c) ^ (tid & 7)) << 4)),
-                             "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
-                             : "memory");
-            }
+            __syncwarp();                                                  // the issuing warp meets the next tile's barrier as one
+            NS_STAMP(5);
         }
-        l_run = fmaf(l_run, alpha, (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-        m_run = m_new;
-        }
-        NS_STAMP(5);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (issuer) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_pv(kt);
-        }
-        NS_STAMP(6);
-        if (worker && kt > 0) accumulate(kt - 1, alpha_prev);          // PV(kt-1) ran under this tile's softmax
-        alpha_prev = alpha;
-        NS_STAMP(7);
+        if (!ok) abort_flag = 1;                                           // (every thread that saw a failure writes the same value)
     }
-    if (ok && worker && n_tiles > 0) accumulate(n_tiles - 1, alpha_prev);
-    cp_async_wait<0>();
-    ok = __syncthreads_and(ok);
+    __syncthreads();                  // all three roles are through their tiles (or gave up)
+    if (abort_flag) {
+        ok = false;
+        if (copier) {
+            // the copies already issued must land before this CTA's shared memory goes away (bounded like every wait)
+            for (int t = max(0, k_issued - kStagesK); t < k_issued; ++t) mbar_wait(bar(kBarKFull + t % kStagesK), (uint32_t)((t / kStagesK) & 1));
+            for (int t = max(0, v_issued - kStagesV); t < v_issued; ++t) mbar_wait(bar(kBarVFull + t % kStagesV), (uint32_t)((t / kStagesV) & 1));
+        }
+        __syncthreads();
+    }
+
+    // the row's output leaves tensor memory once, after the last PV
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    if (ok && worker && n_tiles > 0) {
+        if (!mbar_wait(bar(kBarPV + ((n_tiles - 1) & 1)), (uint32_t)(((n_tiles - 1) >> 1) & 1))) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32_issue(t_lane + COL_O + 32 * c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(r[i]);
+        }
+    }
 
     if (csize > 1) {
         // every CTA of the cluster is through its tiles: the first CTA's shared memory is free to receive the others'
@@ -437,10 +572,52 @@ bool prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim, int block_s
     return group >= 1 && group <= 8 && (head_dim == 64 || head_dim == 128);
 }
 
+namespace tc {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 4-D tensor map over one layer's K or V pool, innermost first: [head_dim, kv heads, 16 positions of a block, blocks],
+// bf16, strides as the caller gave them; a box is one head's 64 elements (one 128-byte atom) x 16 positions of one block,
+// written to shared memory with the 128-byte swizzle the UMMA descriptors expect. The pool's block count is not part of
+// the attention call: the block extent is the largest the map takes, and block ids come from the block tables.
+static bool make_pool_map(CUtensorMap* map, const void* pool, int head_dim, int n_kv_heads, int64_t blk_stride, int64_t pos_stride,
+                          int64_t head_stride) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t gdim[4] = {(cuuint64_t)head_dim, (cuuint64_t)n_kv_heads, 16, (cuuint64_t)1 << 31};
+    const cuuint64_t gstride[3] = {(cuuint64_t)head_stride * 2, (cuuint64_t)pos_stride * 2, (cuuint64_t)blk_stride * 2};
+    const cuuint32_t box[4] = {64, 1, 16, 1};
+    const cuuint32_t estride[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
+// NS_ERR_UNSUPPORTED: the driver refused a tensor map over these pools (strides it cannot express); the caller then uses
+// the mma.sync kernel.
 template <int HD>
 static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t st) {
     constexpr int atoms = HD / 64;
     constexpr int smem = tc::kRows * 128 * atoms + (tc::kStagesK + tc::kStagesV) * tc::kKeys * 128 * atoms + 2 * tc::kRows * 128 + 1024;
+    CUtensorMap k_map, v_map;
+    if (!tc::make_pool_map(&k_map, p.k_pool, HD, p.n_kv_heads, p.blk_stride, p.pos_stride, p.head_stride) ||
+        !tc::make_pool_map(&v_map, p.v_pool, HD, p.n_kv_heads, p.blk_stride, p.pos_stride, p.head_stride))
+        return NS_ERR_UNSUPPORTED;
     static SmemOptIn optin;
     if (optin.needs((size_t)smem)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -466,7 +643,7 @@ static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.overlap_prefill ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_tc_kernel<HD>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_tc_kernel<HD>, k_map, v_map, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "prefill attention (tcgen05): launch failed: %s", cudaGetErrorString(e));
     return NS_OK;
 }

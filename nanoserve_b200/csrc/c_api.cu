@@ -194,10 +194,10 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
         int64_t max_items = n_tokens / kPrefillTileTokens + n_seqs;
         const int64_t cap = (int64_t)ws_max_tokens / kPrefillTileTokens + ws_max_seqs + 1;
         if (max_items > cap) max_items = cap;
+        rc = NS_ERR_UNSUPPORTED;
         if (g_tuning[NS_TUNE_PREFILL_IMPL] == 0 && prefill_tc_supported(n_heads, n_kv_heads, head_dim, block_size))
-            rc = launch_prefill_tc(a, head_dim, (int)max_items, st);
-        else
-            rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
+            rc = launch_prefill_tc(a, head_dim, (int)max_items, st);      // NS_ERR_UNSUPPORTED: no tensor map over these pools
+        if (rc == NS_ERR_UNSUPPORTED) rc = launch_prefill_mma(a, head_dim, (int)max_items, st);
     }
     return rc;
 }

@@ -21,7 +21,7 @@
 namespace ns {
 namespace {
 
-enum ThinEpilogue { kThinBias = 0, kThinRopeKv = 2 };
+enum ThinEpilogue { kThinBias = 0, kThinRopeKv = 2, kThinResidual = 3 };
 
 struct ThinParams {
     const __nv_bfloat16* x;          // [M, K]
@@ -33,6 +33,8 @@ struct ThinParams {
     __nv_bfloat16* k_cache;          // kThinRopeKv: one layer's pool, rows of n_kv_heads * 64
     __nv_bfloat16* v_cache;
     const int64_t* slots;            // kThinRopeKv: [M]
+    const __nv_bfloat16* residual;   // kThinResidual: [M, N], added to the product; out = the new residual stream
+    float* ss_out;                   // kThinResidual: [M, N / 8] sums of squares of out's 8-column pieces
     int M, N, K;
     int n_heads, n_kv_heads, head_dim;
 };
@@ -138,6 +140,9 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
                 e_bias[ps][0] = p.bias[tile * R + nt * 8 + 2 * j];
                 e_bias[ps][1] = p.bias[tile * R + nt * 8 + 2 * j + 1];
             }
+        } else if (EPI == kThinResidual) {
+            e_bias[ps][0] = p.residual[(int64_t)row * p.N + tile * R + nt * 8 + 2 * j];
+            e_bias[ps][1] = p.residual[(int64_t)row * p.N + tile * R + nt * 8 + 2 * j + 1];
         } else {
             const int g = tile * NT + nt, head = g / per_head, d = (g - head * per_head) * 4 + j;   // rotation pair (d, d + half)
             if (p.bias) {
@@ -216,6 +221,35 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
         }
     }
     __syncthreads();
+    if (EPI == kThinResidual) {
+        // new residual = bf16(residual + bf16(x . w^T)), stored where the next layer piece reads it, plus the sum of its
+        // squares over this n-tile's eight columns: the consumer's RMSNorm adds the N / 8 pieces of a row instead of
+        // re-reading the row (the four lanes of a (row, n-tile) item meet by shuffles, so no lane leaves early)
+#pragma unroll
+        for (int ps = 0; ps < PASSES; ++ps) {
+            const int idx = tid + ps * kThinThreads, j = idx & 3, row = (idx >> 2) & (MP - 1), nt = idx / (4 * MP);
+            const bool valid = row < p.M && idx < ITEMS;
+            float lo = 0.f, hi = 0.f;
+            if (idx < ITEMS) {
+#pragma unroll
+                for (int wv = 0; wv < 4; ++wv) {
+                    const float2 v = *reinterpret_cast<const float2*>(c_sm + ((size_t)(wv * NT + nt) * MP + row) * 8 + 2 * j);
+                    lo += v.x;
+                    hi += v.y;
+                }
+            }
+            const float r0 = round_to<__nv_bfloat16>(__bfloat162float(e_bias[ps][0]) + round_to<__nv_bfloat16>(lo));
+            const float r1 = round_to<__nv_bfloat16>(__bfloat162float(e_bias[ps][1]) + round_to<__nv_bfloat16>(hi));
+            float ss = valid ? fmaf(r0, r0, r1 * r1) : 0.f;
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            if (valid) {
+                *reinterpret_cast<uint32_t*>(p.out + (int64_t)row * p.N + tile * R + nt * 8 + 2 * j) = pack_bf16x2(r0, r1);
+                if (j == 0) p.ss_out[(int64_t)row * (p.N / 8) + tile * NT + nt] = ss;
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
         const int idx = tid + ps * kThinThreads, j = idx & 3, row = (idx >> 2) & (MP - 1), nt = idx / (4 * MP);
@@ -273,9 +307,15 @@ __global__ void __launch_bounds__(kThinThreads) thin_gemm_kernel(const ThinParam
 constexpr int kSwTiles = 9;
 constexpr int kSwThreads = 384;
 
-template <int MT>
+// NORM: x is the un-normalised residual stream and the RMSNorm is applied here, in shared memory, before the k-loop:
+// h = ln_w * bf16(x * rsqrt(sum(x^2) / K + eps)) with sum(x^2) handed over as ss_parts pieces per row by the kernel
+// that produced x (ns_thin_gemm_residual). Every CTA normalises its own copy of the rows (M x K elements on twelve warps:
+// about half a microsecond) - less than the separate norm kernel and its boundary cost inside a decode layer.
+template <int MT, bool NORM>
 __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                                                                 __nv_bfloat16* __restrict__ out, int M, int K, int inter) {
+                                                                 __nv_bfloat16* __restrict__ out, int M, int K, int inter,
+                                                                 const float* __restrict__ ss_in, int ss_parts,
+                                                                 const __nv_bfloat16* __restrict__ ln_w, float eps) {
     constexpr int MP = 16 * MT;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -284,6 +324,7 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
     const uint32_t x_sm = smem_u32(smem);                // [MP][pitch]; later the partial tiles [9][4][MP][8] fp32
     const uint32_t w_sm = x_sm + MP * pitch;             // [9 * 8][pitch]
     float* c_sm = reinterpret_cast<float*>(smem);
+    const uint32_t ln_sm = w_sm + kSwTiles * 8 * pitch;  // NORM: [K] bf16 norm weights
     const int n_tiles = inter / 4;
     const int tile0 = blockIdx.x * kSwTiles + grp * 3;   // this warp's first tile
     pdl_launch_dependents();                              // the next kernel's launch latency passes while this one runs
@@ -298,6 +339,10 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
     }
     __syncthreads();
     const uint32_t kbase = (uint32_t)q * (uint32_t)(K / 4) * 2;      // byte offset of this warp's K quarter in a row
+    if (NORM) {                                           // the norm weights are weights too: fetched before the wait, as
+        for (int c = tid; c < K / 8; c += kSwThreads) cp_async16(ln_sm + c * 16, ln_w + c * 8, 16);   // the OLDEST group
+        cp_async_commit();
+    }
     // This warp's quarter of its three tiles' weight rows, before the dependency wait (they stream while the norm runs),
     // in the order the k-loop uses them: one commit group per iteration (32 columns = 64 bytes of each of the 24 rows;
     // lane = (row, 16-byte chunk)), so the loop can start on the first group while the rest is still on its way.
@@ -323,6 +368,33 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
     if (lane < 3) {                                       // token rows over the twelve warps, up to three copies each
         const int m = warp + 12 * lane;
         if (m < M) bulk_g2s(x_sm + m * pitch, x + (int64_t)m * K, (uint32_t)K * 2, mb_x);
+    }
+    float rstd[3] = {0.f, 0.f, 0.f};                      // NORM: of rows warp, warp + 12, warp + 24
+    if (NORM) {
+        // all of a warp's pieces are requested before any is used: one L2 round trip, under the X copies' own
+        float part[3] = {0.f, 0.f, 0.f};
+        if ((ss_parts & 3) == 0) {
+            float4 v[3];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = lane; c < ss_parts / 4; c += 32) {
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+                    if (warp + 12 * i < M) {
+                        const float4 t = *reinterpret_cast<const float4*>(ss_in + (int64_t)(warp + 12 * i) * ss_parts + 4 * c);
+                        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+                    }
+            }
+#pragma unroll
+            for (int i = 0; i < 3; ++i) part[i] = (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        } else {
+            for (int c = lane; c < ss_parts; c += 32)
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+                    if (warp + 12 * i < M) part[i] += ss_in[(int64_t)(warp + 12 * i) * ss_parts + c];
+        }
+#pragma unroll
+        for (int i = 0; i < 3; ++i) rstd[i] = rsqrtf(warp_sum(part[i]) / (float)K + eps);
     }
 
     float acc[3][MT][4];
@@ -369,6 +441,41 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
         Frag f0, f1;
         if (iters > 8) cp_async_wait<7>();                // groups 0 .. iters - 9: the switch above covers the last eight
         if (!mbar_wait_bounded(mb_x, 0) && lane == 0) atomicAdd(&g_thin_errors, 1u);
+        if (NORM) {
+            // every thread waits for its own copies of the norm weights: the oldest group, so the seven youngest (the
+            // weights of the last iterations) may stay in flight
+            cp_async_wait<7>();
+            __syncthreads();
+            // 16 bytes (eight elements) per lane and step; the three rows of a warp side by side for the loads' latency
+            for (int c = lane; c < K / 8; c += 32) {
+                uint4 wv;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w) : "r"(ln_sm + c * 16));
+                uint4 xv[3];
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+                    if (warp + 12 * i < M)
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(xv[i].x), "=r"(xv[i].y), "=r"(xv[i].z), "=r"(xv[i].w)
+                                     : "r"(x_sm + (warp + 12 * i) * pitch + c * 16));
+#pragma unroll
+                for (int i = 0; i < 3; ++i) {
+                    if (warp + 12 * i >= M) continue;
+                    uint32_t* xe = reinterpret_cast<uint32_t*>(&xv[i]);
+                    const uint32_t* we = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&xe[e]);
+                        const __nv_bfloat162 n = __floats2bfloat162_rn(__bfloat162float(v.x) * rstd[i], __bfloat162float(v.y) * rstd[i]);
+                        const __nv_bfloat162 h = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&we[e]), n);
+                        xe[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(x_sm + (warp + 12 * i) * pitch + c * 16), "r"(xv[i].x),
+                                 "r"(xv[i].y), "r"(xv[i].z), "r"(xv[i].w)
+                                 : "memory");
+                }
+            }
+            __syncthreads();
+        }
         wait_for(0);
         load_frag(f0, 0);
         for (int it = 0; it < iters; it += 2) {
@@ -419,18 +526,20 @@ __global__ void __launch_bounds__(kSwThreads) thin_swiglu_kernel(const __nv_bflo
     }
 }
 
-template <int MT>
-int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out, int M, int K, int inter, cudaStream_t st) {
-    const size_t smem = (size_t)(16 * MT + kSwTiles * 8) * ((size_t)K * 2 + 16);
+template <int MT, bool NORM>
+int launch_thin_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out, int M, int K, int inter, const float* ss_in,
+                       int ss_parts, const __nv_bfloat16* ln_w, float eps, cudaStream_t st) {
+    const size_t smem = (size_t)(16 * MT + kSwTiles * 8) * ((size_t)K * 2 + 16) + (NORM ? (size_t)K * 2 : 0);
     static SmemOptIn optin;
     if (optin.needs(smem)) {
-        cudaError_t e = cudaFuncSetAttribute(thin_swiglu_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(thin_swiglu_kernel<MT, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_swiglu_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
         optin.done(smem);
     }
     const int grid = (inter / 4 + kSwTiles - 1) / kSwTiles;
-    cudaError_t e = launch_pdl(thin_swiglu_kernel<MT>, dim3((unsigned)grid), dim3(kSwThreads), smem, st, x, w, out, M, K, inter);
+    cudaError_t e = launch_pdl(thin_swiglu_kernel<MT, NORM>, dim3((unsigned)grid), dim3(kSwThreads), smem, st, x, w, out, M, K, inter,
+                               ss_in, ss_parts, ln_w, eps);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "thin_swiglu_gemm: launch failed: %s", cudaGetErrorString(e));
     return NS_OK;
 }
@@ -523,8 +632,50 @@ extern "C" int ns_thin_swiglu_gemm(const void* x, const void* w, void* out, int3
     NS_REQUIRE(smem <= 227 * 1024 && (size_t)kSwTiles * 4 * mp * 8 * 4 <= (size_t)mp * ((size_t)K * 2 + 16), NS_ERR_UNSUPPORTED,
                "thin_swiglu_gemm: K=%d does not fit shared memory (72 weight rows + %d token rows)", K, mp);
     cudaStream_t st = (cudaStream_t)stream;
-    if (M <= 16) return launch_thin_swiglu<1>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
-    return launch_thin_swiglu<2>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, st);
+    if (M <= 16) return launch_thin_swiglu<1, false>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, nullptr, 0, nullptr, 0.f, st);
+    return launch_thin_swiglu<2, false>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, nullptr, 0, nullptr, 0.f, st);
+}
+
+extern "C" int ns_thin_gemm_residual(const void* x, const void* w, const void* residual, void* out, float* ss_out, int32_t M,
+                                     int32_t N, int32_t K, void* stream) {
+    NS_REQUIRE(M >= 0 && N > 0 && K > 0, NS_ERR_INVALID_ARG, "thin_gemm_residual: bad shape");
+    if (M == 0) return NS_OK;
+    NS_REQUIRE(x && w && residual && out && ss_out, NS_ERR_INVALID_ARG, "thin_gemm_residual: null pointer");
+    NS_REQUIRE(M <= 64, NS_ERR_UNSUPPORTED, "thin_gemm_residual: %d token rows > 64", M);
+    NS_REQUIRE(K % 128 == 0 && N % 8 == 0, NS_ERR_UNSUPPORTED, "thin_gemm_residual: K=%d must be a multiple of 128 and N=%d of 8", K, N);
+    NS_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 3) == 0,
+               NS_ERR_INVALID_ARG, "thin_gemm_residual: x / w must be 16-byte aligned, out / residual 4-byte aligned");
+    const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    NS_REQUIRE(thin_smem(mp, thin_ntiles(N), K) <= 220 * 1024, NS_ERR_UNSUPPORTED,
+               "thin_gemm_residual: %d token rows + %d weight rows of K=%d do not fit shared memory", mp, kThinRows * thin_ntiles(N), K);
+    ThinParams p = {};
+    p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.out = (__nv_bfloat16*)out;
+    p.residual = (const __nv_bfloat16*)residual; p.ss_out = ss_out;
+    p.M = M; p.N = N; p.K = K;
+    return dispatch_thin<kThinResidual>(p, (cudaStream_t)stream);
+}
+
+extern "C" int ns_thin_swiglu_gemm_norm(const void* x, const float* ss_in, int32_t ss_parts, const void* ln_w, float eps,
+                                        const void* w, void* out, int32_t M, int32_t inter, int32_t K, void* stream) {
+    NS_REQUIRE(M >= 0 && inter > 0 && K > 0 && ss_parts > 0, NS_ERR_INVALID_ARG, "thin_swiglu_gemm_norm: bad shape");
+    if (M == 0) return NS_OK;
+    NS_REQUIRE(x && w && out && ss_in && ln_w, NS_ERR_INVALID_ARG, "thin_swiglu_gemm_norm: null pointer");
+    NS_REQUIRE(M <= 32, NS_ERR_UNSUPPORTED, "thin_swiglu_gemm_norm: %d token rows > 32", M);
+    NS_REQUIRE(K % 128 == 0 && inter % 4 == 0, NS_ERR_UNSUPPORTED, "thin_swiglu_gemm_norm: K=%d must be a multiple of 128 and inter=%d of 4", K, inter);
+    NS_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(ln_w)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 7) == 0,
+               NS_ERR_INVALID_ARG, "thin_swiglu_gemm_norm: x / w / ln_w must be 16-byte aligned, out 8-byte aligned");
+    const int mp = M <= 16 ? 16 : 32;
+    const size_t smem = (size_t)(mp + kSwTiles * 8) * ((size_t)K * 2 + 16) + (size_t)K * 2;
+    NS_REQUIRE(smem <= 227 * 1024 && (size_t)kSwTiles * 4 * mp * 8 * 4 <= (size_t)mp * ((size_t)K * 2 + 16), NS_ERR_UNSUPPORTED,
+               "thin_swiglu_gemm_norm: K=%d does not fit shared memory (72 weight rows + %d token rows)", K, mp);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M <= 16)
+        return launch_thin_swiglu<1, true>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, ss_in,
+                                           ss_parts, (const __nv_bfloat16*)ln_w, eps, st);
+    return launch_thin_swiglu<2, true>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, K, inter, ss_in, ss_parts,
+                                       (const __nv_bfloat16*)ln_w, eps, st);
 }
 
 namespace ns {

@@ -206,6 +206,44 @@ def thin_swiglu_gemm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def thin_gemm_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """residual + x[M<=64, K] @ w[N, K]^T (the new residual stream, bf16 [M, N]) and the sums of squares of its rows'
+    8-column pieces (fp32 [M, N / 8]) for thin_swiglu_gemm's norm prologue (ns_thin_gemm_residual in the header)."""
+    _lib.require_cuda(x, w, residual)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16
+    M, K = x.shape
+    N = w.shape[0]
+    assert residual.shape == (M, N) and residual.is_contiguous()
+    out = torch.empty(M, N, device=x.device, dtype=x.dtype)
+    ss = torch.empty(M, N // 8, device=x.device, dtype=torch.float32)
+    _lib.call("ns_thin_gemm_residual", x.data_ptr(), w.data_ptr(), residual.data_ptr(), out.data_ptr(), ss.data_ptr(), M, N, K,
+              _lib.stream_ptr())
+    return out, ss
+
+
+def thin_swiglu_gemm_norm(x: torch.Tensor, ss: torch.Tensor, ln_w: torch.Tensor, eps: float, w: torch.Tensor) -> torch.Tensor:
+    """thin_swiglu_gemm on RMSNorm(x) * ln_w, the norm applied inside the kernel from the row pieces `ss` that
+    thin_gemm_residual left (ns_thin_swiglu_gemm_norm in the header); x [M<=32, K] is the un-normalised residual stream."""
+    _lib.require_cuda(x, ss, ln_w, w)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.is_contiguous() and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ln_w.dtype == torch.bfloat16 and w.shape[0] % 2 == 0
+    assert ss.dtype == torch.float32 and ss.dim() == 2 and ss.shape[0] == x.shape[0] and ss.is_contiguous()
+    M, K = x.shape
+    assert ln_w.shape == (K,) and ln_w.is_contiguous()
+    inter = w.shape[0] // 2
+    out = torch.empty(M, inter, device=x.device, dtype=x.dtype)
+    _lib.call("ns_thin_swiglu_gemm_norm", x.data_ptr(), ss.data_ptr(), ss.shape[1], ln_w.data_ptr(), float(eps), w.data_ptr(),
+              out.data_ptr(), M, inter, K, _lib.stream_ptr())
+    return out
+
+
+def thin_swiglu_gemm_norm_supported(M: int, inter: int, K: int) -> bool:
+    """thin_swiglu_gemm_supported with room for the K norm weights in shared memory as well."""
+    mp = 16 if M <= 16 else 32
+    return thin_swiglu_gemm_supported(M, inter, K) and (mp + 72) * (2 * K + 16) + 2 * K <= 227 * 1024
+
+
 def thin_gemm_errors() -> int:
     """Bulk copies of ns_thin_swiglu_gemm that did not land within the kernel's bounded wait since the library was
     loaded (synchronises; 0 unless the device faulted)."""

@@ -333,7 +333,8 @@ class Qwen2Model:
         from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
                                                   rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
                                                   sm_count, swiglu_gemm_supported, thin_gemm, thin_gemm_ctas, thin_gemm_supported, thin_swiglu_gemm,
-                                                  thin_swiglu_gemm_supported)
+                                                  thin_swiglu_gemm_supported, thin_gemm_residual, thin_swiglu_gemm_norm,
+                                                  thin_swiglu_gemm_norm_supported)
         from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
         cfg, eps = self.cfg, self.cfg.rms_norm_eps
         nh, nkv, hd = cfg.n_heads // self.tp_size, cfg.n_kv_heads // self.tp_size, cfg.head_dim
@@ -374,6 +375,11 @@ class Qwen2Model:
         thin_o = (skinny and bool(mask & 128) and thin_gemm_ctas(hidden) <= sm_count() and (nh * hd) % 128 == 0 and
                   thin_gemm_supported(T, hidden, nh * hd))
         thin_gu = skinny and bool(mask & 256) and thin_swiglu_gemm_supported(T, inter, hidden)      # bit 8: gate/up + SiLU*mul
+        # bit 9: where both o_proj and gate/up run on the 8-row-tile kernels, the residual add moves into o_proj's epilogue
+        # and the RMSNorm into gate/up's prologue (one kernel and one launch boundary less per layer); not with tensor
+        # parallelism, whose all-reduce sits between the two
+        fold_norm = (thin_o and thin_gu and bool(mask & 512) and self.tp_group is None and
+                     thin_swiglu_gemm_norm_supported(T, inter, hidden))
         # The attention plan (one CTA, ~14 us) depends only on the step metadata and is first needed by layer 0's
         # attention: it runs on a second stream next to the RoPE tables, the embedding, the first norm and the first QKV
         # GEMM (inside a capture this becomes a fork and a join in the graph).
@@ -410,7 +416,10 @@ class Qwen2Model:
                                        n_seqs=meta.n_seqs, table_rows=meta.table_rows, workspace=meta.workspace,
                                        planned=True)
             o2 = o.view(T, nh * hd)
-            if thin_o:
+            if fold_norm:
+                x, ss = thin_gemm_residual(o2, layer.o_w, x)
+                m = thin_swiglu_gemm_norm(x, ss, layer.ln2, eps, layer.gate_up_w)
+            elif thin_o:
                 a = thin_gemm(o2, layer.o_w)
             elif stream_o:
                 a = stream_gemm(o2, layer.o_w)
@@ -422,7 +431,7 @@ class Qwen2Model:
                 h, x = peer.reduce_add_rmsnorm(0, T, x, layer.ln2, eps)
             else:
                 a = F.linear(o2, layer.o_w)
-            if peer is not None and a is None:
+            if fold_norm or (peer is not None and a is None):
                 pass
             elif peer is not None:
                 peer.partial(0, T).copy_(a)                 # (a GEMM kernel of this library: its output is copied over)
@@ -430,7 +439,9 @@ class Qwen2Model:
             else:
                 a = self._all_reduce(a)
                 h, x = norm(a, layer.ln2, eps, residual=x)
-            if thin_gu:
+            if fold_norm:
+                pass
+            elif thin_gu:
                 m = thin_swiglu_gemm(h, layer.gate_up_w)
             elif umma_gu:
                 m = swiglu_gemm(h, layer.gate_up_w)

@@ -2,6 +2,7 @@
 
     python -m nanoserve_b200.probes --launch-probe          # 2 decode steps at c=32 + 1 mixed step inside a profiler range
     python -m nanoserve_b200.probes --layer-probe 32        # marginal cost of each kernel of a decode layer, 32 rows
+    python -m nanoserve_b200.probes --mixed-layer-probe 512 # what the separate token-wise kernels cost in a 512-row layer
     python -m nanoserve_b200.probes --attn-overlap-probe    # prefill kernel after / beside the decode kernel
     python -m nanoserve_b200.probes --attn-alone-probe      # one decode attention call alone, cluster mode on / off
     python -m nanoserve_b200.probes --fused-ops 2048        # the token-wise fused ops at a 2048-token step, GB/s each
@@ -98,7 +99,8 @@ def layer_probe(rows: int) -> None:
     import torch.nn.functional as F
     from nanoserve_b200 import _lib
     from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, rms_norm, rope_cos_sin, silu_mul, skinny_gemm,
-                                              stream_gemm, swiglu_gemm, thin_gemm, thin_swiglu_gemm)
+                                              stream_gemm, swiglu_gemm, thin_gemm, thin_gemm_residual, thin_swiglu_gemm,
+                                              thin_swiglu_gemm_norm)
     from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
     from nanoserve_b200.synthetic import attention_workload
     M, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
@@ -128,12 +130,20 @@ def layer_probe(rows: int) -> None:
                 q = ragged_paged_attention(q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, None, 0.125, workspace=ws,
                                            planned=True)
             o2 = q.view(M, H)
-            a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else (thin_gemm(o2, l["o"]) if o == "thin" else o2))
-            if norm1:
+            if o == "fold":                # residual add in o_proj's epilogue, the norm in gate/up's prologue
+                x, ss = thin_gemm_residual(o2, l["o"], x)
+                a = None
+            else:
+                a = F.linear(o2, l["o"]) if o == "cublas" else (stream_gemm(o2, l["o"]) if o == "stream" else (thin_gemm(o2, l["o"]) if o == "thin" else o2))
+            if o == "fold":
+                pass
+            elif norm1:
                 h, x = rms_norm(a, l["ln"], 1e-6, residual=x)
             else:
                 h = a
-            if gu == "cublas":
+            if o == "fold":
+                m = thin_swiglu_gemm_norm(x, ss, l["ln"], 1e-6, l["gu"])
+            elif gu == "cublas":
                 m = silu_mul(F.linear(h, l["gu"]))
             elif gu == "umma":
                 m = swiglu_gemm(h, l["gu"])
@@ -179,6 +189,7 @@ def layer_probe(rows: int) -> None:
                 "gate_up on stream_gemm": e(gu="stream"), "gate_up on swiglu_gemm (tcgen05)": e(gu="umma"),
                 "qkv on skinny_gemm (split-K cluster)": e(qkv="skinny"), "o_proj on cublas": e(o="cublas"),
                 "o_proj on stream_gemm": e(o="stream"), "down on cublas": e(down="cublas"),
+                "residual add folded into o_proj, first norm into gate_up (thin kernels)": e(o="fold", gu="thin"),
                 "before the 8-row-tile kernels: qkv and down_proj on skinny_gemm, o_proj and gate_up on cublas": {}}
     def try_variant(kw):
         try:
@@ -197,6 +208,87 @@ def layer_probe(rows: int) -> None:
     hook(0)
     out["attention_us_per_layer_by_min_blocks_per_cta"] = sweep
     print(json.dumps(out))
+
+
+def mixed_layer_probe(rows: int) -> None:
+    """What the separate token-wise kernels cost in a layer of a LARGE step (a prefill chunk of `rows` tokens on a
+    cached context of 512, Qwen2.5-0.5B shape): 24 layers of {QKV library GEMM with bias, RoPE + KV write kernel, prefill
+    attention, o_proj GEMM, add + RMSNorm, gate/up GEMM, SiLU*mul kernel, down_proj GEMM, add + RMSNorm} in one CUDA graph,
+    then the same chain with one token-wise kernel left out at a time (its consumer reads a buffer of the right shape
+    instead). Prints us per layer of each variant: an upper bound on what fusing that kernel into a GEMM epilogue can
+    save."""
+    import torch.nn.functional as F
+    from nanoserve_b200.kernels.fused import rms_norm, rope_cos_sin, rope_qkv, silu_mul
+    from nanoserve_b200.kernels.paged_attention import AttnWorkspace, ragged_paged_attention
+    from nanoserve_b200.synthetic import attention_workload
+    T, H, I, L, dev, bf = rows, 896, 4864, 24, "cuda", torch.bfloat16
+    W = [dict(qkv=torch.randn(1152, H, device=dev, dtype=bf) * .02, b=torch.randn(1152, device=dev, dtype=bf) * .02,
+              o=torch.randn(H, H, device=dev, dtype=bf) * .02, gu=torch.randn(2 * I, H, device=dev, dtype=bf) * .02,
+              down=torch.randn(H, I, device=dev, dtype=bf) * .02, ln=torch.ones(H, device=dev, dtype=bf)) for _ in range(L)]
+    w = attention_workload(n_decode=0, n_prefill=1, chunk=T, prefill_ctx_range=(512, 512), num_blocks=4096)
+    ws = AttnWorkspace(64, T, 14, 64, dev)
+    ws.plan(w.seq_lens, w.cu_seqlens, 1, 16)
+    inv = (1.0 / (1e6 ** (torch.arange(0, 64, 2, dtype=torch.float) / 64))).to(dev)
+    cos, sin = rope_cos_sin(torch.arange(512, 512 + T, device=dev), inv, 64, bf)
+    x0 = torch.randn(T, H, device=dev, dtype=bf)
+    q0 = torch.randn(T, 14, 64, device=dev, dtype=bf)
+    m0 = torch.randn(T, I, device=dev, dtype=bf)
+
+    def chain(rope=True, silu=True, norm1=True, norm2=True, attn=True, gemms=True):
+        x = h = x0
+        for l in W:
+            qkv = F.linear(h, l["qkv"], l["b"]) if gemms else None
+            q = rope_qkv(qkv, cos, sin, 14, 2, 64, w.k_pool, w.v_pool, w.slot_mapping, dense_kv=False)[0] if rope and gemms else q0
+            if attn:
+                q = ragged_paged_attention(q, w.k_pool, w.v_pool, w.block_tables, w.seq_lens, w.cu_seqlens, 0.125, workspace=ws,
+                                           planned=True)
+            a = F.linear(q.view(T, H), l["o"]) if gemms else x0
+            if norm1:
+                h, x = rms_norm(a, l["ln"], 1e-6, residual=x)
+            else:
+                h = a
+            gu = F.linear(h, l["gu"]) if gemms else None
+            m = silu_mul(gu) if silu and gemms else m0
+            d = F.linear(m, l["down"]) if gemms else x0
+            if norm2:
+                h, x = rms_norm(d, l["ln"], 1e-6, residual=x)
+            else:
+                h = d
+        return h
+
+    def us_per_layer(**kw) -> float:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain(**kw)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            chain(**kw)
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3 / L)
+        return round(sorted(ts)[2], 2)
+
+    full = us_per_layer()
+    res = {"the engine's chain for this step size": full,
+           "without the RoPE + KV write kernel": us_per_layer(rope=False),
+           "without the SiLU*mul kernel": us_per_layer(silu=False),
+           "without the first add + RMSNorm": us_per_layer(norm1=False),
+           "without the second add + RMSNorm": us_per_layer(norm2=False),
+           "without attention": us_per_layer(attn=False),
+           "the four library GEMMs alone": us_per_layer(rope=False, silu=False, norm1=False, norm2=False, attn=False)}
+    flops = 2 * T * (1152 * H + H * H + 2 * I * H + H * I)
+    tokenwise = sum(full - res[k] for k in list(res)[1:5])
+    print(json.dumps({"rows": T, "us_per_layer": res, "gemm_tflops_alone": round(flops / res["the four library GEMMs alone"] / 1e6, 1),
+                      "token_wise_kernels_us": round(tokenwise, 2), "token_wise_share": round(tokenwise / full, 3)}))
 
 
 def fused_ops_probe(tokens: int, reps: int = 20) -> None:
@@ -358,6 +450,7 @@ def main() -> None:
     ap.add_argument("--attn-overlap-probe", action="store_true")
     ap.add_argument("--attn-alone-probe", action="store_true")
     ap.add_argument("--layer-probe", type=int, default=0, metavar="ROWS")
+    ap.add_argument("--mixed-layer-probe", type=int, default=0, metavar="ROWS")
     ap.add_argument("--fused-ops", type=int, default=0, metavar="TOKENS")
     ap.add_argument("--decode-step-probe", default="", metavar="SHAPE", help="e.g. qwen2.5-7b")
     ap.add_argument("--rows", type=int, default=64)
@@ -369,6 +462,8 @@ def main() -> None:
         launch_probe()
     elif args.layer_probe:
         layer_probe(args.layer_probe)
+    elif args.mixed_layer_probe:
+        mixed_layer_probe(args.mixed_layer_probe)
     elif args.attn_overlap_probe:
         attn_overlap_probe()
     elif args.attn_alone_probe:

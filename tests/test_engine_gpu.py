@@ -285,7 +285,7 @@ def test_config0_fp32_greedy_tokens_match_the_reference():
     assert free == total - 1
 
 
-@pytest.mark.parametrize("gemm_mask", [None, "0", "3", "27", "195", "451"])
+@pytest.mark.parametrize("gemm_mask", [None, "0", "3", "27", "195", "451", "963"])
 def test_config0_bf16_greedy_tokens_tie_rule(gemm_mask, monkeypatch):
     """Benchmark configuration 0 (0.5B shape, 8 requests x 64 greedy tokens) on the bf16 graph path. Two checks over
     the first 32 generated tokens: (1) every logits row computed on the reference's context is within LOGIT_TOL_BF16
@@ -294,7 +294,8 @@ def test_config0_bf16_greedy_tokens_tie_rule(gemm_mask, monkeypatch):
     error measured in this run, the largest gap an error of that size can flip. Run with the engine's default choice of decode-GEMM kernels (None)
     and with each other choice forced for every decode-sized step: 0 = library GEMMs + the separate RoPE / SiLU
     kernels, 3 = split-K cluster kernel for QKV and down_proj, 27 = + streaming kernel for gate/up and o_proj, 195 =
-    8-row-tile kernel for QKV and o_proj, 451 = + 8-row-tile gate/up with SiLU*mul."""
+    8-row-tile kernel for QKV and o_proj, 451 = + 8-row-tile gate/up with SiLU*mul, 963 = + the residual add in o_proj's
+    epilogue and the RMSNorm in gate/up's prologue."""
     if gemm_mask is not None:
         monkeypatch.setenv("NS_SKINNY_MASK", gemm_mask)
         monkeypatch.setenv("NS_SKINNY_MASK_SMALL", gemm_mask)

@@ -276,3 +276,24 @@ def test_decode_small_steps_in_cluster_mode_match_oracle(n_heads, n_kv, hd, rows
                 assert err <= 1e-2, (on, err)
     finally:
         _lib.set_tuning(_lib.TUNE_DECODE_CLUSTER, 1)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(14, 2, 64), (12, 2, 128)])
+@pytest.mark.parametrize("case", range(len(MIXED)))
+def test_unused_pool_slots_may_hold_anything(n_heads, n_kv, hd, case):
+    """The reference allocates its pools uninitialised: slots at or past a sequence's length (the tail of its last block)
+    and blocks no table names may hold NaN bit patterns. Whole blocks are copied to shared memory, so the kernels must
+    not let such a slot reach an output (0 x NaN): every such slot is poisoned here and the result is the oracle's."""
+    from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
+    ctx_lens, q_lens = MIXED[case]
+    q, k, v, tables, lens, cu = make_case(n_heads, n_kv, hd, ctx_lens, torch.bfloat16, q_lens, seed=21 + case)
+    ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, hd ** -0.5)
+    live = torch.zeros(k.shape[0], 16, dtype=torch.bool)
+    for i, L in enumerate(ctx_lens):
+        for pos in range(L):
+            live[tables[i, pos // 16], pos % 16] = True
+    k[~live] = float("nan")
+    v[~live] = float("nan")
+    out = ragged_paged_attention(*dev(q, k, v, tables, lens, cu), hd ** -0.5).float().cpu()
+    assert torch.isfinite(out).all()
+    assert (out - ref).abs().max().item() <= 1e-2

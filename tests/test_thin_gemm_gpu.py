@@ -108,3 +108,46 @@ def test_gate_up_rejects_what_it_cannot_run():
     with pytest.raises(NanoserveB200Error):
         thin_swiglu_gemm(torch.zeros(8, 1536, dtype=torch.bfloat16, device="cuda"),
                          torch.zeros(2 * 64, 1536, dtype=torch.bfloat16, device="cuda"))             # K too wide for shared memory
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 17, 29, 32, 64])
+@pytest.mark.parametrize("N,K", [(896, 896), (200, 256), (1536, 1536)])
+def test_residual_epilogue_and_row_pieces(M, N, K):
+    """o_proj with the residual add in its epilogue: the new residual stream against the unfused ops, and the sums of
+    squares of its rows' 8-column pieces against the kernel's OWN output (exact up to fp32 summation order: 1e-5 rel)."""
+    from nanoserve_b200.kernels.fused import thin_gemm_residual, thin_gemm_supported
+    if not thin_gemm_supported(M, N, K):
+        pytest.skip("shape outside the kernel's shared-memory budget")
+    g = torch.Generator().manual_seed(M * 31 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    res = (torch.randn(M, N, generator=g) * 2).to(torch.bfloat16)
+    out, ss = thin_gemm_residual(x.cuda(), w.cuda(), res.cuda())
+    want = (res.float() + lin(x, w).float()).to(torch.bfloat16)
+    close(out, want, min_same=0.97)
+    pieces = out.float().cpu().view(M, N // 8, 8).pow(2).sum(-1)
+    assert ss.shape == (M, N // 8)
+    torch.testing.assert_close(ss.cpu(), pieces, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 17, 24, 32])
+@pytest.mark.parametrize("inter,K", [(4864, 896), (100, 128), (36 * 5 + 8, 256), (4864, 1024)])
+def test_gate_up_with_the_norm_in_its_prologue(M, inter, K):
+    """o_proj + residual -> (norm inside) gate/up + SiLU*mul, against the oracle's rms_norm and silu_mul on the SAME new
+    residual stream the first kernel produced: the norm's bf16 rounding points are the unfused ops'; the row's sum of
+    squares is added in another order (a last-bit difference of rstd can move a bf16 element by one ulp)."""
+    from nanoserve_b200.kernels.fused import (thin_gemm_errors, thin_gemm_residual, thin_swiglu_gemm_norm,
+                                              thin_swiglu_gemm_norm_supported)
+    if not thin_swiglu_gemm_norm_supported(M, inter, K):
+        pytest.skip("shape outside the kernel's shared-memory budget")
+    g = torch.Generator().manual_seed(M * 11 + inter)
+    o = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ow = (torch.randn(K, K, generator=g) * 0.02).to(torch.bfloat16)
+    res = (torch.randn(M, K, generator=g) * 2).to(torch.bfloat16)
+    ln = (1 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, generator=g) * 0.02).to(torch.bfloat16)
+    x, ss = thin_gemm_residual(o.cuda(), ow.cuda(), res.cuda())
+    got = thin_swiglu_gemm_norm(x, ss, ln.cuda(), 1e-6, w.cuda())
+    h = O.rms_norm(x.cpu(), ln, 1e-6)
+    close(got, O.silu_mul(lin(h, w)), min_same=0.96)
+    assert thin_gemm_errors() == 0
