@@ -354,11 +354,19 @@ class Qwen2Model:
         #   bit 5 gate/up + SiLU*mul on the tcgen05 + TMA kernel (ns_swiglu_gemm; measured slower, never a default);
         #   bit 6 QKV (+RoPE, KV write), 7 o_proj on the 8-row-tile kernel without split-K (ns_thin_gemm; wins over bits
         #         1, 2 and 4), bit 8 gate/up + SiLU*mul on the same construction (ns_thin_swiglu_gemm, up to 32 rows).
-        # Defaults from measurements inside a decode layer and at engine level: 8-row-tile kernels for QKV, o_proj and (17..32
-        # rows) gate/up; up to 16 rows the streaming kernel for gate/up; down_proj on the split-K kernel; a GEMM whose
-        # kernel does not take the step's shape falls back to the next choice and finally to F.linear.
-        if T <= 16:
+        #   bit 9 (with bits 7 and 8): the residual add in o_proj's epilogue and the RMSNorm in gate/up's prologue
+        #         (ns_thin_gemm_residual + ns_thin_swiglu_gemm_norm) instead of the add + RMSNorm kernel between them.
+        # Defaults from measurements of whole decode steps: up to 4 rows the streaming kernel for gate/up and o_proj's
+        # 8-row-tile kernel (219); 5..16 rows the 8-row-tile kernels everywhere with the norm folded in, the streaming kernel
+        # where a shape does not fit them (987); 17..32 rows
+        # the same without the fold, which gains nothing there (451); down_proj on the split-K kernel throughout; a GEMM
+        # whose kernel does not take the step's shape falls back to the next choice and finally to F.linear.
+        # (decode steps of 24 layers at 1 / 4 / 8 / 16 / 32 rows: 664 / 670 / 687 / 735 / - us with 219, 675 / 679 / 681 / 711 / 785
+        # with 451, 703 at 16 and 784 at 32 rows with 963)
+        if T <= 4:
             mask = int(os.environ.get("NS_SKINNY_MASK_SMALL", os.environ.get("NS_SKINNY_MASK", "219")))
+        elif T <= 16:
+            mask = int(os.environ.get("NS_SKINNY_MASK_SMALL", os.environ.get("NS_SKINNY_MASK", "987")))
         else:
             mask = int(os.environ.get("NS_SKINNY_MASK", "451"))
         skinny_down = skinny_down and bool(mask & 1)
