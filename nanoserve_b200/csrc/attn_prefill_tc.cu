@@ -4,10 +4,10 @@
 // 128 rows of one UMMA tile (row r = token r/8, head r%8), so Q.K^T and P.V are dense 128-row contractions even
 // though each sequence contributes few tokens per head. head_dim HD = 64 or 128.
 //   S[128 x 64]  = Q[128 x HD] . K_tile[64 keys x HD]^T     tcgen05.mma kind::f16, A and B K-major, SWIZZLE_128B
-//   PV[128 x HD] = P[128 x 64 keys] . V_tile[64 keys x HD]  A K-major (P written to shared memory as bf16),
+//   O[128 x HD] += P[128 x 64 keys] . V_tile[64 keys x HD]  A K-major (P written to shared memory as bf16),
 //                                                            B MN-major (V rows are the pool's rows, untransposed)
 // Three roles (192 threads):
-//   warps 0-3  one softmax thread per row (lane = row of tensor memory): S(j) -> P(j), o = o * alpha + PV(j-1)
+//   warps 0-3  one softmax thread per row (lane = row of tensor memory): S(j) -> P(j)
 //   warp 4     lane 0 issues every tcgen05.mma with PRECOMPUTED descriptors (a tcgen05.mma of this size occupies the
 //              tensor pipe for ~50 cycles; building two 64-bit descriptors per instruction in a lone thread cost three
 //              times that)
@@ -15,11 +15,13 @@
 //              tokens and 128-byte atom from a 4-D tensor map over THIS GPU's pool [head_dim, kv head, position, block],
 //              128-byte swizzle, K three tiles deep and V four; a stage is refilled when the MMA that read it has
 //              committed (tcgen05.commit -> mbarrier). The softmax threads never touch K or V.
-// Pipeline over the key tiles (S, PV and P double buffered): S runs two tiles ahead,
-//   iteration j:  softmax(j) from tensor memory -> P(j) in shared memory | one 160-thread barrier | issue PV(j), S(j+2)
-//                 | o = o * alpha(j-1) + PV(j-1)
-// so the tensor cores compute PV(j-1) and S(j+1) while the threads are in softmax(j). Tiles wholly below every row's
-// causal limit skip the mask. Rows of a sequence's last V tile at or past its length are zeroed in shared memory (a block's
+// Pipeline over the key tiles (S and P double buffered, the output O single): S runs two tiles ahead,
+//   softmax thread, tile j:  wait S(j) | 64 scores into registers | max | (rescale O) | exp, sum, P(j) to shared memory
+//                            | arrive on "P(j) ready" - and on to tile j+1 without waiting for the other rows
+//   issuing lane, tile j:    wait until all 128 rows delivered P(j) | issue PV(j) (O += P.V in tensor memory), S(j+2)
+// so the tensor cores compute PV(j-1) and S(j+1) while the threads are in softmax(j). O stays in tensor memory: it is
+// rescaled only when a row's maximum outgrew the exponent's reference by more than 2^8 (see the kernel), and read once
+// at the end. No CTA-wide barrier inside the loop. Tiles wholly below every row's causal limit skip the mask. Rows of a sequence's last V tile at or past its length are zeroed in shared memory (a block's
 // unused slots may hold anything, and 0 x NaN would poison the row). Every mbarrier wait is bounded: on expiry the CTA
 // counts an error in the plan header (ns_collect_status), skips its stores, waits for its copies in flight, frees its
 // tensor memory and returns.
@@ -36,13 +38,12 @@ namespace tc {
 
 constexpr int kRows = 128;          // UMMA M = softmax threads (one per row)
 constexpr int kThreads = kRows + 64; // + one warp whose first lane issues every tcgen05.mma + one whose first lane copies
-constexpr int kSyncThreads = kRows + 32;   // softmax threads + issuing warp meet once per tile (named barrier 1)
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
 constexpr int kStagesK = 3;         // K tiles in shared memory (S runs two tiles ahead of the tile in softmax)
 constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) when K(j)'s buffer is long free
-// mbarriers: S0 S1 PV0 PV1 | K full x3 | V full x4 | K free x3 | V free x4
+// mbarriers: S0 S1 PV0 PV1 | K full x3 | V full x4 | K free x3 | V free x4 | P0 P1 ready (one arrival per softmax thread)
 constexpr int kBarS = 0, kBarPV = 2, kBarKFull = 4, kBarVFull = kBarKFull + kStagesK, kBarKFree = kBarVFull + kStagesV,
-              kBarVFree = kBarKFree + kStagesK, kBars = kBarVFree + kStagesV;
+              kBarVFree = kBarKFree + kStagesK, kBarPReady = kBarVFree + kStagesV, kBars = kBarPReady + 2;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kDefaultCluster = 1;  // CTAs sharing one work item's key tiles (see launch_prefill_tc_hd)
 
@@ -132,20 +133,8 @@ __device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* 
         : "memory");
 }
 
-// Named barrier 1 over the softmax threads and the issuing warp, AND-reducing `ok`.
-__device__ __forceinline__ bool tile_barrier_and(bool ok) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 1, %2, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(r)
-        : "r"((uint32_t)ok), "r"(kSyncThreads)
-        : "memory");
-    return r != 0;
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar_saddr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_saddr) : "memory");
 }
 
 // 32 consecutive fp32 columns of this thread's TMEM lane, requested only: tmem_ld_wait() before the values are used.
@@ -230,7 +219,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < kBars; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar(i)) : "memory");
+        for (int i = 0; i < kBars; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar(i)), "r"(i >= kBarPReady ? kRows : 1) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_flag = 0;
     }
@@ -302,7 +292,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             v_issued = kt + 1;
         }
         if (!ok) abort_flag = 1;
-    } else if (warp <= 4) {
+    } else if (issuer) {
         // ---- descriptors, built once: an instruction's operand is the base plus a byte offset (>> 4) in the address field
         constexpr uint32_t idesc_s = instr_desc(false, kKeys), idesc_pv = instr_desc(true, HD);
         const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
@@ -337,15 +327,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             mma_commit(bar(kBarVFree + sv));
         };
 
+        // S(0) and S(1) first; then, per tile, PV(kt) and S(kt + 2) as soon as every softmax thread has delivered P(kt) -
+        // which also says that each of them has read S(kt) for the last time and left the output alone
+        if (n_tiles > 0) issue_s(0);
+        if (n_tiles > 1) issue_s(1);
+        for (int kt = 0; kt < n_tiles && ok; ++kt) {
+            if (!mbar_wait_or_abort(bar(kBarPReady + (kt & 1)), (uint32_t)((kt >> 1) & 1), &abort_flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_pv(kt);
+            if (kt + 2 < n_tiles) issue_s(kt + 2);
+        }
+        if (!ok) abort_flag = 1;
+    } else if (worker) {
         const int limit = ctx + tok;      // last key this row may see
         const uint32_t t_o = t_lane + COL_O;
-
-        // prologue: S(0) and S(1) under way
-        if (issuer) {
-            if (n_tiles > 0) issue_s(0);
-            if (n_tiles > 1) issue_s(1);
-        }
-        __syncwarp();
+        const volatile uint32_t* abort_now = &abort_flag;
 
 #ifdef NS_DEBUG_HOOKS
         // profiling build: clock64 stamps of the first work item's thread 0, 8 per key tile, first 16 tiles
@@ -356,8 +352,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 #endif
         for (int kt = 0; kt < n_tiles; ++kt) {
             NS_STAMP(0);
-            if (worker) {
-                if (!mbar_wait(bar(kBarS + (kt & 1)), (uint32_t)((kt >> 1) & 1))) ok = false;
+            if (*abort_now) ok = false;                                    // another thread's wait ran out
+            if (!ok) break;
+            {
+                if (!mbar_wait(bar(kBarS + (kt & 1)), (uint32_t)((kt >> 1) & 1))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 NS_STAMP(1);
 
@@ -462,16 +460,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of P (and V's tail) -> the MMA
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            ok = tile_barrier_and(ok);
-            if (!ok) break;
+            if (!ok) break;                                                // (no arrival: the issuing thread gives up on the flag)
+            mbar_arrive(bar(kBarPReady + (kt & 1)));                       // no softmax thread waits for another one
             NS_STAMP(4);
-            if (issuer) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_pv(kt);                                              // P(kt) is complete, the output is where the softmax left it
-                if (kt + 2 < n_tiles) issue_s(kt + 2);                     // S buffer kt & 1 has just been read for the last time
-            }
-            __syncwarp();                                                  // the issuing warp meets the next tile's barrier as one
-            NS_STAMP(5);
         }
         if (!ok) abort_flag = 1;                                           // (every thread that saw a failure writes the same value)
     }
