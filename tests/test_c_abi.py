@@ -61,6 +61,15 @@ def test_decode_gemm_entry_points_validate_before_touching_the_device():
     assert lib.ns_thin_swiglu_gemm(x, w, out, 8, 4866, 896, nul) == UNSUPPORTED
     assert lib.ns_skinny_gemm(x, nul, nul, nul, w, nul, out, 65, 896, 896, 8, ctypes.c_float(1e-6), 0, 0, nul, nul, nul, nul, nul,
                               0, 0, nul) == UNSUPPORTED and "65 token rows" in msg()
+    ss, eps = ctypes.cast(P(2048), ctypes.POINTER(ctypes.c_float)), ctypes.c_float(1e-6)
+    assert lib.ns_thin_gemm_residual(x, w, x, out, ss, 0, 896, 896, nul) == 0                                  # empty step
+    assert lib.ns_thin_gemm_residual(x, w, nul, out, ss, 8, 896, 896, nul) == INVALID and "null pointer" in msg()
+    assert lib.ns_thin_gemm_residual(x, w, x, out, ss, 65, 896, 896, nul) == UNSUPPORTED and "65 token rows" in msg()
+    assert lib.ns_thin_gemm_residual(x, w, x, out, ss, 64, 3584, 3584, nul) == UNSUPPORTED and "shared memory" in msg()
+    assert lib.ns_thin_swiglu_gemm_norm(x, ss, 112, w, eps, w, out, 33, 4864, 896, nul) == UNSUPPORTED and "33 token rows" in msg()
+    assert lib.ns_thin_swiglu_gemm_norm(x, ss, 0, w, eps, w, out, 8, 4864, 896, nul) == INVALID and "bad shape" in msg()
+    assert lib.ns_thin_swiglu_gemm_norm(x, ss, 192, w, eps, w, out, 8, 8960, 1536, nul) == UNSUPPORTED and "shared memory" in msg()
+    assert lib.ns_thin_swiglu_gemm_norm(x, nul, 112, w, eps, w, out, 8, 4864, 896, nul) == INVALID and "null pointer" in msg()
 
 
 def test_no_undeclared_entry_point_is_exported():
