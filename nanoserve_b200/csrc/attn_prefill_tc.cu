@@ -133,6 +133,9 @@ __device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* 
         : "memory");
 }
 
+// Named barrier 1: the 128 softmax threads and the issuing warp meet once, when Q is in place.
+__device__ __forceinline__ void q_ready_barrier() { asm volatile("bar.sync 1, %0;" ::"r"(kRows + 32) : "memory"); }
+
 __device__ __forceinline__ void mbar_arrive(uint32_t mbar_saddr) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_saddr) : "memory");
 }
@@ -240,10 +243,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             cp_async16(sQ + (c >> 3) * (kRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4), src + c * 8, row_ok ? 16 : 0);
     }
     cp_async_commit();
-    cp_async_wait<0>();
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes of Q -> visible to the MMA
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();                                                   // barriers initialised, tensor memory allocated, Q in place
+    __syncthreads();                  // barriers initialised, tensor memory allocated; Q is still on its way, so that the
+                                      // copying lane's first K/V requests travel beside it
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
     const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);     // this warp's 32 lanes; lane = row
@@ -292,7 +294,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             v_issued = kt + 1;
         }
         if (!ok) abort_flag = 1;
-    } else if (issuer) {
+    } else if (warp == 4) {
+        q_ready_barrier();            // the softmax threads' Q rows are in shared memory and visible to the tensor cores
+        if (issuer) {
         // ---- descriptors, built once: an instruction's operand is the base plus a byte offset (>> 4) in the address field
         constexpr uint32_t idesc_s = instr_desc(false, kKeys), idesc_pv = instr_desc(true, HD);
         const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
@@ -338,7 +342,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             if (kt + 2 < n_tiles) issue_s(kt + 2);
         }
         if (!ok) abort_flag = 1;
+        }
     } else if (worker) {
+        cp_async_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes of Q -> visible to the MMA
+        q_ready_barrier();
         const int limit = ctx + tok;      // last key this row may see
         const uint32_t t_o = t_lane + COL_O;
         const volatile uint32_t* abort_now = &abort_flag;
