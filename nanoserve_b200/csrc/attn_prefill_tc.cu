@@ -39,11 +39,17 @@ namespace tc {
 constexpr int kRows = 128;          // UMMA M = softmax threads (one per row)
 constexpr int kThreads = kRows + 64; // + one warp whose first lane issues every tcgen05.mma + one whose first lane copies
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
-constexpr int kStagesK = 3;         // K tiles in shared memory (S runs two tiles ahead of the tile in softmax)
-constexpr int kStagesV = 4;         // V tiles: one more, PV(j) still reads V(j) when K(j)'s buffer is long free
-// mbarriers: S0 S1 PV0 PV1 | K full x3 | V full x4 | K free x3 | V free x4 | P0 P1 ready (one arrival per softmax thread)
-constexpr int kBarS = 0, kBarPV = 2, kBarKFull = 4, kBarVFull = kBarKFull + kStagesK, kBarKFree = kBarVFull + kStagesV,
-              kBarVFree = kBarKFree + kStagesK, kBarPReady = kBarVFree + kStagesV, kBars = kBarPReady + 2;
+// Pipeline depth per head size. head_dim 64: K three tiles deep (S runs two tiles ahead of the tile in softmax), V four, P
+// double buffered - 104 KB, two CTAs per SM. head_dim 128 (tiles twice as large): two K, two V, ONE P buffer - 112 KB, so
+// that two CTAs fit an SM there too; a softmax thread then waits for PV(j-1) before it overwrites P, and the second CTA
+// fills that gap.
+template <int HD> struct Depth {
+    static constexpr int K = HD == 64 ? 3 : 2, V = HD == 64 ? 4 : 2, P = HD == 64 ? 2 : 1;
+    // mbarriers: S0 S1 PV0 PV1 | K full | V full | K free | V free | P0 P1 ready (one arrival per softmax thread)
+    static constexpr int BarS = 0, BarPV = 2, BarKFull = 4, BarVFull = BarKFull + K, BarKFree = BarVFull + V, BarVFree = BarKFree + K,
+                         BarPReady = BarVFree + V, Bars = BarPReady + 2;
+};
+constexpr int kTailBytes = 256;     // mbarriers, the tensor-memory address and the abort flag, behind the tiles
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kDefaultCluster = 1;  // CTAs sharing one work item's key tiles (see launch_prefill_tc_hd)
 
@@ -173,19 +179,23 @@ constexpr float kRescaleStep = 8.f;   // the exponent's reference may lag the ro
 }  // namespace tc
 
 template <int HD>
-__global__ void __launch_bounds__(tc::kThreads, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(tc::kThreads, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
     using namespace tc;
+    using D = Depth<HD>;
+    constexpr int kStagesK = D::K, kStagesV = D::V, kBufsP = D::P;
+    constexpr int kBarS = D::BarS, kBarPV = D::BarPV, kBarKFull = D::BarKFull, kBarVFull = D::BarVFull, kBarKFree = D::BarKFree,
+                  kBarVFree = D::BarVFree, kBarPReady = D::BarPReady, kBars = D::Bars;
+    static_assert(kBars * 8 + 8 <= kTailBytes, "the tail holds the barriers and two words");
     constexpr int ATOMS = HD / 64;                  // 128-byte-wide swizzle atoms per head row
     constexpr int Q_BYTES = kRows * 128 * ATOMS;    // [atom][128 rows][128 B]
     constexpr int KV_BYTES = kKeys * 128 * ATOMS;   // [atom][64 keys][128 B]
     constexpr int P_BYTES = kRows * 128;            // [128 rows][64 keys] bf16
     constexpr uint32_t COL_S = 0, COL_O = 2 * kKeys;             // tensor memory: S0, S1, O
     constexpr uint32_t TMEM_COLS = 256;                            // 128 + HD rounded up to a power of two
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t mbar[kBars];
-    __shared__ uint32_t tmem_slot;
-    __shared__ uint32_t abort_flag;                 // raised when a bounded wait ran out: the copying thread stops too
+    // No static shared memory: the dynamic array then starts at the CTA's first usable byte, which is 1024-byte aligned
+    // on this architecture (the launcher adds 1 KB of slack where there is room, and the kernel checks - see below).
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.ws + p.L.header);
     // The CTAs of a thread-block cluster share one work item: rank r takes the r-th share of its key tiles and the shares
@@ -215,10 +225,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     const int tile0 = (int)(((long long)all_tiles * crank) / csize);              // this CTA's tiles: [tile0, tile0 + n_tiles)
     const int n_tiles = (int)(((long long)all_tiles * (crank + 1)) / csize) - tile0;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
     const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + kStagesK * KV_BYTES, sP = sV + kStagesV * KV_BYTES;
-    const uint32_t bar0 = smem_u32(&mbar[0]);
+    const uint32_t bar0 = sP + kBufsP * P_BYTES;    // the tail: barriers, then two words
     auto bar = [&](int i) -> uint32_t { return bar0 + 8u * (uint32_t)i; };
+    volatile uint32_t* tail_words = reinterpret_cast<volatile uint32_t*>(smem_raw + (bar0 - raw) + kBars * 8);
+    volatile uint32_t& tmem_slot = tail_words[0];
+    volatile uint32_t& abort_flag = tail_words[1];  // raised when a bounded wait ran out: the copying thread stops too
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (bar0 - raw + kTailBytes > dyn_bytes) {      // the array did not start where the launcher's size assumes: never expected
+        if (tid == 0) atomicAdd(&reinterpret_cast<PlanHeader*>(p.ws + p.L.header)->errors, 1);
+        if (p.overlap_prefill) pdl_wait();
+        return;
+    }
 
     if (tid == 0) {
 #pragma unroll
@@ -228,7 +249,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         abort_flag = 0;
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bar0 + kBars * 8), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // row of this thread
@@ -272,7 +293,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             const int nb = tile_blocks(kt), sk = kt % kStagesK, sv = kt % kStagesV;
             const uint32_t bytes = (uint32_t)nb * 16u * 128u * ATOMS;
             // K(kt) goes where K(kt - 3) was: free once S(kt - 3) has committed
-            if (kt >= kStagesK && !mbar_wait_or_abort(bar(kBarKFree + sk), (uint32_t)((kt / kStagesK - 1) & 1), &abort_flag)) { ok = false; break; }
+            if (kt >= kStagesK && !mbar_wait_or_abort(bar(kBarKFree + sk), (uint32_t)((kt / kStagesK - 1) & 1), tail_words + 1)) { ok = false; break; }
             mbar_expect_tx(bar(kBarKFull + sk), bytes);
 #pragma unroll
             for (int it = 0; it < kKeys / 16; ++it)
@@ -282,7 +303,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
                         tma_load_block(sK + sk * KV_BYTES + a * (kKeys * 128) + it * 2048, &k_map, a * 64, g, ids[it], bar(kBarKFull + sk));
                 }
             k_issued = kt + 1;
-            if (kt >= kStagesV && !mbar_wait_or_abort(bar(kBarVFree + sv), (uint32_t)((kt / kStagesV - 1) & 1), &abort_flag)) { ok = false; break; }
+            if (kt >= kStagesV && !mbar_wait_or_abort(bar(kBarVFree + sv), (uint32_t)((kt / kStagesV - 1) & 1), tail_words + 1)) { ok = false; break; }
             mbar_expect_tx(bar(kBarVFull + sv), bytes);
 #pragma unroll
             for (int it = 0; it < kKeys / 16; ++it)
@@ -321,7 +342,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             const int sv = kt % kStagesV;
             if (!mbar_wait(bar(kBarVFull + sv), (uint32_t)((kt / kStagesV) & 1))) { ok = false; return; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t p0 = dP + (uint64_t)(((kt & 1) * P_BYTES) >> 4);
+            const uint64_t p0 = dP + (uint64_t)(((kt % kBufsP) * P_BYTES) >> 4);
             const uint64_t v0 = dV + (uint64_t)((sv * KV_BYTES) >> 4);
             const uint32_t d = tmem + COL_O;
 #pragma unroll
@@ -336,7 +357,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         if (n_tiles > 0) issue_s(0);
         if (n_tiles > 1) issue_s(1);
         for (int kt = 0; kt < n_tiles && ok; ++kt) {
-            if (!mbar_wait_or_abort(bar(kBarPReady + (kt & 1)), (uint32_t)((kt >> 1) & 1), &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_or_abort(bar(kBarPReady + (kt & 1)), (uint32_t)((kt >> 1) & 1), tail_words + 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_pv(kt);
             if (kt + 2 < n_tiles) issue_s(kt + 2);
@@ -349,7 +370,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         q_ready_barrier();
         const int limit = ctx + tok;      // last key this row may see
         const uint32_t t_o = t_lane + COL_O;
-        const volatile uint32_t* abort_now = &abort_flag;
+        const volatile uint32_t* abort_now = tail_words + 1;
 
 #ifdef NS_DEBUG_HOOKS
         // profiling build: clock64 stamps of the first work item's thread 0, 8 per key tile, first 16 tiles
@@ -401,16 +422,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 #ifdef NS_DEBUG_HOOKS
                 if (stamps != nullptr && kt < 16) stamps[kt * 8 + 7] = move ? 1 : 0;
 #endif
-                // P(kt) overwrites the buffer PV(kt-2) read: PV(kt-2) was issued before S(kt) by the same thread, so S(kt)'s
-                // commit, waited for above, covers it. Only a move has to wait for PV(kt-1), issued one barrier ago.
+                // With two P buffers P(kt) overwrites what PV(kt-2) read: PV(kt-2) was issued before S(kt) by the same thread, so
+                // S(kt)'s commit, waited for above, covers it. With one buffer, and for a move (which rewrites the output), PV(kt-1)
+                // - issued when the last row of tile kt-1 arrived - has to be over.
+                if ((kBufsP == 1 || move) && kt > 0) {
+                    if (!mbar_wait(bar(kBarPV + ((kt - 1) & 1)), (uint32_t)(((kt - 1) >> 1) & 1))) ok = false;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
                 if (move) {
                     const float m_new = fmaxf(m_run, mx);
                     const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);      // 0 while the row has seen nothing
                     m_run = m_new;
                     l_run *= alpha;
                     if (kt > 0) {
-                        if (!mbar_wait(bar(kBarPV + ((kt - 1) & 1)), (uint32_t)(((kt - 1) >> 1) & 1))) ok = false;
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                         for (int c = 0; c < HD / 32; ++c) {
                             uint32_t r[32];
@@ -426,7 +450,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
                 // a CTA that holds only late tiles of its item can meet rows that see none of its keys yet
                 const float m_ref = m_run == -INFINITY ? 0.f : m_run;
                 float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t p_dst = sP + (kt & 1) * P_BYTES + tid * 128;
+                const uint32_t p_dst = sP + (kt % kBufsP) * P_BYTES + tid * 128;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     float v[32];
@@ -485,22 +509,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         __syncthreads();
     }
 
-    // the row's output leaves tensor memory once, after the last PV
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    if (ok && worker && n_tiles > 0) {
+    // The row's output leaves tensor memory once, after the last PV, 32 columns at a time (registers: the loop above and
+    // this epilogue share one budget that lets two CTAs fit an SM).
+    const bool have_o = ok && worker && n_tiles > 0;      // warp-uniform
+    if (have_o) {
         if (!mbar_wait(bar(kBarPV + ((n_tiles - 1) & 1)), (uint32_t)(((n_tiles - 1) >> 1) & 1))) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+    }
+    auto load_o = [&](int c, float (&v)[32]) {            // columns [32 c, 32 c + 32) of this row; zeros without tiles
+        if (have_o) {
             uint32_t r[32];
             tmem_ld32_issue(t_lane + COL_O + 32 * c, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
-    }
+    };
+    __nv_bfloat16* out_row = p.out + (int64_t)(q0 + (row_ok ? tok : 0)) * p.out_stride + (int64_t)(row_ok ? h : 0) * HD;
+    auto store_o = [&](int c, const float (&v)[32], float inv) {
+        if (!(ok && row_ok)) return;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            uint4 w;
+            w.x = pack_bf16x2(v[8 * e + 0] * inv, v[8 * e + 1] * inv);
+            w.y = pack_bf16x2(v[8 * e + 2] * inv, v[8 * e + 3] * inv);
+            w.z = pack_bf16x2(v[8 * e + 4] * inv, v[8 * e + 5] * inv);
+            w.w = pack_bf16x2(v[8 * e + 6] * inv, v[8 * e + 7] * inv);
+            *reinterpret_cast<uint4*>(out_row + 32 * c + 8 * e) = w;
+        }
+    };
 
     if (csize > 1) {
         // every CTA of the cluster is through its tiles: the first CTA's shared memory is free to receive the others'
@@ -515,45 +555,61 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
             asm volatile("cvta.shared::cluster.u64 %0, %1;" : "=l"(generic) : "l"((uint64_t)remote));
             float* dst = reinterpret_cast<float*>(generic) + ((size_t)(crank - 1) * kRows + tid) * PART_ROW;
 #pragma unroll
-            for (int c = 0; c < HD / 4; ++c)
-                *reinterpret_cast<float4*>(dst + 4 * c) = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                load_o(c, v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    *reinterpret_cast<float4*>(dst + 32 * c + 4 * e) = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+            }
             *reinterpret_cast<float2*>(dst + HD) = make_float2(m_run, l_run);
         }
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (crank == 0 && worker) {
-            const float* mine = reinterpret_cast<const float*>(smem_raw + (base - smem_u32(smem_raw)));
-            for (uint32_t r = 1; r < csize; ++r) {
-                const float* src = mine + ((size_t)(r - 1) * kRows + tid) * PART_ROW;
-                const float2 ml = *reinterpret_cast<const float2*>(src + HD);
-                const float m_new = fmaxf(m_run, ml.x);
-                if (m_new == -INFINITY) continue;
-                const float wa = ex2(m_run - m_new), wb = ex2(ml.x - m_new);
-#pragma unroll
-                for (int c = 0; c < HD / 4; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(src + 4 * c);
-                    o[4 * c] = fmaf(o[4 * c], wa, v.x * wb);
-                    o[4 * c + 1] = fmaf(o[4 * c + 1], wa, v.y * wb);
-                    o[4 * c + 2] = fmaf(o[4 * c + 2], wa, v.z * wb);
-                    o[4 * c + 3] = fmaf(o[4 * c + 3], wa, v.w * wb);
+            const float* mine = reinterpret_cast<const float*>(smem_raw + (base - raw));
+            // weights of the shares under the common maximum, then the output 32 columns at a time
+            float m_fin = m_run;
+            for (uint32_t r = 1; r < csize; ++r) m_fin = fmaxf(m_fin, mine[((size_t)(r - 1) * kRows + tid) * PART_ROW + HD]);
+            float wgt[4] = {0.f, 0.f, 0.f, 0.f};            // [0]: this CTA's share; clusters have at most 4 CTAs
+            float l_fin = 0.f;
+            if (m_fin != -INFINITY) {
+                wgt[0] = ex2(m_run - m_fin);
+                l_fin = l_run * wgt[0];
+                for (uint32_t r = 1; r < csize && r < 4; ++r) {
+                    const float2 ml = *reinterpret_cast<const float2*>(mine + ((size_t)(r - 1) * kRows + tid) * PART_ROW + HD);
+                    wgt[r] = ex2(ml.x - m_fin);
+                    l_fin = fmaf(ml.y, wgt[r], l_fin);
                 }
-                l_run = fmaf(l_run, wa, ml.y * wb);
-                m_run = m_new;
+            }
+            const float inv = l_fin > 0.f ? 1.f / l_fin : 0.f;
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                load_o(c, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] *= wgt[0];
+                for (uint32_t r = 1; r < csize && r < 4; ++r) {
+                    const float* src = mine + ((size_t)(r - 1) * kRows + tid) * PART_ROW + 32 * c;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float4 t = *reinterpret_cast<const float4*>(src + 4 * e);
+                        v[4 * e] = fmaf(t.x, wgt[r], v[4 * e]);
+                        v[4 * e + 1] = fmaf(t.y, wgt[r], v[4 * e + 1]);
+                        v[4 * e + 2] = fmaf(t.z, wgt[r], v[4 * e + 2]);
+                        v[4 * e + 3] = fmaf(t.w, wgt[r], v[4 * e + 3]);
+                    }
+                }
+                store_o(c, v, inv);
             }
         }
-    }
-
-    if (ok && row_ok && crank == 0) {
+    } else if (worker) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = p.out + (int64_t)(q0 + tok) * p.out_stride + (int64_t)h * HD;
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(o[8 * c + 0] * inv, o[8 * c + 1] * inv);
-            v.y = pack_bf16x2(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
-            v.z = pack_bf16x2(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
-            v.w = pack_bf16x2(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
-            *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        for (int c = 0; c < HD / 32; ++c) {
+            float v[32];
+            load_o(c, v);
+            store_o(c, v, inv);
         }
     }
     if (!ok && tid == 0)        // a wait expired: count it where the host can read it (ns_collect_status)
@@ -612,7 +668,10 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, int head_dim, int 
 template <int HD>
 static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t st) {
     constexpr int atoms = HD / 64;
-    constexpr int smem = tc::kRows * 128 * atoms + (tc::kStagesK + tc::kStagesV) * tc::kKeys * 128 * atoms + 2 * tc::kRows * 128 + 1024;
+    using D = tc::Depth<HD>;
+    // tiles + tail; 1 KB of slack for the 1024-byte alignment where two CTAs still fit an SM with it (head_dim 64)
+    constexpr int smem = tc::kRows * 128 * atoms + (D::K + D::V) * tc::kKeys * 128 * atoms + D::P * tc::kRows * 128 + tc::kTailBytes +
+                         (HD == 64 ? 1024 : 0);
     CUtensorMap k_map, v_map;
     if (!tc::make_pool_map(&k_map, p.k_pool, HD, p.n_kv_heads, p.blk_stride, p.pos_stride, p.head_stride) ||
         !tc::make_pool_map(&v_map, p.v_pool, HD, p.n_kv_heads, p.blk_stride, p.pos_stride, p.head_stride))
@@ -627,7 +686,7 @@ static int launch_prefill_tc_hd(const AttnParams& p, int max_items, cudaStream_t
     // a work item's key tiles can be shared by a cluster of CTAs (NS_TUNE_PREFILL_CLUSTER); clamped to what fits: the
     // other CTAs' rows of HD + 4 floats land in the first CTA's shared memory
     int cl = prefill_cluster_size() > 0 ? prefill_cluster_size() : tc::kDefaultCluster;
-    while (cl > 1 && (cl - 1) * tc::kRows * (HD + 4) * 4 > smem - 1024) cl >>= 1;     // the other CTAs' rows must fit the first one's
+    while (cl > 1 && ((cl - 1) * tc::kRows * (HD + 4) * 4 > smem - 1024 - tc::kTailBytes || cl > 4)) cl >>= 1;     // the other CTAs' rows must fit the first one's
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(max_items * cl), (unsigned)p.n_kv_heads);
     cfg.blockDim = dim3(tc::kThreads);
