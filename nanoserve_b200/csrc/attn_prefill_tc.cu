@@ -13,9 +13,10 @@
 //              times that)
 //   warp 5     lane 0 fetches the K/V tiles: one tiled TMA load (cp.async.bulk.tensor, no multicast) per pool block of 16
 //              tokens and 128-byte atom from a 4-D tensor map over THIS GPU's pool [head_dim, kv head, position, block],
-//              128-byte swizzle, K three tiles deep and V four; a stage is refilled when the MMA that read it has
-//              committed (tcgen05.commit -> mbarrier). The softmax threads never touch K or V.
-// Pipeline over the key tiles (S and P double buffered, the output O single): S runs two tiles ahead,
+//              128-byte swizzle, K three tiles deep and V four (head_dim 128: two and two); a stage is refilled when the
+//              MMA that read it has committed (tcgen05.commit -> mbarrier). The softmax threads never touch K or V.
+// Two CTAs per SM at both head sizes (Depth<HD> below). Pipeline over the key tiles (S double buffered, P double buffered
+// at head_dim 64 and single at 128, the output O single): S runs two tiles ahead,
 //   softmax thread, tile j:  wait S(j) | 64 scores into registers | max | (rescale O) | exp, sum, P(j) to shared memory
 //                            | arrive on "P(j) ready" - and on to tile j+1 without waiting for the other rows
 //   issuing lane, tile j:    wait until all 128 rows delivered P(j) | issue PV(j) (O += P.V in tensor memory), S(j+2)
