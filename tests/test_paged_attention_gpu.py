@@ -297,3 +297,38 @@ def test_unused_pool_slots_may_hold_anything(n_heads, n_kv, hd, case):
     out = ragged_paged_attention(*dev(q, k, v, tables, lens, cu), hd ** -0.5).float().cpu()
     assert torch.isfinite(out).all()
     assert (out - ref).abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(14, 2, 64), (28, 4, 128), (16, 2, 128), (7, 1, 128), (8, 4, 64), (3, 3, 64)])
+def test_prefill_chunks_long_contexts_odd_sizes(n_heads, n_kv, hd):
+    """Prefill chunks whose work items run through many key tiles (every mbarrier phase wraps many times) and whose sizes
+    are not multiples of anything: 100 tokens on 6,000 cached, 17 on 4,095, 333 on 1, one token short of a block, a
+    fresh 2-token prompt, next to a few decode rows; GQA groups of 1, 2, 7 and 8."""
+    from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
+    ctx_lens = [6100, 4112, 334, 31, 2, 900, 17]
+    q_lens = [100, 17, 333, 16, 2, 1, 1]
+    q, k, v, tables, lens, cu = make_case(n_heads, n_kv, hd, ctx_lens, torch.bfloat16, q_lens, seed=77)
+    out = ragged_paged_attention(*dev(q, k, v, tables, lens, cu), hd ** -0.5).float().cpu()
+    ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, hd ** -0.5)
+    err = (out - ref).abs().max().item()
+    assert err <= 1e-2, err
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(14, 2, 64), (12, 2, 128)])
+def test_prefill_row_maximum_that_keeps_growing(n_heads, n_kv, hd):
+    """The prefill kernel keeps its running output in tensor memory and rescales it only when a row's maximum has grown
+    past the exponent's reference by a fixed step. Here key j is a fixed direction times j / 64, so for about half of the
+    rows (those whose query points along it) the maximum grows with every key tile and the rescale path runs again and
+    again, while the other rows of the same warp never need it."""
+    from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
+    ctx_lens, q_lens = [2100, 700], [300, 64]
+    q, k, v, tables, lens, cu = make_case(n_heads, n_kv, hd, ctx_lens, torch.bfloat16, q_lens, seed=5)
+    g = torch.Generator().manual_seed(6)
+    direction = torch.randn(n_kv, hd, generator=g)
+    for i, L in enumerate(ctx_lens):
+        for pos in range(L):
+            k[tables[i, pos // 16], pos % 16] = (direction * (pos / 64.0)).to(torch.bfloat16)
+    out = ragged_paged_attention(*dev(q, k, v, tables, lens, cu), hd ** -0.5).float().cpu()
+    ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, hd ** -0.5)
+    err = (out - ref).abs().max().item()
+    assert err <= 1e-2, err
