@@ -101,6 +101,34 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const int32_t* 
         max_nb_sm = 0;
     }
     __syncthreads();
+    // Prefill items heaviest first over the whole step (weight = key tiles of 64 the item walks), ties in the order they
+    // were written: the prefill kernels hand them to CTAs in this order (longest first; where the items are one wave of
+    // two CTAs per SM, the heaviest next to the lightest). One item per thread; steps with more items keep the order above.
+    {
+        __shared__ int item_key[kPlanThreads];
+        const int n = n_items < max_items ? n_items : max_items;
+        if (n > 1 && n <= kPlanThreads) {
+            const int i = threadIdx.x;
+            int2 mine = make_int2(0, 0);
+            if (i < n) {
+                mine = items[i];
+                const int q0 = cu_seqlens[mine.x], T = cu_seqlens[mine.x + 1] - q0, len = seq_lens[mine.x];
+                const int kv_end = min(len, len - T + mine.y + kPrefillTileTokens);
+                item_key[i] = (kv_end + 63) >> 6;
+            }
+            __syncthreads();
+            int rank = 0;
+            if (i < n) {
+                const int k = item_key[i];
+                for (int j = 0; j < n; ++j) {
+                    const int kj = item_key[j];
+                    rank += (kj > k || (kj == k && j < i)) ? 1 : 0;
+                }
+            }
+            __syncthreads();
+            if (i < n) items[rank] = mine;
+        }
+    }
     if (my_max_nb > 0) atomicMax(&max_nb_sm, my_max_nb);
     __syncthreads();
     const int max_nb = max_nb_sm;                  // blocks of the longest decode row

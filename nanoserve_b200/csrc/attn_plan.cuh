@@ -123,6 +123,7 @@ struct AttnParams {
     // once, several kernels before the first layer's attention) and the early reads are safe.
     int plan_fresh = 0;
     int n_seqs = 0;                // sequences of the call (sizes the thread-block cluster of small steps)
+    int sm_count = 0;              // SMs of the device (the prefill kernel pairs heavy and light items on an SM)
 };
 
 }  // namespace ns

@@ -205,13 +205,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     uint32_t crank, csize;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
     asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(csize));
-    const int item_idx = (int)(blockIdx.x / csize);
-    if (item_idx >= hdr->n_prefill_items) {       // the whole cluster leaves together
-        if (p.overlap_prefill) pdl_wait();        // the grid must not complete before the decode kernel it overlaps
-        return;
+    // Which (item, KV head) this CTA takes. The plan lists the items heaviest first. Without cluster sharing the CTAs take
+    // them in the order the hardware hands CTAs out (linear block id): longest first. Where the units are more than one CTA
+    // per SM but at most two (one wave), ids past the first SM-count take the LIGHTEST units first, so that an SM's second
+    // CTA is light where its first is heavy: the kernel lasts as long as its slowest SM, and two heavy items on one SM
+    // (40 + 36 key tiles of 64 in benchmark configuration 1) were that.
+    int item_idx, g;
+    {
+        const int n_items = hdr->n_prefill_items, n_kv = (int)gridDim.y;
+        if (csize > 1) {
+            item_idx = (int)(blockIdx.x / csize);
+            g = blockIdx.y;
+        } else {
+            const int units = n_items * n_kv, S = p.sm_count;
+            const int lin = (int)(blockIdx.x + gridDim.x * blockIdx.y);
+            int r = lin;
+            if (S > 0 && units > S && units <= 2 * S && lin >= S) r = units - 1 - (lin - S);
+            item_idx = lin < units ? r / n_kv : n_items;
+            g = r % n_kv;
+        }
+        if (item_idx >= n_items) {                // the whole cluster leaves together
+            if (p.overlap_prefill) pdl_wait();    // the grid must not complete before the decode kernel it overlaps
+            return;
+        }
     }
     const int2 item = reinterpret_cast<const int2*>(p.ws + p.L.prefill_items)[item_idx];
-    const int s = item.x, q_start = item.y, g = blockIdx.y;
+    const int s = item.x, q_start = item.y;
     const int tid = threadIdx.x, warp = tid >> 5;
     const bool worker = tid < kRows;              // one softmax thread per row
     const bool issuer = tid == kRows;             // first lane of warp 4: every tcgen05.mma

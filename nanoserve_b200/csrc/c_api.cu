@@ -185,6 +185,7 @@ extern "C" int ns_ragged_paged_attn(const void* q, const void* k_pool, const voi
     const bool has_prefill = cu_seqlens != nullptr && n_tokens > n_seqs;
     a.overlap_prefill = (has_prefill && g_tuning[NS_TUNE_PREFILL_OVERLAP]) ? 1 : 0;
     a.n_seqs = n_seqs;
+    a.sm_count = sms;
     a.plan_fresh = (g_fresh_plan_ws == workspace && g_fresh_plan_stream == st) ? 1 : 0;
     g_fresh_plan_ws = nullptr;
     int rc = launch_paged_decode(a, head_dim, sms, st);
