@@ -332,3 +332,23 @@ def test_prefill_row_maximum_that_keeps_growing(n_heads, n_kv, hd):
     ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, hd ** -0.5)
     err = (out - ref).abs().max().item()
     assert err <= 1e-2, err
+
+
+@pytest.mark.parametrize("knob,value", [("TUNE_PREFILL_IMPL", 1), ("TUNE_PREFILL_CLUSTER", 2), ("TUNE_PREFILL_CLUSTER", 4)])
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(14, 2, 64), (12, 2, 128)])
+def test_prefill_fallback_kernel_and_cluster_sharing_match_oracle(knob, value, n_heads, n_kv, hd):
+    """The paths a default call does not take: the mma.sync prefill kernel (the fallback for GQA groups above 8 and for
+    pools no tensor map can describe) and an item's key tiles shared by a cluster of 2 or 4 CTAs with the merge in the
+    first CTA's shared memory (4 is clamped to 2 where three other CTAs' rows do not fit). Same cases, same bound."""
+    from nanoserve_b200 import _lib
+    from nanoserve_b200.kernels.paged_attention import ragged_paged_attention
+    _lib.set_tuning(getattr(_lib, knob), value)
+    try:
+        for case, (ctx_lens, q_lens) in enumerate(MIXED + [([6100, 334, 900], [100, 333, 1])]):
+            q, k, v, tables, lens, cu = make_case(n_heads, n_kv, hd, ctx_lens, torch.bfloat16, q_lens, seed=40 + case)
+            out = ragged_paged_attention(*dev(q, k, v, tables, lens, cu), hd ** -0.5).float().cpu()
+            ref = O.ragged_paged_attention(q.float(), k.float(), v.float(), tables, lens, cu, hd ** -0.5)
+            err = (out - ref).abs().max().item()
+            assert err <= 1e-2, (case, err)
+    finally:
+        _lib.set_tuning(getattr(_lib, knob), 0)
