@@ -60,6 +60,26 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two fp32 values in one 64-bit register pair and the packed FMA-pipe instructions on them.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 // 64-bit shared-memory matrix descriptor, SWIZZLE_128B, version 1 (sm_100): start address, leading-dimension byte
 // offset and stride byte offset are stored without their 4 low bits.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -469,16 +489,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
                 }
                 // a CTA that holds only late tiles of its item can meet rows that see none of its keys yet
                 const float m_ref = m_run == -INFINITY ? 0.f : m_run;
-                float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+                // exponent arguments and row sums two at a time (fma / add .f32x2: half the FMA-pipe instructions)
+                const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
+                uint64_t ps2[2] = {0ull, 0ull};                           // (0.f, 0.f) twice: four chains
                 const uint32_t p_dst = sP + (kt % kBufsP) * P_BYTES + tid * 128;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float e = ex2(fmaf(__uint_as_float(sr[hf][i]), p.scale_log2, -m_ref));
-                        v[i] = e;
-                        ps4[i & 3] += e;
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0, x1;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[hf][i]), __uint_as_float(sr[hf][i + 1])), scale2, neg_m2), x0, x1);
+                        v[i] = ex2(x0);
+                        v[i + 1] = ex2(x1);
+                        ps2[(i >> 1) & 1] = add_f32x2(ps2[(i >> 1) & 1], pack_f32x2(v[i], v[i + 1]));
                     }
                     // P row as bf16 into shared memory (K-major, swizzled like the other operands)
 #pragma unroll
@@ -493,7 +517,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
                                      : "memory");
                     }
                 }
-                l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+                {
+                    float a0, a1, b0, b1;
+                    unpack_f32x2(ps2[0], a0, a1);
+                    unpack_f32x2(ps2[1], b0, b1);
+                    l_run += (a0 + a1) + (b0 + b1);
+                }
                 NS_STAMP(3);
                 // V rows the copies did not bring (blocks past kv_end) or that lie at or past the sequence's length hold
                 // whatever shared memory or the pool's unused slots held: zero them (their P columns are zero, but 0 x NaN is
