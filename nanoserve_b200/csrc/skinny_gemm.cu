@@ -5,7 +5,10 @@
 //   * a CTA owns 64 weight rows and a K-slice; rows arrive by TMA bulk copies (cp.async.bulk, one per row: the
 //     k-slice of a row is one contiguous run) completing on mbarriers - one per warp for its own 16 weight rows, one
 //     for the activations - so a CTA issues ~100 copy instructions instead of ~10,000 16-byte ones; rows are padded
-//     by 16 bytes in shared memory so ldmatrix is conflict-free without a swizzle;
+//     by 16 bytes in shared memory so ldmatrix is conflict-free without a swizzle. The plain GEMM (no prologue, bias
+//     epilogue: down_proj) fetches its WEIGHTS by tiled TMA loads instead - boxes of 64 rows x 32 columns from a tensor
+//     map over W, 64-byte swizzle, 19 instructions for a 608-column slice where the per-row copies were 64: issuing the
+//     copies was 1.4 us of the kernel's 5.7;
 //   * 4 warps x (16 weight rows x all token rows) of mma.sync m16n8k16 bf16 -> fp32;
 //   * narrow-N GEMMs (o_proj, down_proj, QKV) are split over K across a thread-block cluster; the partial tiles are
 //     pushed into the shared memory of the rank that finishes the row and summed there in rank order (deterministic,
@@ -17,6 +20,7 @@
 // Rounding points are those of the unfused ops: GEMM result (+bias) rounded to bf16 first, then every elementwise op
 // rounded to bf16 as the framework would.
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 #include "common.cuh"
 
@@ -81,11 +85,21 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
+// One box [64 rows x 32 columns] of a row-major bf16 matrix into shared memory (4 KB, 64-byte swizzle); no multicast.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int col, int row, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(col), "r"(row), "r"(mbar)
+                 : "memory");
+}
+constexpr int kBoxCols = 32;         // columns per weight box: 64 bytes, the span of the 64-byte swizzle
+
 constexpr int kBN = 64;              // weight rows per CTA
 constexpr int kGemmThreads = 128;
 
-template <int MT, int EPI>
-__global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmParams p) {
+// WTMA: the weights arrive by tiled TMA loads into [k-slice / 32 boxes][64 rows][64 bytes], 64-byte swizzle (16-byte
+// chunk c of row r sits at chunk c ^ ((r >> 1) & 3)), instead of one bulk copy per row into padded rows.
+template <int MT, int EPI, bool WTMA>
+__global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const GemmParams p) {
     constexpr int MP = 16 * MT;                         // padded token rows
     extern __shared__ __align__(128) uint8_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
@@ -96,8 +110,9 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     const int a_stride = ks * 2 + 16;                   // bytes per activation row in shared memory (+16: no bank conflicts)
     uint8_t* a_sm = smem;
     uint8_t* w_sm = smem + (size_t)MP * a_stride;       // 4 warps x [16 weight rows][k-slice], rows padded like a_sm
-    w_sm += (128 - (reinterpret_cast<uintptr_t>(w_sm) & 127)) & 127;
-    float* c_sm = reinterpret_cast<float*>(w_sm + (size_t)kBN * a_stride);          // [csize][rows per rank][64] fp32
+    constexpr uint32_t W_ALIGN = WTMA ? 1024 : 128;
+    w_sm += (W_ALIGN - (smem_u32(w_sm) & (W_ALIGN - 1))) & (W_ALIGN - 1);
+    float* c_sm = reinterpret_cast<float*>(w_sm + (WTMA ? (size_t)kBN * ks * 2 : (size_t)kBN * a_stride));   // [csize][rows per rank][64] fp32
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // QKV only: the attention kernel that follows fetches its plan, block ids and older K/V rows while this GEMM runs.
@@ -113,24 +128,33 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
     // Loads: one TMA bulk copy per row (the k-slice of a row is one contiguous run), completing on mbarriers: one
     // barrier for the activations, one per warp for its own 16 weight rows. ~100 copy instructions per CTA.
     __shared__ __align__(8) uint64_t mbars[5];
-    const uint32_t mb_a = smem_u32(&mbars[4]), mb_w = smem_u32(&mbars[warp]);
+    const uint32_t mb_a = smem_u32(&mbars[4]), mb_w = smem_u32(&mbars[WTMA ? 0 : warp]);
     const uint32_t row_bytes = (uint32_t)ks * 2;
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < 5; ++i) mbar_init(smem_u32(&mbars[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // the byte counts are known now; every copy that completes on these barriers is issued after the barrier below
-        for (int i = 0; i < 4; ++i) {
-            int valid = 0;
-            for (int r = 0; r < 16; ++r) valid += w_row(16 * i + r) < p.N;
-            mbar_expect_tx(smem_u32(&mbars[i]), valid * row_bytes);
+        if (WTMA) {
+            mbar_expect_tx(smem_u32(&mbars[0]), (uint32_t)kBN * row_bytes);     // a box counts in full, rows past N arrive as zeros
+        } else {
+            for (int i = 0; i < 4; ++i) {
+                int valid = 0;
+                for (int r = 0; r < 16; ++r) valid += w_row(16 * i + r) < p.N;
+                mbar_expect_tx(smem_u32(&mbars[i]), valid * row_bytes);
+            }
         }
         if (p.ln_w == nullptr) mbar_expect_tx(mb_a, (uint32_t)p.M * row_bytes);
     }
     __syncthreads();
     cluster_arrive();                                   // "this CTA runs": peers wait for it before they store into c_sm
     const uint32_t my_w = smem_u32(w_sm) + (uint32_t)(16 * warp) * a_stride;
-    {
+    if (WTMA) {
+        if (tid == 0) {
+            const uint32_t wb = smem_u32(w_sm);
+            for (int j = 0; j < ks / kBoxCols; ++j) tma_load_box(wb + j * (kBN * kBoxCols * 2), &w_map, k0 + j * kBoxCols, tile * kBN, mb_w);
+        }
+    } else {
         // this warp's weight rows
         if (lane < 16) {
             const int wr = w_row(16 * warp + lane);
@@ -209,9 +233,16 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
         // fragments one k-step ahead of the mma that use them (ldmatrix -> mma back to back was ~100 cycles per k-step)
         struct Frag { uint32_t b[4]; uint32_t a[MT][4]; };
         const uint32_t b_addr = my_w + ((lane & 7) + ((lane >> 4) << 3)) * a_stride + (((lane >> 3) & 1) << 3) * 2;
+        // WTMA: this lane's row of the CTA tile, its swizzle term and which 16-byte half of a k-step it fetches
+        const uint32_t b_row = (uint32_t)(16 * warp + (lane & 7) + ((lane >> 4) << 3)), b_half = (lane >> 3) & 1;
+        const uint32_t b_tma = smem_u32(w_sm) + b_row * (kBoxCols * 2), b_sw = (b_row >> 1) & 3;
         const uint32_t a_addr = a_base + ((lane & 7) + (((lane >> 3) & 1) << 3)) * a_stride + ((lane >> 4) << 3) * 2;
         auto load_frag = [&](Frag& f, int kk) {
-            ldmatrix_x4(b_addr + kk * 32, f.b[0], f.b[1], f.b[2], f.b[3]);
+            if (WTMA)
+                ldmatrix_x4(b_tma + (uint32_t)(kk >> 1) * (kBN * kBoxCols * 2) + ((((uint32_t)(kk & 1) << 1 | b_half) ^ b_sw) << 4), f.b[0],
+                            f.b[1], f.b[2], f.b[3]);
+            else
+                ldmatrix_x4(b_addr + kk * 32, f.b[0], f.b[1], f.b[2], f.b[3]);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a_addr + 16 * mt * a_stride + kk * 32, f.a[mt][0], f.a[mt][1], f.a[mt][2], f.a[mt][3]);
         };
@@ -315,12 +346,47 @@ __global__ void __launch_bounds__(kGemmThreads) skinny_gemm_kernel(const GemmPar
 
 namespace ns {
 
-template <int MT, int EPI>
-static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
-    const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + 128 + (size_t)(16 * MT + 8) * kBN * 4;
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map over row-major bf16 weights [N, K] for boxes of 64 rows x 32 columns, 64-byte swizzle, zero fill past the
+// matrix. Weights do not move: the last few maps are kept per thread, keyed by (pointer, N, K).
+static const CUtensorMap* weight_map(const void* w, int N, int K) {
+    struct Entry { const void* w; int N, K; CUtensorMap map; };
+    static thread_local Entry cache[64];
+    static thread_local int next = 0;
+    for (Entry& e : cache)
+        if (e.w == w && e.N == N && e.K == K) return &e.map;
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    Entry& e = cache[next];
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)N};
+    const cuuint64_t gstride[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBoxCols, (cuuint32_t)kBN};
+    const cuuint32_t estride[2] = {1, 1};
+    if (fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        e.w = nullptr;
+        return nullptr;
+    }
+    e.w = w; e.N = N; e.K = K;
+    next = (next + 1) % 64;
+    return &e.map;
+}
+
+template <int MT, int EPI, bool WTMA>
+static int launch_skinny_impl(const GemmParams& p, const CUtensorMap& w_map, int tiles, int split_k, cudaStream_t st) {
+    const size_t smem = (size_t)(16 * MT + kBN) * (p.k_slice * 2 + 16) + (WTMA ? 1024 : 128) + (size_t)(16 * MT + 8) * kBN * 4;
     static SmemOptIn optin;
     if (optin.needs(smem)) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, WTMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
                                           cudaGetErrorString(e));
         optin.done(smem);
@@ -339,9 +405,20 @@ static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<MT, EPI>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<MT, EPI, WTMA>, w_map, p);
     if (e != cudaSuccess) return fail(NS_ERR_CUDA, "skinny_gemm: launch failed: %s", cudaGetErrorString(e));
     return NS_OK;
+}
+
+template <int MT, int EPI>
+static int launch_skinny(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
+    // the plain GEMM fetches its weights by tiled TMA loads where the K slice is whole boxes and the driver gives a map
+    if (EPI == kEpiBias && p.ln_w == nullptr && p.k_slice % kBoxCols == 0 && (p.K * 2) % 16 == 0) {
+        const CUtensorMap* map = weight_map(p.w, p.N, p.K);
+        if (map != nullptr) return launch_skinny_impl<MT, EPI, EPI == kEpiBias>(p, *map, tiles, split_k, st);
+    }
+    static const CUtensorMap none = {};
+    return launch_skinny_impl<MT, EPI, false>(p, none, tiles, split_k, st);
 }
 
 template <int EPI> static int dispatch_mt(const GemmParams& p, int tiles, int split_k, cudaStream_t st) {
