@@ -53,12 +53,13 @@ class Sequence:
 
     @property
     def remaining(self) -> int:
-        return self.num_tokens - self.num_cached
+        return len(self.prompt_ids) + len(self.output_ids) - self.num_cached
 
     @property
     def is_prefill(self) -> bool:
         # nothing cached yet (new or preempted), or part-way through a chunked prefill [scheduler.py:56-60]
-        return self.num_cached == 0 or self.remaining > 1
+        # (written out: this runs for every running sequence in every step)
+        return self.num_cached == 0 or len(self.prompt_ids) + len(self.output_ids) - self.num_cached > 1
 
     @property
     def step_cost(self) -> int:
@@ -164,8 +165,10 @@ class Scheduler:
         if self.kv is not None:
             self._make_room_for_decodes()
         budget = self.max_num_batched_tokens
-        decodes = [s for s in self.running if not s.is_prefill]
-        partial = [s for s in self.running if s.is_prefill]
+        decodes: list[Sequence] = []
+        partial: list[Sequence] = []
+        for s in self.running:
+            (partial if s.is_prefill else decodes).append(s)
         scheduled: list[Sequence] = list(decodes)
         chunks: list[int] = [1] * len(decodes)
         budget -= len(decodes)
