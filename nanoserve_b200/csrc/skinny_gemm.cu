@@ -469,7 +469,9 @@ extern "C" int ns_skinny_gemm(const void* x, const void* residual, const void* l
     p.eps = eps;
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const size_t a_bytes = (size_t)(mp + kBN) * (p.k_slice * 2 + 16);
-    NS_REQUIRE(a_bytes + (size_t)(mp + 8) * kBN * 4 + 128 <= 220 * 1024 && p.k_slice <= 1024, NS_ERR_UNSUPPORTED,
+    // (what launch_skinny_impl reserves: both tiles in padded rows, the alignment slack of the TMA form, the receive buffer;
+    // 227 KB is a CTA's limit and the kernel's static shared memory is a few barriers)
+    NS_REQUIRE(a_bytes + (size_t)(mp + 8) * kBN * 4 + 1024 <= 226 * 1024, NS_ERR_UNSUPPORTED,
                "skinny_gemm: K slice of %d does not fit shared memory (raise split_k)", p.k_slice);
     cudaStream_t st = (cudaStream_t)stream;
     if (epilogue == kEpiBias) return dispatch_mt<kEpiBias>(p, (N + kBN - 1) / kBN, split_k, st);

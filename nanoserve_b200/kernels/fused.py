@@ -104,6 +104,17 @@ EPI_RESIDUAL = 2          # ns_stream_gemm's third epilogue (ns_skinny_gemm: 3)
 SKINNY_MAX_ROWS = 64
 
 
+def skinny_gemm_fits(M: int, K: int, split_k: int = 8) -> bool:
+    """Shared memory ns_skinny_gemm needs for M token rows and a K slice of K / split_k (the library's own check):
+    both tiles in padded rows + the cluster's receive buffer + alignment slack within 226 KB."""
+    if K % (16 * split_k) != 0:
+        return False
+    mp = 16 if M <= 16 else (32 if M <= 32 else 64)
+    ks = K // split_k
+    return (mp + 64) * (ks * 2 + 16) + (mp + 8) * 64 * 4 + 1024 <= 226 * 1024
+
+
+
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, split_k: int = 1,
                 ln_w: torch.Tensor | None = None, residual: torch.Tensor | None = None, eps: float = 1e-6,
                 want_residual: bool = False, epilogue: int = EPI_BIAS, cos: torch.Tensor | None = None,

@@ -330,7 +330,7 @@ class Qwen2Model:
         sequence's last token. Fused path only."""
         if not self.fused:
             raise NotImplementedError("forward_step is the fused-kernel path: use model.with_fused_ops()")
-        from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin,
+        from nanoserve_b200.kernels.fused import (EPI_ROPE_KV, EPI_SILU_MUL, SKINNY_MAX_ROWS, rms_norm as norm, rope_cos_sin, skinny_gemm_fits,
                                                   rope_qkv, silu_mul, skinny_gemm, stream_gemm, stream_gemm_supported, swiglu_gemm,
                                                   sm_count, swiglu_gemm_supported, thin_gemm, thin_gemm_ctas, thin_gemm_supported, thin_swiglu_gemm,
                                                   thin_swiglu_gemm_supported, thin_gemm_residual, thin_swiglu_gemm_norm,
@@ -345,7 +345,10 @@ class Qwen2Model:
         # dependent launch). Larger steps keep F.linear everywhere.
         inter = self.layers[0].down_w.shape[1]
         skinny = self.dtype == torch.bfloat16 and T <= SKINNY_MAX_ROWS and self.skinny_gemms
-        skinny_down = skinny and inter % 128 == 0 and inter // 8 <= 1024
+        # down_proj on the split-K cluster kernel where its K slice fits shared memory; slices above 1024 columns (1.5B shape:
+        # 1120) only up to 16 rows - at 32 rows the library GEMM is faster there (28-layer decode step 1,661 vs 1,739 us;
+        # at 16 rows 1,491 vs 1,462)
+        skinny_down = skinny and inter % 128 == 0 and skinny_gemm_fits(T, inter) and (inter // 8 <= 1024 or T <= 16)
         hidden = cfg.hidden_size
         import os
         # Which kernel serves which GEMM is a bit mask (NS_SKINNY_MASK; NS_SKINNY_MASK_SMALL for steps of at most 16 rows):
