@@ -201,6 +201,7 @@ swiglu_umma_kernel(const __grid_constant__ CUtensorMap w_main, const __grid_cons
     } else if (warp == 0 && lane == 0) {
         // ---- MMA issuer ---------------------------------------------------------------------------------------------
         constexpr uint32_t idesc = instr_desc(NT);
+        const uint64_t dA = smem_desc(sA), dB = smem_desc(sB);
         bool ok = mbar_wait(smem_u32(&b_full), 0);
         if (tl) tl[16] = clock64() - t_start;
         for (int c = 0; c < NC && ok; ++c) {
@@ -208,10 +209,12 @@ swiglu_umma_kernel(const __grid_constant__ CUtensorMap w_main, const __grid_cons
             if (!ok) break;
             if (tl && c < 30) tl[17 + c] = clock64() - t_start;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = sA + (uint32_t)(c % S) * stage_bytes, b = sB + (uint32_t)c * kBChunk;
+            // descriptors = the bases built once + a byte offset (>> 4) in the address field: a lone thread that builds two
+            // 64-bit descriptors per instruction needs ~190 cycles per tcgen05.mma, one that adds an offset ~40
+            const uint64_t a = dA + (uint64_t)(((uint32_t)(c % S) * stage_bytes) >> 4), b = dB + (uint64_t)(((uint32_t)c * kBChunk) >> 4);
 #pragma unroll
             for (int kk = 0; kk < kChunk / 16; ++kk)       // 16 columns per instruction = 32 bytes along K
-                mma_f16(tmem, smem_desc(a + kk * 32), smem_desc(b + kk * 32), idesc, (c > 0 || kk > 0) ? 1u : 0u);
+                mma_f16(tmem, a + (uint64_t)((kk * 32) >> 4), b + (uint64_t)((kk * 32) >> 4), idesc, (c > 0 || kk > 0) ? 1u : 0u);
             mma_commit(smem_u32(&empty_bar[c % S]));       // arrives when the MMAs above have read the stage
         }
         if (!ok) atomicExch(&failed, 1);
