@@ -13,10 +13,10 @@
 //              times that)
 //   warp 5     lane 0 fetches the K/V tiles: one tiled TMA load (cp.async.bulk.tensor, no multicast) per pool block of 16
 //              tokens and 128-byte atom from a 4-D tensor map over THIS GPU's pool [head_dim, kv head, position, block],
-//              128-byte swizzle, K three tiles deep and V four (head_dim 128: two and two); a stage is refilled when the
+//              128-byte swizzle, K three tiles deep and V four (head_dim 128: one and two); a stage is refilled when the
 //              MMA that read it has committed (tcgen05.commit -> mbarrier). The softmax threads never touch K or V.
-// Two CTAs per SM at both head sizes (Depth<HD> below). Pipeline over the key tiles (S double buffered, P double buffered
-// at head_dim 64 and single at 128, the output O single): S runs two tiles ahead,
+// Two CTAs per SM at both head sizes (Depth<HD> below). Pipeline over the key tiles (S and P double buffered, the output O
+// single): S runs two tiles ahead,
 //   softmax thread, tile j:  wait S(j) | 64 scores into registers | max | (rescale O) | exp, sum, P(j) to shared memory
 //                            | arrive on "P(j) ready" - and on to tile j+1 without waiting for the other rows
 //   issuing lane, tile j:    wait until all 128 rows delivered P(j) | issue PV(j) (O += P.V in tensor memory), S(j+2)
@@ -41,11 +41,12 @@ constexpr int kRows = 128;          // UMMA M = softmax threads (one per row)
 constexpr int kThreads = kRows + 64; // + one warp whose first lane issues every tcgen05.mma + one whose first lane copies
 constexpr int kKeys = 64;           // keys per tile (UMMA N of S, K extent of P.V)
 // Pipeline depth per head size. head_dim 64: K three tiles deep (S runs two tiles ahead of the tile in softmax), V four, P
-// double buffered - 104 KB, two CTAs per SM. head_dim 128 (tiles twice as large): two K, two V, ONE P buffer - 112 KB, so
-// that two CTAs fit an SM there too; a softmax thread then waits for PV(j-1) before it overwrites P, and the second CTA
-// fills that gap.
+// double buffered - 104 KB, two CTAs per SM. head_dim 128 (tiles twice as large): ONE K stage (K(j+2) is fetched as soon as
+// S(j+1) has committed, a whole tile before S(j+2) is issued), two V, P double buffered - 112 KB, so that two CTAs fit an
+// SM there too. (Two K stages with a single P buffer, where every softmax thread waits for PV(j-1) before it overwrites P,
+// measured 4 % slower.)
 template <int HD> struct Depth {
-    static constexpr int K = HD == 64 ? 3 : 2, V = HD == 64 ? 4 : 2, P = HD == 64 ? 2 : 1;
+    static constexpr int K = HD == 64 ? 3 : 1, V = HD == 64 ? 4 : 2, P = 2;
     // mbarriers: S0 S1 PV0 PV1 | K full | V full | K free | V free | P0 P1 ready (one arrival per softmax thread)
     static constexpr int BarS = 0, BarPV = 2, BarKFull = 4, BarVFull = BarKFull + K, BarKFree = BarVFull + V, BarVFree = BarKFree + K,
                          BarPReady = BarVFree + V, Bars = BarPReady + 2;
