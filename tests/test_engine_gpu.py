@@ -389,3 +389,31 @@ def test_bounds_check_counts_bad_metadata_and_stays_silent_on_good_steps(monkeyp
     checked = run_requests(eng, G.tiny_requests(), concurrency=4)
     assert checked == plain and eng.buffers.device_errors == 0
     assert eng.stats["graph_steps"] > 0 and eng.stats["piecewise_steps"] > 0
+
+
+@pytest.mark.parametrize("head_shape", ["qwen2.5-0.5b", "qwen2.5-1.5b"])
+def test_bf16_engine_with_prefix_hits_chunked_prompts_and_preemption_follows_the_oracle(head_shape):
+    """The tensor-core kernels under everything the scheduler can do to them at once (the fp32 tests of these features run
+    on the scalar attention kernel): a two-layer bf16 model of a benchmark layer shape (head_dim 64 / 128), requests that
+    share a 48-token prefix (prefix caching on: later prompts start on cached blocks), a step budget of 80 tokens (prompts
+    are fed in chunks on top of their own context) and a KV pool of 560 tokens, small enough to preempt twice. Stepped beside the fp32 oracle
+    engine, which takes the same decisions: logits within the bf16 bound, tokens under the tie rule, no block leaked."""
+    from nanoserve_b200.engine import LLMEngine
+    from nanoserve_b200.model import ModelConfig, Qwen2Model
+    from nanoserve_b200.synthetic import random_state_dict, serving_requests
+    from oracle.engine import OracleEngine, OracleModel
+    sd32, cfg = random_state_dict(head_shape, dtype=torch.float32, n_layers=2, vocab=4096)
+    sd16 = {k: v.to(torch.bfloat16) for k, v in sd32.items()}
+    kw = dict(max_seq_len=512, max_num_seqs=6, max_num_batched_tokens=80, kv_cache_tokens=560, prefix_caching=True)
+    reqs = serving_requests(12, prompt_range=(20, 200), output_range=(8, 40), vocab=4096, seed=5, shared_prefix=48)
+    eng = LLMEngine(Qwen2Model(ModelConfig(**cfg), {k: v.cuda() for k, v in sd16.items()}), eos_token_ids=[], **kw)
+    ora = OracleEngine(OracleModel(cfg, {k: v.float() for k, v in sd16.items()}), reserve_garbage_block=True, **kw)
+    from tests.parity import run_lockstep
+    got, want, worst = run_lockstep(eng, ora, reqs)
+    assert worst <= 0.10, f"bf16 logits differ from the fp32 oracle by {worst:.4f}"
+    same, accepted = check_tokens(got, want, lambda i, j: ora.gaps[i][j], 2 * worst, what=f"bf16 {head_shape} layers, prefix + chunks")
+    st = eng.stats
+    print(f"{head_shape}: {same}/12 identical, accepted {accepted}, worst {worst:.4f}, preemptions "
+          f"{eng.scheduler.num_preemptions}, prefix hits {st.get('prefix_hit_tokens')}, chunks {st.get('prefill_chunks')}")
+    assert st.get("prefill_chunks", 0) > 0 and st.get("prefix_hit_tokens", 0) > 0 and eng.scheduler.num_preemptions > 0
+    assert eng.buffers.device_errors == 0
